@@ -1,0 +1,422 @@
+"""Cluster -> kernel-template instance.
+
+This module takes the place of the reference's Choreo DSL emitter
+(``conductor/codegen/dslgen.py:154-217`` ``generate_dsl_file``,
+``dslgen.py:524-737`` body generation, ``dma_generator.py:80-268`` tile DMA).  Instead of
+printing a ``.co`` program that a compiler turns into a kernel, it *selects* one of the
+hand-written sm_100a templates of ``libconductor_b200.so`` for each fused cluster and
+fills in that template's parameter block (``include/conductor_b200.h``).
+
+Scope mapping (reference scopes: ``graph_analyzer.py:630-647``): cluster-internal LOCAL
+buffers become virtual registers of the elementwise program and never touch memory;
+SHARED buffers are HBM temporaries owned by the plan; GLOBAL buffers are the caller's
+tensors.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from ..optimization.buffers import Buffer
+from ..optimization.fusion import FusionCluster, FusionType, _is_last_dim_reduction
+from ..utils.exceptions import UnsupportedOperationError
+from ..utils.type_mapping import is_float, is_int, to_cdr_dtype
+from .operator_registry import EwOp, ReduceOp, Template, get_op_desc
+
+# ---------------------------------------------------------------- C structs
+CDR_MAX_RANK = 8
+CDR_EW_MAX_INPUTS = 8
+CDR_EW_MAX_INSTR = 24
+CDR_EW_MAX_OUTPUTS = 4
+
+IN_FULL, IN_ROW, IN_COL, IN_SCALAR = range(4)
+
+
+class CdrTensor(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("dtype", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * CDR_MAX_RANK), ("stride", ctypes.c_int64 * CDR_MAX_RANK)]
+
+
+class CdrEwInstr(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_int32), ("a", ctypes.c_int32), ("b", ctypes.c_int32), ("c", ctypes.c_int32),
+                ("imm", ctypes.c_float), ("round_to", ctypes.c_int32)]
+
+
+class CdrEwParams(ctypes.Structure):
+    _fields_ = [("n_inputs", ctypes.c_int32), ("n_instr", ctypes.c_int32), ("n_outputs", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("input_mode", ctypes.c_int32 * CDR_EW_MAX_INPUTS),
+                ("out_reg", ctypes.c_int32 * CDR_EW_MAX_OUTPUTS), ("instr", CdrEwInstr * CDR_EW_MAX_INSTR)]
+
+
+class CdrReduceParams(ctypes.Structure):
+    _fields_ = [("chain", CdrEwParams), ("reduce_op", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class CdrGemmParams(ctypes.Structure):
+    _fields_ = [("activation", ctypes.c_int32), ("has_bias", ctypes.c_int32)]
+
+
+class CdrAttnParams(ctypes.Structure):
+    _fields_ = [("scale", ctypes.c_float), ("causal", ctypes.c_int32)]
+
+
+# ---------------------------------------------------------------- launch description
+@dataclass
+class KernelLaunch:
+    """One step of a compiled plan."""
+
+    template: int                       # cdr_template id; 0 = alias (no kernel)
+    name: str
+    inputs: list[Buffer]
+    outputs: list[Buffer]
+    params: Any = None                  # ctypes struct or None
+    out_shapes: list[tuple] = field(default_factory=list)
+    out_dtypes: list[torch.dtype] = field(default_factory=list)
+    alias_of: Optional[Buffer] = None   # SHAPE clusters: output is a view of this buffer
+    cluster: Optional[FusionCluster] = None
+    needs_workspace: bool = False
+
+    def describe(self) -> str:
+        ins = ", ".join(b.name for b in self.inputs)
+        outs = ", ".join(f"{b.name}:{b.scope.value}" for b in self.outputs)
+        tname = {0: "alias", 1: "elementwise", 2: "row_reduce", 3: "softmax_fwd", 4: "softmax_bwd",
+                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce"}[self.template]
+        return f"{outs} = {tname}<{self.name}>({ins})"
+
+
+# ---------------------------------------------------------------- elementwise lowering
+def _strip_ones(shape):
+    s = list(shape)
+    while s and s[0] == 1:
+        s.pop(0)
+    return tuple(s)
+
+
+def classify_broadcast(in_shape, out_shape) -> int:
+    """How an input of `in_shape` is indexed against the [rows, cols] view of `out_shape`."""
+    n_in = math.prod(in_shape) if in_shape else 1
+    n_out = math.prod(out_shape) if out_shape else 1
+    if _strip_ones(in_shape) == _strip_ones(out_shape):
+        return IN_FULL
+    if n_in == 1:
+        return IN_SCALAR
+    if n_in == n_out:
+        raise UnsupportedOperationError("broadcast", f"{in_shape} against {out_shape} needs a reshape")
+    cols = out_shape[-1] if out_shape else 1
+    if _strip_ones(in_shape) == (cols,):
+        return IN_ROW
+    aligned = (1,) * (len(out_shape) - len(in_shape)) + tuple(in_shape)
+    if len(aligned) == len(out_shape) and aligned[-1] == 1 and aligned[:-1] == tuple(out_shape[:-1]):
+        return IN_COL
+    raise UnsupportedOperationError("broadcast", f"input {tuple(in_shape)} against output {tuple(out_shape)}")
+
+
+_CAST_METHODS = {"float": torch.float32, "bfloat16": torch.bfloat16, "half": torch.float16}
+_FLOAT_RANK = {torch.bfloat16: 1, torch.float16: 1, torch.float32: 2}
+
+
+class _ProgramBuilder:
+    """Turns the nodes of a cluster into a cdr_ew_params program."""
+
+    def __init__(self, ext_inputs: list[Buffer], iter_shape):
+        if len(ext_inputs) > CDR_EW_MAX_INPUTS:
+            raise UnsupportedOperationError("elementwise", f"{len(ext_inputs)} inputs (max {CDR_EW_MAX_INPUTS})")
+        self.inputs = list(ext_inputs)
+        self.iter_shape = tuple(iter_shape)
+        self.reg_of: dict[Buffer, int] = {b: i for i, b in enumerate(self.inputs)}
+        self.instr: list[tuple] = []
+        self.is_int = bool(self.inputs) and all(is_int(b.dtype) for b in self.inputs)
+
+    def _emit(self, op, a=0, b=0, c=0, imm=0.0, dtype=torch.float32) -> int:
+        if len(self.instr) >= CDR_EW_MAX_INSTR:
+            raise UnsupportedOperationError("elementwise", f"more than {CDR_EW_MAX_INSTR} instructions")
+        self.instr.append((op, a, b, c, float(imm), to_cdr_dtype(dtype)))
+        return len(self.inputs) + len(self.instr) - 1
+
+    def _operand(self, node, spec, dtype) -> int:
+        kind, val = spec
+        if kind == "buf":
+            return self.reg_of[node.inputs[val]]
+        if kind == "const" and isinstance(val, (int, float, bool)):
+            return self._emit(EwOp.CONST, imm=val, dtype=dtype)
+        raise UnsupportedOperationError(node.op_name, f"operand {val!r} cannot be lowered")
+
+    def lower(self, node) -> None:
+        info = get_op_desc(node.op_name)
+        out = node.outputs[0]
+        odt = out.dtype
+        spec = list(node.metadata.get("arg_spec", []))
+        kw = node.metadata.get("kwargs", {})
+        kws = node.metadata.get("kwarg_spec", {})
+        op = info.ew_op
+
+        def is_buf(s):
+            return s[0] == "buf"
+
+        def is_num(s):
+            return s[0] == "const" and isinstance(s[1], (int, float)) and not isinstance(s[1], bool)
+
+        if op == EwOp.COPY:                                   # dtype cast
+            src = self._operand(node, spec[0], odt)
+            src_dt = node.inputs[spec[0][1]].dtype if is_buf(spec[0]) else odt
+            widening = (src_dt == odt) or (is_float(src_dt) and is_float(odt)
+                                          and _FLOAT_RANK[odt] > _FLOAT_RANK[src_dt])
+            self.reg_of[out] = src if widening else self._emit(EwOp.COPY, src, dtype=odt)
+            return
+        if op in (EwOp.ADD, EwOp.SUB, EwOp.MUL, EwOp.DIV, EwOp.MAX, EwOp.MIN):
+            if len(spec) < 2:
+                raise UnsupportedOperationError(node.op_name, "needs two operands")
+            alpha = kw.get("alpha", 1)
+            if alpha != 1:
+                raise UnsupportedOperationError(node.op_name, "alpha != 1")
+            if kw.get("rounding_mode") is not None:
+                raise UnsupportedOperationError(node.op_name, "rounding_mode")
+            a, b = spec[0], spec[1]
+            if is_buf(a) and is_num(b):
+                ra = self._operand(node, a, odt)
+                if op == EwOp.ADD:
+                    r = self._emit(EwOp.ADD_IMM, ra, imm=b[1], dtype=odt)
+                elif op == EwOp.SUB:
+                    r = self._emit(EwOp.ADD_IMM, ra, imm=-b[1], dtype=odt)
+                elif op == EwOp.MUL:
+                    r = self._emit(EwOp.MUL_IMM, ra, imm=b[1], dtype=odt)
+                else:
+                    r = self._emit(op, ra, self._operand(node, b, odt), dtype=odt)
+            elif is_num(a) and is_buf(b):
+                rb = self._operand(node, b, odt)
+                if op == EwOp.ADD:
+                    r = self._emit(EwOp.ADD_IMM, rb, imm=a[1], dtype=odt)
+                elif op == EwOp.MUL:
+                    r = self._emit(EwOp.MUL_IMM, rb, imm=a[1], dtype=odt)
+                elif op == EwOp.SUB:
+                    r = self._emit(EwOp.RSUB_IMM, rb, imm=a[1], dtype=odt)
+                elif op == EwOp.DIV:
+                    r = self._emit(EwOp.RDIV_IMM, rb, imm=a[1], dtype=odt)
+                else:
+                    r = self._emit(op, self._operand(node, a, odt), rb, dtype=odt)
+            else:
+                r = self._emit(op, self._operand(node, a, odt), self._operand(node, b, odt), dtype=odt)
+            self.reg_of[out] = r
+            return
+        if op in (EwOp.ADDCDIV, EwOp.ADDCMUL):
+            value = kw.get("value", 1)
+            if len(spec) > 3 and spec[3][0] == "const":
+                value = spec[3][1]
+            regs = [self._operand(node, s, odt) for s in spec[:3]]
+            self.reg_of[out] = self._emit(op, regs[0], regs[1], regs[2], imm=value, dtype=odt)
+            return
+        if info.arity == 1:                                   # unary math / relu
+            self.reg_of[out] = self._emit(op, self._operand(node, spec[0], odt), dtype=odt)
+            return
+        raise UnsupportedOperationError(node.op_name, "no elementwise lowering")
+
+    def build(self, out_regs: list[int]) -> CdrEwParams:
+        p = CdrEwParams()
+        p.n_inputs = len(self.inputs)
+        p.n_instr = len(self.instr)
+        p.n_outputs = len(out_regs)
+        for i, b in enumerate(self.inputs):
+            if b.shape is None:
+                raise UnsupportedOperationError("elementwise", f"input {b.name} has no static shape")
+            p.input_mode[i] = classify_broadcast(b.shape, self.iter_shape)
+        for i, r in enumerate(out_regs):
+            p.out_reg[i] = r
+        for i, (op, a, b, c, imm, rt) in enumerate(self.instr):
+            p.instr[i] = CdrEwInstr(op, a, b, c, imm, rt)
+        return p
+
+
+def _require_shapes(cluster: FusionCluster) -> None:
+    for b in cluster.external_inputs + cluster.external_outputs:
+        if b.shape is None:
+            raise UnsupportedOperationError(cluster.signature(), f"buffer {b.name} has no static shape")
+
+
+def _lower_elementwise(cluster: FusionCluster) -> KernelLaunch:
+    _require_shapes(cluster)
+    outs = cluster.external_outputs
+    if not outs or len(outs) > CDR_EW_MAX_OUTPUTS:
+        raise UnsupportedOperationError(cluster.signature(), f"{len(outs)} outputs")
+    iter_shape = outs[0].shape
+    for b in outs:
+        if b.shape != iter_shape:
+            raise UnsupportedOperationError(cluster.signature(), "outputs of different shapes")
+    builder = _ProgramBuilder(cluster.external_inputs, iter_shape)
+    for node in cluster._topological_sort():
+        if node.outputs[0].shape != iter_shape:
+            raise UnsupportedOperationError(cluster.signature(), "intermediate of a different shape")
+        builder.lower(node)
+    out_regs = [builder.reg_of[b] for b in outs]
+    for i, (b, r) in enumerate(zip(outs, out_regs)):
+        if r < len(builder.inputs):         # output is a pure alias of an input: materialise a copy
+            out_regs[i] = builder._emit(EwOp.COPY, r, dtype=b.dtype)
+    params = builder.build(out_regs)
+    return KernelLaunch(Template.ELEMENTWISE, cluster.signature(), list(cluster.external_inputs), list(outs),
+                        params, [b.shape for b in outs], [b.dtype for b in outs], cluster=cluster)
+
+
+def _lower_reduction(cluster: FusionCluster) -> KernelLaunch:
+    _require_shapes(cluster)
+    order = cluster._topological_sort()
+    red = [n for n in order if n.is_reduction()]
+    if len(red) != 1 or order[-1] is not red[0]:
+        raise UnsupportedOperationError(cluster.signature(), "expected a chain ending in one reduction")
+    red = red[0]
+    last = _is_last_dim_reduction(red)
+    if last is False:
+        raise UnsupportedOperationError(red.op_name, "only the last dimension (or all) can be reduced")
+    full_shape = red.inputs[0].shape
+    if not full_shape:
+        raise UnsupportedOperationError(red.op_name, "rank-0 input")
+    builder = _ProgramBuilder(cluster.external_inputs, full_shape)
+    for node in order[:-1]:
+        builder.lower(node)
+    src = builder.reg_of[red.inputs[0]]
+    if not any(classify_broadcast(b.shape, full_shape) == IN_FULL for b in cluster.external_inputs):
+        raise UnsupportedOperationError(cluster.signature(), "no full-size input")
+    out = red.outputs[0]
+    if not is_float(out.dtype):
+        raise UnsupportedOperationError(red.op_name, f"{out.dtype} reduction")
+    p = CdrReduceParams()
+    p.chain = builder.build([src])
+    p.reduce_op = get_op_desc(red.op_name).reduce_op
+    template = Template.FULL_REDUCE if last is None else Template.ROW_REDUCE
+    return KernelLaunch(template, cluster.signature(), list(cluster.external_inputs), [out], p, [out.shape],
+                        [out.dtype], cluster=cluster, needs_workspace=template == Template.FULL_REDUCE)
+
+
+def _const_args(node):
+    return [v for k, v in node.metadata.get("arg_spec", []) if k == "const"]
+
+
+def _lower_softmax(cluster: FusionCluster) -> KernelLaunch:
+    _require_shapes(cluster)
+    if cluster.pattern == "softmax_bwd_written_out":
+        roles = cluster.nodes[0].metadata["softmax_bwd_roles"]
+        out = cluster.external_outputs[0]
+        return KernelLaunch(Template.SOFTMAX_BWD, cluster.signature(), [roles["grad"], roles["y"]], [out], None,
+                            [out.shape], [out.dtype], cluster=cluster)
+    node = cluster.nodes[0]
+    kw = node.metadata.get("kwargs", {})
+    consts = _const_args(node)
+    out = node.outputs[0]
+    if node.op_name == "softmax":
+        x = node.inputs[0]
+        dim = kw.get("dim", consts[0] if consts else None)
+        dtype = kw.get("dtype", consts[2] if len(consts) > 2 else None)
+        if dim is None or (dim % len(x.shape)) != len(x.shape) - 1:
+            raise UnsupportedOperationError("softmax", f"dim={dim}; only the last dimension is supported")
+        if dtype is not None and dtype != x.dtype:
+            raise UnsupportedOperationError("softmax", "dtype conversion inside softmax")
+        if kw.get("_half_to_float", consts[1] if len(consts) > 1 and isinstance(consts[1], bool) else False):
+            raise UnsupportedOperationError("softmax", "half_to_float")
+        return KernelLaunch(Template.SOFTMAX_FWD, cluster.signature(), [x], [out], None, [out.shape], [out.dtype],
+                            cluster=cluster)
+    if node.op_name == "_softmax_backward_data":
+        g, y = node.inputs[0], node.inputs[1]
+        dim = kw.get("dim", consts[0] if consts else None)
+        if dim is None or (dim % len(y.shape)) != len(y.shape) - 1:
+            raise UnsupportedOperationError("_softmax_backward_data", f"dim={dim}")
+        return KernelLaunch(Template.SOFTMAX_BWD, cluster.signature(), [g, y], [out], None, [out.shape], [out.dtype],
+                            cluster=cluster)
+    raise UnsupportedOperationError(node.op_name, "not a softmax operation")
+
+
+def _lower_gemm(cluster: FusionCluster) -> KernelLaunch:
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    if node.op_name != "linear":
+        raise UnsupportedOperationError(node.op_name, "only linear(x, W, b) lowers to the GEMM template")
+    spec = node.metadata.get("arg_spec", [])
+    kws = node.metadata.get("kwarg_spec", {})
+    ops = [s for s in spec if s[0] == "buf"]
+    if "bias" in kws and kws["bias"][0] == "buf":
+        ops.append(kws["bias"])
+    bufs = [node.inputs[s[1]] for s in ops]
+    if len(bufs) not in (2, 3):
+        raise UnsupportedOperationError("linear", "expected (x, weight[, bias])")
+    x, w = bufs[0], bufs[1]
+    if len(w.shape) != 2 or x.shape[-1] != w.shape[1]:
+        raise UnsupportedOperationError("linear", f"shapes {x.shape} x {w.shape}")
+    act = 0
+    if len(cluster.nodes) == 2:
+        if cluster.nodes[1].op_name != "relu":
+            raise UnsupportedOperationError(cluster.signature(), "unsupported epilogue")
+        act = 1
+    out = cluster.external_outputs[0]
+    p = CdrGemmParams(act, 1 if len(bufs) == 3 else 0)
+    return KernelLaunch(Template.GEMM_EPILOGUE, cluster.signature(), bufs, [out], p, [out.shape], [out.dtype],
+                        cluster=cluster)
+
+
+def _lower_attention(cluster: FusionCluster) -> KernelLaunch:
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    kw = node.metadata.get("kwargs", {})
+    kws = node.metadata.get("kwarg_spec", {})
+    spec = node.metadata.get("arg_spec", [])
+    bufs = [node.inputs[s[1]] for s in spec if s[0] == "buf"]
+    if len(bufs) != 3 or any(v[0] == "buf" for v in kws.values()):
+        raise UnsupportedOperationError("scaled_dot_product_attention", "attn_mask tensors are not supported")
+    consts = _const_args(node)
+    if kw.get("attn_mask") is not None or (consts and consts[0] is not None):
+        raise UnsupportedOperationError("scaled_dot_product_attention", "attn_mask")
+    dropout = kw.get("dropout_p", consts[1] if len(consts) > 1 else 0.0)
+    if dropout:
+        raise UnsupportedOperationError("scaled_dot_product_attention", "dropout")
+    if kw.get("enable_gqa"):
+        raise UnsupportedOperationError("scaled_dot_product_attention", "enable_gqa")
+    causal = bool(kw.get("is_causal", consts[2] if len(consts) > 2 else False))
+    q = bufs[0]
+    scale = kw.get("scale", consts[3] if len(consts) > 3 else None)
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    out = node.outputs[0]
+    p = CdrAttnParams(float(scale), 1 if causal else 0)
+    return KernelLaunch(Template.ATTENTION, cluster.signature(), bufs, [out], p, [out.shape], [out.dtype],
+                        cluster=cluster, needs_workspace=True)
+
+
+def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
+    node = cluster.nodes[0]
+    out = node.outputs[0]
+    if out.shape is None or not node.inputs:
+        raise UnsupportedOperationError(node.op_name, "unknown output shape")
+    src = node.inputs[0]
+    if src.shape is not None and math.prod(src.shape) != math.prod(out.shape):
+        raise UnsupportedOperationError(node.op_name, "element count changes")
+    return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
+                        cluster=cluster)
+
+
+_LOWERING = {
+    FusionType.ELEMENTWISE: _lower_elementwise,
+    FusionType.REDUCTION: _lower_reduction,
+    FusionType.SOFTMAX: _lower_softmax,
+    FusionType.GEMM_EPILOGUE: _lower_gemm,
+    FusionType.ATTENTION: _lower_attention,
+    FusionType.SHAPE: _lower_shape,
+}
+
+
+class KernelTemplateSelector:
+    """Public face of this module; plays the role of ``ChoreoDslGen`` in the reference pipeline
+    (``jit_compiler.py:150-163`` calls ``generate_dsl_file(dag, function_name)``)."""
+
+    def select(self, cluster: FusionCluster) -> KernelLaunch:
+        fn = _LOWERING.get(cluster.cluster_type)
+        if fn is None:
+            ops = ",".join(n.op_name for n in cluster.nodes)
+            raise UnsupportedOperationError(ops, "no kernel template implements this operation")
+        return fn(cluster)
+
+    def generate_plan_text(self, launches: list[KernelLaunch], function_name: str = "kernel") -> str:
+        """Readable plan, the analogue of the ``.co`` text the reference dumps for debugging."""
+        lines = [f"plan {function_name} {{"]
+        lines += [f"  {l.describe()}" for l in launches]
+        lines.append("}")
+        return "\n".join(lines)

@@ -1,0 +1,170 @@
+"""Operator table: FX op name -> classification and kernel-template binding.
+
+Counterpart of the reference's ``conductor/codegen/operator_registry.py:245-601``,
+whose ``OperatorInfo`` carries Choreo DSL snippets.  Here an operator carries the
+opcode it contributes to an elementwise program (``cdr_ew_op`` in
+``include/conductor_b200.h``) or the template family that implements it.
+
+Differences from the reference table, all needed by the five benchmark graphs:
+  * ``relu`` and the unary math ops are ELEMENTWISE and fusable (the reference
+    registers relu as ACTIVATION, ``operator_registry.py:365-373``, which blocks every
+    chain that contains it);
+  * ``softmax``, ``_softmax_backward_data``, ``linear``, ``scaled_dot_product_attention``,
+    ``addcdiv``, ``addcmul`` and the dtype casts are registered (absent in the reference,
+    ``operator_registry.py:489-500``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from enum import Enum
+from typing import Dict, Optional
+
+from ..utils.constants import FusionLevel
+
+
+class OpType(Enum):
+    """Operation classes (reference: ``operator_registry.py:72-83``)."""
+
+    ELEMENTWISE = "elementwise"
+    REDUCTION = "reduction"
+    MATRIX = "matrix"
+    ACTIVATION = "activation"
+    SHAPE = "shape"
+    MATH = "math"
+    SOFTMAX = "softmax"
+    ATTENTION = "attention"
+    UNKNOWN = "unknown"
+
+
+# cdr_ew_op codes (include/conductor_b200.h)
+class EwOp:
+    ADD, SUB, MUL, DIV, RELU, NEG, ABS, EXP, LOG, SQRT, SIGMOID, TANH, SIN, COS = range(1, 15)
+    MAX, MIN, ADDCDIV, ADDCMUL, CONST, COPY, ADD_IMM, MUL_IMM, RSUB_IMM, RDIV_IMM = range(15, 25)
+
+
+class ReduceOp:
+    SUM, MEAN, MAX, MIN = 1, 2, 3, 4
+
+
+class Template:
+    """cdr_template ids."""
+
+    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE = range(1, 8)
+
+
+@dataclass(frozen=True)
+class OperatorInfo:
+    """What the analysis and template selection need to know about one operator."""
+
+    name: str
+    canonical_name: str
+    operation_type: OpType
+    fusable: bool = True
+    arity: int = 2                      # tensor operands of the elementwise form
+    ew_op: Optional[int] = None         # opcode inside an elementwise program
+    reduce_op: Optional[int] = None     # reduction kind for REDUCTION operators
+    template: Optional[int] = None      # template family for non-elementwise operators
+    preferred_fusion_level: FusionLevel = FusionLevel.LOCAL
+    requires_device_kernel: bool = True
+
+    def is_elementwise(self) -> bool:
+        return self.operation_type is OpType.ELEMENTWISE
+
+    def is_reduction(self) -> bool:
+        return self.operation_type is OpType.REDUCTION
+
+
+def _ew(name, op, arity, canonical=None):
+    return OperatorInfo(name, canonical or name, OpType.ELEMENTWISE, True, arity, ew_op=op,
+                        template=Template.ELEMENTWISE)
+
+
+def _red(name, op, canonical=None):
+    return OperatorInfo(name, canonical or name, OpType.REDUCTION, True, 1, reduce_op=op,
+                        template=Template.ROW_REDUCE, preferred_fusion_level=FusionLevel.GLOBAL)
+
+
+class OperatorRegistry:
+    """Name -> OperatorInfo, with the aliases Dynamo and ``fx.symbolic_trace`` produce."""
+
+    def __init__(self):
+        self._ops: Dict[str, OperatorInfo] = {}
+        self._register_defaults()
+
+    def register(self, info: OperatorInfo, *aliases: str) -> None:
+        self._ops[info.name] = info
+        for a in aliases:
+            self._ops[a] = info
+
+    def _register_defaults(self) -> None:
+        r = self.register
+        r(_ew("add", EwOp.ADD, 2), "iadd", "add_")
+        r(_ew("sub", EwOp.SUB, 2), "isub", "sub_", "subtract")
+        r(_ew("mul", EwOp.MUL, 2), "imul", "mul_", "multiply")
+        r(_ew("div", EwOp.DIV, 2), "truediv", "itruediv", "div_", "true_divide", "divide")
+        r(_ew("relu", EwOp.RELU, 1), "relu_")
+        r(_ew("neg", EwOp.NEG, 1), "negative")
+        r(_ew("abs", EwOp.ABS, 1), "absolute")
+        r(_ew("exp", EwOp.EXP, 1))
+        r(_ew("log", EwOp.LOG, 1))
+        r(_ew("sqrt", EwOp.SQRT, 1))
+        r(_ew("sigmoid", EwOp.SIGMOID, 1))
+        r(_ew("tanh", EwOp.TANH, 1))
+        r(_ew("sin", EwOp.SIN, 1))
+        r(_ew("cos", EwOp.COS, 1))
+        r(_ew("maximum", EwOp.MAX, 2))
+        r(_ew("minimum", EwOp.MIN, 2))
+        r(_ew("addcdiv", EwOp.ADDCDIV, 3))
+        r(_ew("addcmul", EwOp.ADDCMUL, 3))
+        # dtype casts are a rounding-only instruction
+        r(_ew("to_dtype", EwOp.COPY, 1), "float", "bfloat16", "half", "to", "type")
+        r(_red("sum", ReduceOp.SUM))
+        r(_red("reduce_mean", ReduceOp.MEAN), "mean")
+        r(_red("amax", ReduceOp.MAX))
+        r(_red("amin", ReduceOp.MIN))
+        r(OperatorInfo("softmax", "softmax", OpType.SOFTMAX, False, 1, template=Template.SOFTMAX_FWD,
+                       preferred_fusion_level=FusionLevel.GLOBAL), "_softmax")
+        r(OperatorInfo("_softmax_backward_data", "softmax_backward", OpType.SOFTMAX, False, 2,
+                       template=Template.SOFTMAX_BWD, preferred_fusion_level=FusionLevel.GLOBAL))
+        r(OperatorInfo("linear", "linear", OpType.MATRIX, True, 3, template=Template.GEMM_EPILOGUE,
+                       preferred_fusion_level=FusionLevel.GLOBAL))
+        r(OperatorInfo("matmul", "matmul", OpType.MATRIX, False, 2, template=Template.GEMM_EPILOGUE,
+                       preferred_fusion_level=FusionLevel.GLOBAL), "mm", "bmm")
+        r(OperatorInfo("scaled_dot_product_attention", "attention", OpType.ATTENTION, False, 3,
+                       template=Template.ATTENTION, preferred_fusion_level=FusionLevel.GLOBAL), "attention")
+        # metadata-only reshapes of contiguous tensors: no kernel
+        for shape_op in ("view", "reshape", "flatten", "unsqueeze", "squeeze", "contiguous", "detach", "clone_view"):
+            r(OperatorInfo(shape_op, shape_op, OpType.SHAPE, False, 1, requires_device_kernel=False))
+
+    def get_operation(self, name: str) -> Optional[OperatorInfo]:
+        return self._ops.get(name)
+
+    def has_operation(self, name: str) -> bool:
+        return name in self._ops
+
+    def list_operations(self) -> list[str]:
+        return sorted(self._ops)
+
+
+_registry: Optional[OperatorRegistry] = None
+
+
+def get_operator_registry() -> OperatorRegistry:
+    global _registry
+    if _registry is None:
+        _registry = OperatorRegistry()
+    return _registry
+
+
+def get_op_desc(name: str) -> Optional[OperatorInfo]:
+    return get_operator_registry().get_operation(name)
+
+
+def is_elementwise(name: str) -> bool:
+    info = get_op_desc(name)
+    return bool(info and info.is_elementwise())
+
+
+def is_reduction(name: str) -> bool:
+    info = get_op_desc(name)
+    return bool(info and info.is_reduction())

@@ -1,0 +1,138 @@
+"""The object ``torch.compile`` calls at run time (reference: ``conductor/compiler/callable.py:42-94``).
+
+Contract kept from the reference: called with the graph's placeholders positionally, returns a
+**tuple**; a failing kernel raises :class:`ExecutionError`.  Input handling:
+
+* CUDA tensors: the plan runs on their device and stream, asynchronously; outputs are CUDA tensors.
+* CPU tensors (the reference's only mode, ``host_wrapper.py:374-396``): inputs are staged to the
+  GPU through pinned buffers, the plan runs, outputs are copied back; the call is synchronous.
+
+There is no eager fallback: everything in the plan is a hand-written kernel template.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..codegen.kernel_templates import KernelLaunch
+from ..utils.exceptions import DeviceError, ExecutionError
+from ..utils.logging import get_logger
+from .executor import get_executor
+from .jit_compiler import CompiledArtifact
+
+logger = get_logger(__name__)
+
+
+class Callable:
+    def __init__(self, artifact: CompiledArtifact, graph_module: Optional[torch.fx.GraphModule] = None,
+                 device: Optional[torch.device] = None):
+        self.artifact = artifact
+        self.graph_module = graph_module      # kept for introspection only; never executed
+        self.dag = artifact.dag
+        self.launches: list[KernelLaunch] = artifact.launches
+        self.default_device = device
+        self._executor = None
+        self._const_cache: dict[tuple, torch.Tensor] = {}
+        self._pinned: dict[int, torch.Tensor] = {}
+        self.calls = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _exec(self):
+        if self._executor is None:
+            self._executor = get_executor()
+        return self._executor
+
+    def _pick_device(self, tensors) -> torch.device:
+        for t in tensors:
+            if t.device.type == "cuda":
+                return t.device
+        if self.default_device is not None:
+            return self.default_device
+        if not torch.cuda.is_available():
+            raise DeviceError("no CUDA device available; this backend has no CPU execution path")
+        return torch.device("cuda", torch.cuda.current_device())
+
+    def _constant_on(self, buf, device) -> torch.Tensor:
+        key = (id(buf), device)
+        t = self._const_cache.get(key)
+        src = buf.constant_value
+        if t is None or t._version != getattr(src, "_version", 0) and False:
+            t = src.detach().to(device).contiguous()
+            self._const_cache[key] = t
+        return t
+
+    def _stage_in(self, idx: int, t: torch.Tensor, device) -> torch.Tensor:
+        """Host -> device through a reusable pinned buffer (pageable tensors) or directly
+        (already pinned)."""
+        if t.is_pinned():
+            return t.to(device, non_blocking=True)
+        t = t.contiguous()
+        pin = self._pinned.get(idx)
+        if pin is None or pin.shape != t.shape or pin.dtype != t.dtype:
+            pin = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            self._pinned[idx] = pin
+        pin.copy_(t)
+        return pin.to(device, non_blocking=True)
+
+    # ------------------------------------------------------------------ call
+    def __call__(self, *args):
+        tensors = [a for a in args if isinstance(a, torch.Tensor)]
+        dag = self.dag
+        if len(tensors) != len(dag.inputs):
+            raise ExecutionError(f"compiled graph takes {len(dag.inputs)} tensors, got {len(tensors)}",
+                                 kernel_name=self.artifact.entry_point)
+        device = self._pick_device(tensors)
+        host_mode = any(t.device.type == "cpu" for t in tensors)
+        env: dict = {}
+        with torch.cuda.device(device):
+            for i, (buf, t) in enumerate(zip(dag.inputs, tensors)):
+                if buf.shape is not None and tuple(t.shape) != buf.shape:
+                    raise ExecutionError(
+                        f"input {i} has shape {tuple(t.shape)}, compiled for {buf.shape}",
+                        kernel_name=self.artifact.entry_point)
+                env[buf] = self._stage_in(i, t, device) if t.device.type == "cpu" else t
+            outputs = self._run_plan(env, device)
+            if host_mode:
+                outputs = [o.cpu() if isinstance(o, torch.Tensor) else o for o in outputs]
+        self.calls += 1
+        return tuple(outputs)
+
+    def _run_plan(self, env: dict, device) -> list:
+        ex = self._exec()
+        for launch in self.launches:
+            ins = []
+            for b in launch.inputs:
+                t = env.get(b)
+                if t is None:
+                    if b.constant_value is None:
+                        raise ExecutionError(f"value {b.name} is not available", kernel_name=launch.name)
+                    t = env[b] = self._constant_on(b, device)
+                ins.append(t)
+            if launch.template == 0:                       # alias: reshape, no kernel
+                env[launch.outputs[0]] = ins[0].reshape(launch.out_shapes[0])
+                continue
+            outs = ex.execute(launch, ins)
+            for b, t in zip(launch.outputs, outs):
+                env[b] = t
+        result = []
+        for item in self.dag.output_spec:
+            if hasattr(item, "name") and item in env:
+                result.append(env[item])
+            elif hasattr(item, "constant_value") and item.constant_value is not None:
+                result.append(self._constant_on(item, device))
+            elif hasattr(item, "producer"):
+                raise ExecutionError(f"output {item.name} was not produced", kernel_name=self.artifact.entry_point)
+            else:
+                result.append(item)
+        return result
+
+    # reference API (callable.py:96-152)
+    def get_artifact(self) -> CompiledArtifact:
+        return self.artifact
+
+    def plan_text(self) -> str:
+        return self.artifact.metadata.get("plan", "")
+
+    def __repr__(self) -> str:
+        return f"Callable({self.artifact.entry_point}, kernels={sum(1 for l in self.launches if l.template)})"

@@ -1,0 +1,138 @@
+"""Marshal tensors across the C ABI and launch kernel templates
+(reference: ``conductor/compiler/executor.py:47-62,577-628`` ``GCUKernelExecutor`` and
+``conductor/compiler/host_wrapper.py:360-403`` ``execute_kernel_with_library``).
+
+What is kept: tensors are made contiguous, passed as (pointer, shape) descriptors, the call
+returns an ``int`` status and a non-zero status raises :class:`ExecutionError`.  What changed:
+no per-call DSL parsing or dummy-tensor allocation (``executor.py:466-469``), outputs are
+allocated from the plan's recorded shapes instead of ``empty_like(inputs[0])``
+(``executor.py:611``), and launches are asynchronous on the current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from ..codegen.kernel_templates import CdrTensor, KernelLaunch
+from ..utils.exceptions import DeviceError, ExecutionError, UnsupportedOperationError
+from ..utils.type_mapping import to_cdr_dtype
+from .loader import load_library
+
+CDR_ERR_UNSUPPORTED = -2
+CDR_ERR_CUDA = -4
+
+
+def fill_descriptor(desc: CdrTensor, t: torch.Tensor) -> None:
+    desc.data = t.data_ptr()
+    desc.dtype = to_cdr_dtype(t.dtype)
+    desc.rank = t.dim()
+    for i, (s, st) in enumerate(zip(t.shape, t.stride())):
+        desc.shape[i] = s
+        desc.stride[i] = st
+
+
+def make_descriptors(tensors: Sequence[torch.Tensor]):
+    arr = (CdrTensor * max(len(tensors), 1))()
+    for i, t in enumerate(tensors):
+        if t.dim() > 8:
+            raise UnsupportedOperationError("tensor", f"rank {t.dim()} > 8")
+        fill_descriptor(arr[i], t)
+    return arr
+
+
+def raise_for_status(lib, status: int, name: str) -> None:
+    if status == 0:
+        return
+    msg = lib.cdr_last_error().decode(errors="replace")
+    what = lib.cdr_status_string(status).decode()
+    text = f"kernel '{name}' failed: {what}" + (f" ({msg})" if msg else "")
+    if status == CDR_ERR_UNSUPPORTED:
+        raise UnsupportedOperationError(name, msg or what)
+    if status == CDR_ERR_CUDA:
+        raise DeviceError(text)
+    raise ExecutionError(text, kernel_name=name, status=status)
+
+
+class GCUKernelExecutor:
+    """Launches one :class:`KernelLaunch` on device tensors.
+
+    The class name is the reference's (``executor.py:33``); the device it drives is a B200.
+    """
+
+    def __init__(self):
+        self.lib = load_library()
+        self._workspaces: dict[tuple, torch.Tensor] = {}
+
+    def workspace_for(self, launch: KernelLaunch, ins, outs, in_desc, out_desc, params_ptr, params_size):
+        need = ctypes.c_size_t(0)
+        rc = self.lib.cdr_workspace_bytes(launch.template, in_desc, len(ins), out_desc, len(outs), params_ptr,
+                                          params_size, ctypes.byref(need))
+        raise_for_status(self.lib, rc, launch.name)
+        if need.value == 0:
+            return None
+        key = (ins[0].device, id(launch))
+        ws = self._workspaces.get(key)
+        if ws is None or ws.numel() < need.value:
+            ws = torch.zeros(need.value, dtype=torch.uint8, device=ins[0].device)
+            self._workspaces[key] = ws
+        return ws
+
+    def execute(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor],
+                outputs: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
+        """Run `launch`; allocates the outputs when none are passed.  Asynchronous."""
+        if not inputs:
+            raise ExecutionError("kernel launch without inputs", kernel_name=launch.name)
+        device = inputs[0].device
+        if device.type != "cuda":
+            raise DeviceError(f"kernel templates run on CUDA tensors, got {device}")
+        ins = [t if t.is_contiguous() else t.contiguous() for t in inputs]
+        if outputs is None:
+            outputs = [torch.empty(shape, dtype=dt, device=device)
+                       for shape, dt in zip(launch.out_shapes, launch.out_dtypes)]
+        in_desc, out_desc = make_descriptors(ins), make_descriptors(outputs)
+        if launch.params is not None:
+            params_ptr = ctypes.cast(ctypes.byref(launch.params), ctypes.c_void_p)
+            params_size = ctypes.sizeof(launch.params)
+        else:
+            params_ptr, params_size = None, 0
+        ws = None
+        if launch.needs_workspace:
+            ws = self.workspace_for(launch, ins, outputs, in_desc, out_desc, params_ptr, params_size)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        with torch.cuda.device(device):
+            rc = self.lib.cdr_launch(launch.template, in_desc, len(ins), out_desc, len(outputs), params_ptr,
+                                     params_size, ws.data_ptr() if ws is not None else None,
+                                     ws.numel() if ws is not None else 0, stream)
+        raise_for_status(self.lib, rc, launch.name)
+        return list(outputs)
+
+    def execute_host(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor], device: int = 0) -> list[torch.Tensor]:
+        """Reference calling convention: CPU tensors in, CPU tensors out, synchronous
+        (``cdr_execute_host``; the reference's ``execute_kernel`` does the copies itself,
+        ``host_wrapper.py:169-182``)."""
+        ins = [t.contiguous() for t in inputs]
+        if any(t.device.type != "cpu" for t in ins):
+            raise DeviceError("execute_host takes CPU tensors")
+        outs = [torch.empty(shape, dtype=dt) for shape, dt in zip(launch.out_shapes, launch.out_dtypes)]
+        in_desc, out_desc = make_descriptors(ins), make_descriptors(outs)
+        if launch.params is not None:
+            params_ptr = ctypes.cast(ctypes.byref(launch.params), ctypes.c_void_p)
+            params_size = ctypes.sizeof(launch.params)
+        else:
+            params_ptr, params_size = None, 0
+        rc = self.lib.cdr_execute_host(launch.template, in_desc, len(ins), out_desc, len(outs), params_ptr,
+                                       params_size, device)
+        raise_for_status(self.lib, rc, launch.name)
+        return outs
+
+
+_executor: Optional[GCUKernelExecutor] = None
+
+
+def get_executor() -> GCUKernelExecutor:
+    global _executor
+    if _executor is None:
+        _executor = GCUKernelExecutor()
+    return _executor

@@ -1,0 +1,128 @@
+"""Compilation pipeline: FX graph -> DAG -> clusters -> kernel plan.
+
+Counterpart of ``ChoreoJITCompiler`` (reference: ``conductor/compiler/jit_compiler.py:35-233``).
+The reference's stages 5-6 (print Choreo DSL, run ``choreo -c -fpic`` and ``gcc -shared``,
+``jit_compiler.py:150-207,235-382``) are replaced by template selection against the prebuilt
+kernel library, so "compiling" a graph takes microseconds and produces a :class:`CompiledArtifact`
+whose payload is an ordered list of kernel launches.
+"""
+from __future__ import annotations
+
+import hashlib
+import time
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from ..codegen.kernel_templates import KernelLaunch, KernelTemplateSelector
+from ..optimization.fusion import FusionCluster, LocalPriorityFusionEngine, schedule_clusters
+from ..optimization.graph_analyzer import ComputationDAG, GraphAnalyzer
+from ..utils.config import get_config
+from ..utils.exceptions import CompilationError, ConductorError
+from ..utils.logging import get_logger
+from .loader import library_path
+
+logger = get_logger(__name__)
+
+
+@dataclass
+class CompiledArtifact:
+    """Result of compiling one graph (reference: ``conductor/compiler/loader.py:20-60``)."""
+
+    path: str                         # the kernel library the plan runs against
+    artifact_type: str                # always "kernel_plan"
+    entry_point: str                  # plan name, "kernel_<hash8>"
+    metadata: dict[str, Any] = field(default_factory=dict)
+    launches: list[KernelLaunch] = field(default_factory=list)
+    dag: Optional[ComputationDAG] = None
+    clusters: list[FusionCluster] = field(default_factory=list)
+
+    def is_valid(self) -> bool:
+        return bool(self.launches) or bool(self.dag and not self.dag.nodes)
+
+
+class ChoreoJITCompiler:
+    """Pipeline driver.  The class keeps the reference's name because ``GCUBackend.jit_compiler``
+    is part of the plugin surface; nothing Choreo-related remains inside."""
+
+    def __init__(self):
+        self.config = get_config()
+        self.graph_analyzer = GraphAnalyzer()
+        self.fusion_engine = LocalPriorityFusionEngine()
+        self.template_selector = KernelTemplateSelector()
+        self._cache: dict[str, CompiledArtifact] = {}
+        self.stats = {"compiled": 0, "cache_hits": 0, "seconds": 0.0}
+
+    # ------------------------------------------------------------------ hashing
+    def _generate_graph_hash(self, graph_module: torch.fx.GraphModule, example_inputs=None) -> str:
+        """16 hex digits over op/target/name of every node plus shape, dtype, stride and device
+        kind of every example input (the reference hashes names and shapes only,
+        ``jit_compiler.py:443-470``, so a dtype change would hit a stale entry)."""
+        h = hashlib.sha256()
+        for node in graph_module.graph.nodes:
+            h.update(f"{node.op}:{node.target}:{node.name}:{node.args}:{node.kwargs};".encode())
+        for t in example_inputs or []:
+            if isinstance(t, torch.Tensor):
+                h.update(f"{tuple(t.shape)}:{t.dtype}:{t.stride()}:{t.device.type};".encode())
+            else:
+                h.update(f"{t!r};".encode())
+        return h.hexdigest()[:16]
+
+    # ------------------------------------------------------------------ pipeline
+    def compile_graph(self, graph_module: torch.fx.GraphModule, example_inputs=None) -> CompiledArtifact:
+        t0 = time.perf_counter()
+        cfg = self.config
+        graph_hash = self._generate_graph_hash(graph_module, example_inputs)
+        if cfg.cache.enabled and graph_hash in self._cache:
+            self.stats["cache_hits"] += 1
+            return self._cache[graph_hash]
+        try:
+            tensors = list(example_inputs) if example_inputs is not None else None
+            dag = self.graph_analyzer.parse_fx_graph(
+                graph_module, tensors, enable_shape_inference=cfg.compilation.enable_shape_inference)
+            if cfg.compilation.enable_graph_validation and not dag.validate_graph_correctness():
+                raise CompilationError("graph validation failed")
+            clusters = self.fusion_engine.identify_fusion_opportunities(
+                dag, enable_fusion=cfg.compilation.enable_fusion)
+            for c in clusters:
+                if not c.validate_fusion_safety():
+                    raise CompilationError(f"fusion cluster {c.signature()} failed its safety check")
+                for n in c.nodes:
+                    n.fusion_group = c
+            ordered = schedule_clusters(clusters)
+            launches = [self.template_selector.select(c) for c in ordered]
+            name = f"kernel_{graph_hash[:8]}"
+            plan_text = self.template_selector.generate_plan_text(launches, name)
+        except ConductorError:
+            raise
+        except Exception as exc:
+            raise CompilationError(f"compilation failed: {exc}") from exc
+        artifact = CompiledArtifact(
+            path=str(library_path()), artifact_type="kernel_plan", entry_point=name,
+            metadata={"graph_hash": graph_hash, "plan": plan_text, "dsl_content": plan_text,
+                      "n_clusters": len(clusters), "n_nodes": len(dag.nodes)},
+            launches=launches, dag=dag, clusters=ordered)
+        if cfg.cache.enabled:
+            self._cache[graph_hash] = artifact
+        self.stats["compiled"] += 1
+        self.stats["seconds"] += time.perf_counter() - t0
+        logger.info("compiled %s: %d nodes -> %d kernels", name, len(dag.nodes),
+                    sum(1 for l in launches if l.template))
+        if cfg.debug.enabled:
+            logger.debug("\n%s\n%s", self.graph_analyzer.describe(dag), plan_text)
+            if cfg.debug.dump_dir:
+                self._dump(cfg.debug.dump_dir, name, graph_module, dag, plan_text)
+        return artifact
+
+    def _dump(self, dump_dir: str, name: str, gm, dag, plan_text: str) -> None:
+        """Opt-in artifact dump (reference: ``conductor/utils/artifacts.py:18-237`` always writes
+        ``debug_dir`` next to the package; here nothing is written unless a directory is set)."""
+        import os
+
+        os.makedirs(dump_dir, exist_ok=True)
+        with open(os.path.join(dump_dir, f"{name}.plan.txt"), "w") as f:
+            f.write(str(gm.graph) + "\n\n" + self.graph_analyzer.describe(dag) + "\n\n" + plan_text + "\n")
+
+    def clear_cache(self) -> None:
+        self._cache.clear()

@@ -1,0 +1,513 @@
+// K2 -- elementwise chain + reduction epilogue.
+//
+// The reference only sketches reductions as comment templates
+// (conductor/codegen/operator_registry.py:399-458) and clusters "elementwise
+// producers feeding a reduction" in conductor/optimization/fusion.py:714-728; the
+// executed arithmetic is eager `mean(relu(x*w+b), dim=-1, dtype=float32)`
+// (examples/reduce_mean_fusion_example.py:52-102).
+//
+// HBM-bound: the full-size inputs are read once (128-bit streaming loads), the
+// row-broadcast operands (w, b) are loaded once per CTA and kept in registers for
+// every row the CTA handles, the chain's intermediates never leave registers, and
+// only one value per row is written.  Row sums use warp shuffles plus one
+// shared-memory hop between the warps of a CTA.
+//
+// bf16 chains are evaluated with packed bf16x2 mul/add/max (each correctly rounded,
+// never fused), which is bit-identical to eager's "fp32 op, round to bf16" and keeps
+// the instruction count low enough to stay memory-bound.
+#include "cdr_common.cuh"
+
+namespace cdr {
+
+int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out);
+int64_t expected_input_numel(int mode, int64_t n, int64_t cols);
+
+namespace {
+
+// ---------------------------------------------------------------- packed chains
+// A "word" is 32 bits of a 16-byte vector: one fp32 or two bf16.
+// apply(): adds the chain value(s) of the word to the accumulator.
+struct WordIdentityF32 {
+  using elem = float;
+  static constexpr int NROW = 0;
+  __device__ __forceinline__ static void apply(uint32_t x, const uint32_t*, float& acc) {
+    acc += __uint_as_float(x);
+  }
+};
+struct WordMulAddReluF32 {
+  using elem = float;
+  static constexpr int NROW = 2;
+  __device__ __forceinline__ static void apply(uint32_t x, const uint32_t* row, float& acc) {
+    float v = __fadd_rn(__fmul_rn(__uint_as_float(x), __uint_as_float(row[0])), __uint_as_float(row[1]));
+    v = v > 0.0f ? v : (v != v ? v : 0.0f);
+    acc += v;
+  }
+};
+__device__ __forceinline__ void acc_bf16x2(uint32_t w, float& acc) {
+  acc += __uint_as_float(w << 16);
+  acc += __uint_as_float(w & 0xffff0000u);
+}
+struct WordIdentityBF16 {
+  using elem = __nv_bfloat16;
+  static constexpr int NROW = 0;
+  __device__ __forceinline__ static void apply(uint32_t x, const uint32_t*, float& acc) { acc_bf16x2(x, acc); }
+};
+struct WordMulAddReluBF16 {
+  using elem = __nv_bfloat16;
+  static constexpr int NROW = 2;
+  __device__ __forceinline__ static void apply(uint32_t x, const uint32_t* row, float& acc) {
+    const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&x);
+    const __nv_bfloat162 wv = *reinterpret_cast<const __nv_bfloat162*>(&row[0]);
+    const __nv_bfloat162 bv = *reinterpret_cast<const __nv_bfloat162*>(&row[1]);
+    const __nv_bfloat162 zero = __float2bfloat162_rn(0.0f);
+    __nv_bfloat162 v = __hmax2_nan(__hadd2_rn(__hmul2_rn(xv, wv), bv), zero);
+    acc_bf16x2(*reinterpret_cast<uint32_t*>(&v), acc);
+  }
+};
+
+struct RowArgs {
+  const void* full;      // the one full-size input, [rows, cols]
+  const void* row[2];    // row-broadcast inputs, [cols]
+  void* out;             // [rows]
+  int32_t out_dtype;
+  int32_t mean;          // 1: divide the sum by cols
+  int64_t rows;
+  int64_t cols;
+};
+
+__device__ __forceinline__ void store_result(void* out, int dt, int64_t i, float v) {
+  if (dt == CDR_F32) static_cast<float*>(out)[i] = v;
+  else if (dt == CDR_BF16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(out)[i] = __float2half_rn(v);
+}
+
+// NT threads per CTA; a thread owns vectors {t, t+NT, ...} (VPT of them) of every row;
+// the CTA walks row blocks of RB rows, grid-stride.
+template <class Chain, int NT, int VPT, int RB>
+__global__ void __launch_bounds__(NT) row_reduce_named_kernel(const __grid_constant__ RowArgs a) {
+  using T = typename Chain::elem;
+  constexpr int V = 16 / sizeof(T);
+  constexpr int NW = NT / 32;
+  constexpr int NROW = Chain::NROW;
+  __shared__ float part[2][RB][NW];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t vec_per_row = a.cols / V;
+
+  // row-broadcast operands: loaded once, register resident for the whole kernel
+  uint4 rowv[NROW > 0 ? NROW : 1][VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int64_t v = tid + static_cast<int64_t>(j) * NT;
+#pragma unroll
+    for (int r = 0; r < NROW; ++r)
+      rowv[r][j] = (v < vec_per_row) ? ld_cached16(static_cast<const T*>(a.row[r]) + v * V) : make_uint4(0, 0, 0, 0);
+  }
+
+  const int64_t n_blocks = (a.rows + RB - 1) / RB;
+  int parity = 0;
+  for (int64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x, parity ^= 1) {
+    const int64_t row0 = blk * RB;
+    uint4 x[RB][VPT];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const T* base = static_cast<const T*>(a.full) + (row0 + r) * a.cols;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int64_t v = tid + static_cast<int64_t>(j) * NT;
+        x[r][j] = (row0 + r < a.rows && v < vec_per_row) ? ld_stream16(base + v * V) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    float acc[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int64_t v = tid + static_cast<int64_t>(j) * NT;
+        if (v < vec_per_row) {  // a padded vector would add chain(0) != 0
+          uint32_t rw[4][NROW > 0 ? NROW : 1];
+#pragma unroll
+          for (int q = 0; q < NROW; ++q) {
+            rw[0][q] = rowv[q][j].x; rw[1][q] = rowv[q][j].y; rw[2][q] = rowv[q][j].z; rw[3][q] = rowv[q][j].w;
+          }
+          Chain::apply(x[r][j].x, rw[0], a0);
+          Chain::apply(x[r][j].y, rw[1], a1);
+          Chain::apply(x[r][j].z, rw[2], a0);
+          Chain::apply(x[r][j].w, rw[3], a1);
+        }
+      }
+      acc[r] = warp_sum(a0 + a1);
+    }
+    if (NW == 1) {
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+          if (row0 + r < a.rows) {
+            const float s = a.mean ? __fdiv_rn(acc[r], static_cast<float>(a.cols)) : acc[r];
+            store_result(a.out, a.out_dtype, row0 + r, s);
+          }
+      }
+    } else {
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r) part[parity][r][warp] = acc[r];
+      }
+      __syncthreads();
+      if (tid < RB && row0 + tid < a.rows) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) s += part[parity][tid][w];
+        if (a.mean) s = __fdiv_rn(s, static_cast<float>(a.cols));
+        store_result(a.out, a.out_dtype, row0 + tid, s);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- generic path
+constexpr int kMaxRegs = CDR_EW_MAX_INPUTS + CDR_EW_MAX_INSTR;
+
+struct GenArgs {
+  const void* in[CDR_EW_MAX_INPUTS];
+  int32_t in_dtype[CDR_EW_MAX_INPUTS];
+  void* out;
+  int32_t out_dtype;
+  int32_t reduce_op;
+  int64_t rows;
+  int64_t cols;
+  cdr_ew_params prog;
+};
+
+__device__ __forceinline__ float gen_load(const void* base, int dt, int64_t i) {
+  switch (dt) {
+    case CDR_F32: return static_cast<const float*>(base)[i];
+    case CDR_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+    case CDR_F16: return __half2float(static_cast<const __half*>(base)[i]);
+    default: return 0.0f;
+  }
+}
+
+__device__ __forceinline__ float gen_op(int op, float a, float b, float c, float imm) {
+  switch (op) {
+    case CDR_OP_ADD: return __fadd_rn(a, b);
+    case CDR_OP_SUB: return __fsub_rn(a, b);
+    case CDR_OP_MUL: return __fmul_rn(a, b);
+    case CDR_OP_DIV: return __fdiv_rn(a, b);
+    case CDR_OP_RELU: return a > 0.0f ? a : (a != a ? a : 0.0f);
+    case CDR_OP_NEG: return -a;
+    case CDR_OP_ABS: return fabsf(a);
+    case CDR_OP_EXP: return expf(a);
+    case CDR_OP_LOG: return logf(a);
+    case CDR_OP_SQRT: return __fsqrt_rn(a);
+    case CDR_OP_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-a)));
+    case CDR_OP_TANH: return tanhf(a);
+    case CDR_OP_SIN: return sinf(a);
+    case CDR_OP_COS: return cosf(a);
+    case CDR_OP_MAX: return (a != a || b != b) ? (a + b) : fmaxf(a, b);
+    case CDR_OP_MIN: return (a != a || b != b) ? (a + b) : fminf(a, b);
+    case CDR_OP_ADDCDIV: return __fadd_rn(a, __fdiv_rn(__fmul_rn(imm, b), c));
+    case CDR_OP_ADDCMUL: return __fadd_rn(a, __fmul_rn(__fmul_rn(imm, b), c));
+    case CDR_OP_CONST: return imm;
+    case CDR_OP_COPY: return a;
+    case CDR_OP_ADD_IMM: return __fadd_rn(a, imm);
+    case CDR_OP_MUL_IMM: return __fmul_rn(a, imm);
+    case CDR_OP_RSUB_IMM: return __fsub_rn(imm, a);
+    case CDR_OP_RDIV_IMM: return __fdiv_rn(imm, a);
+    default: return 0.0f;
+  }
+}
+
+// Chain value of flat element `i` of the [rows, cols] view.
+__device__ __forceinline__ float gen_eval(const GenArgs& a, int64_t i, int64_t row, int64_t col) {
+  float reg[kMaxRegs];
+  const cdr_ew_params& p = a.prog;
+  for (int k = 0; k < p.n_inputs; ++k) {
+    const int m = p.input_mode[k];
+    const int64_t idx = m == CDR_IN_FULL ? i : m == CDR_IN_ROW ? col : m == CDR_IN_COL ? row : 0;
+    reg[k] = gen_load(a.in[k], a.in_dtype[k], idx);
+  }
+  for (int k = 0; k < p.n_instr; ++k) {
+    const cdr_ew_instr ins = p.instr[k];
+    reg[p.n_inputs + k] = round_to_dtype(gen_op(ins.op, reg[ins.a], reg[ins.b], reg[ins.c], ins.imm), ins.round_to);
+  }
+  return reg[p.out_reg[0]];
+}
+
+__device__ __forceinline__ float red_identity(int op) {
+  return op == CDR_RED_MAX ? -INFINITY : op == CDR_RED_MIN ? INFINITY : 0.0f;
+}
+__device__ __forceinline__ float red_combine(int op, float a, float b) {
+  if (op == CDR_RED_MAX) return (a != a || b != b) ? (a + b) : fmaxf(a, b);
+  if (op == CDR_RED_MIN) return (a != a || b != b) ? (a + b) : fminf(a, b);
+  return a + b;
+}
+__device__ __forceinline__ float warp_combine(int op, float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = red_combine(op, v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int NT>
+__device__ __forceinline__ float cta_combine(int op, float v, float* smem) {
+  v = warp_combine(op, v);
+  if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red_identity(op);
+  if (threadIdx.x < 32) {
+    if (threadIdx.x < NT / 32) r = smem[threadIdx.x];
+    r = warp_combine(op, r);
+  }
+  __syncthreads();
+  return r;  // valid in warp 0
+}
+
+// One CTA per row (grid-stride over rows), scalar interpreter.
+template <int NT>
+__global__ void __launch_bounds__(NT) row_reduce_generic_kernel(const __grid_constant__ GenArgs a) {
+  __shared__ float smem[NT / 32];
+  for (int64_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    float acc = red_identity(a.reduce_op);
+    for (int64_t c = threadIdx.x; c < a.cols; c += NT)
+      acc = red_combine(a.reduce_op, acc, gen_eval(a, row * a.cols + c, row, c));
+    const float r = cta_combine<NT>(a.reduce_op, acc, smem);
+    if (threadIdx.x == 0) {
+      const float v = a.reduce_op == CDR_RED_MEAN ? __fdiv_rn(r, static_cast<float>(a.cols)) : r;
+      store_result(a.out, a.out_dtype, row, v);
+    }
+  }
+}
+
+// Full reduction, stage 1+2 in one launch: every CTA writes one partial into scratch,
+// the CTA that finishes last (ticket counter in scratch) folds the partials.
+struct FullArgs {
+  GenArgs g;          // rows*cols = all elements
+  float* partials;    // scratch: one float per CTA
+  unsigned int* ticket;  // scratch: zero before the launch
+};
+
+template <int NT>
+__global__ void __launch_bounds__(NT) full_reduce_kernel(const __grid_constant__ FullArgs a) {
+  __shared__ float smem[NT / 32];
+  __shared__ bool is_last;
+  const int64_t n = a.g.rows * a.g.cols;
+  const int op = a.g.reduce_op;
+  float acc = red_identity(op);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * NT + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * NT)
+    acc = red_combine(op, acc, gen_eval(a.g, i, i / a.g.cols, i % a.g.cols));
+  float r = cta_combine<NT>(op, acc, smem);
+  if (threadIdx.x == 0) {
+    a.partials[blockIdx.x] = r;
+    __threadfence();
+    const unsigned int t = atomicAdd(a.ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  acc = red_identity(op);
+  for (int i = threadIdx.x; i < static_cast<int>(gridDim.x); i += NT)
+    acc = red_combine(op, acc, __ldcg(a.partials + i));
+  r = cta_combine<NT>(op, acc, smem);
+  if (threadIdx.x == 0) {
+    const float v = op == CDR_RED_MEAN ? __fdiv_rn(r, static_cast<float>(n)) : r;
+    store_result(a.g.out, a.g.out_dtype, 0, v);
+    *a.ticket = 0;  // leave the counter ready for the next launch
+  }
+}
+
+// ---------------------------------------------------------------- host side
+enum RowChain { kRNone = 0, kRIdentity, kRMulAddRelu };
+
+RowChain match_row_chain(const cdr_ew_params& p, int dt, int* full_idx, int* row_idx) {
+  if (p.n_inputs == 1 && p.n_instr == 0 && p.out_reg[0] == 0 && p.input_mode[0] == CDR_IN_FULL) {
+    *full_idx = 0;
+    return kRIdentity;
+  }
+  if (p.n_inputs == 3 && p.n_instr == 3 && p.out_reg[0] == 5) {
+    for (int k = 0; k < 3; ++k)
+      if (p.instr[k].round_to != dt) return kRNone;
+    const cdr_ew_instr &m = p.instr[0], &s = p.instr[1], &r = p.instr[2];
+    if (m.op != CDR_OP_MUL || s.op != CDR_OP_ADD || r.op != CDR_OP_RELU || r.a != 4) return kRNone;
+    // mul(x, w) with x full and w row; add(mul, b) with b row (either operand order)
+    int x = -1, w = -1, b = -1;
+    if (p.input_mode[m.a] == CDR_IN_FULL && p.input_mode[m.b] == CDR_IN_ROW) { x = m.a; w = m.b; }
+    else if (p.input_mode[m.b] == CDR_IN_FULL && p.input_mode[m.a] == CDR_IN_ROW) { x = m.b; w = m.a; }
+    else return kRNone;
+    if (m.a >= 3 || m.b >= 3) return kRNone;
+    if (s.a == 3 && s.b < 3) b = s.b; else if (s.b == 3 && s.a < 3) b = s.a; else return kRNone;
+    if (b == x || b == w || p.input_mode[b] != CDR_IN_ROW) return kRNone;
+    *full_idx = x; row_idx[0] = w; row_idx[1] = b;
+    return kRMulAddRelu;
+  }
+  return kRNone;
+}
+
+template <class Chain, int NT, int VPT>
+int launch_named_cfg(const RowArgs& a, cudaStream_t s) {
+  constexpr int RB = (VPT >= 8) ? 1 : (8 / VPT);  // 8 16-byte loads in flight per thread
+  auto kern = row_reduce_named_kernel<Chain, NT, VPT, RB>;
+  int per_sm = 0;
+  CDR_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, 0));
+  if (per_sm < 1) per_sm = 1;
+  const int64_t n_blocks = (a.rows + RB - 1) / RB;
+  int64_t grid = static_cast<int64_t>(sm_count()) * per_sm;
+  if (grid > n_blocks) grid = n_blocks;
+  kern<<<static_cast<unsigned>(grid), NT, 0, s>>>(a);
+  CDR_CUDA_TRY(cudaGetLastError());
+  return CDR_OK;
+}
+
+template <class Chain>
+int launch_named_row(const RowArgs& a, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(typename Chain::elem);
+  const int64_t vec = a.cols / V;
+  if (vec <= 32) return launch_named_cfg<Chain, 32, 1>(a, s);
+  if (vec <= 64) return launch_named_cfg<Chain, 64, 1>(a, s);
+  if (vec <= 128) return launch_named_cfg<Chain, 128, 1>(a, s);
+  if (vec <= 256) return launch_named_cfg<Chain, 256, 1>(a, s);
+  if (vec <= 512) return launch_named_cfg<Chain, 256, 2>(a, s);
+  if (vec <= 1024) return launch_named_cfg<Chain, 256, 4>(a, s);
+  if (vec <= 2048) return launch_named_cfg<Chain, 256, 8>(a, s);
+  return CDR_ERR_UNSUPPORTED;
+}
+
+int check_reduce_inputs(const cdr_tensor* ins, int n_in, const cdr_reduce_params* p, int64_t rows, int64_t cols,
+                        const char* who) {
+  for (int i = 0; i < n_in; ++i) {
+    if (!ins[i].data) { set_error("%s: input %d has a null pointer", who, i); return CDR_ERR_BAD_ARG; }
+    if (!is_contiguous(ins[i])) { set_error("%s: input %d is not contiguous", who, i); return CDR_ERR_BAD_ARG; }
+    if (ins[i].dtype != CDR_F32 && ins[i].dtype != CDR_BF16 && ins[i].dtype != CDR_F16) {
+      set_error("%s: input %d has dtype %d; only floating types reduce", who, i, ins[i].dtype);
+      return CDR_ERR_UNSUPPORTED;
+    }
+    const int64_t want = expected_input_numel(p->chain.input_mode[i], rows * cols, cols);
+    if (numel(ins[i]) != want) {
+      set_error("%s: input %d has %lld elements, expected %lld", who, i, (long long)numel(ins[i]), (long long)want);
+      return CDR_ERR_BAD_ARG;
+    }
+  }
+  if (p->reduce_op < CDR_RED_SUM || p->reduce_op > CDR_RED_MIN) {
+    set_error("%s: unknown reduce op %d", who, p->reduce_op);
+    return CDR_ERR_BAD_ARG;
+  }
+  return CDR_OK;
+}
+
+void fill_gen_args(GenArgs& g, const cdr_tensor* ins, int n_in, const cdr_tensor& out, const cdr_reduce_params* p,
+                   int64_t rows, int64_t cols) {
+  for (int i = 0; i < n_in; ++i) { g.in[i] = ins[i].data; g.in_dtype[i] = ins[i].dtype; }
+  g.out = out.data; g.out_dtype = out.dtype; g.reduce_op = p->reduce_op;
+  g.rows = rows; g.cols = cols; g.prog = p->chain;
+}
+
+}  // namespace
+
+int launch_row_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
+                      const cdr_reduce_params* p, cudaStream_t stream) {
+  if (!p) { set_error("row_reduce: params is null"); return CDR_ERR_BAD_ARG; }
+  if (int rc = validate_ew_program(&p->chain, n_in, n_out)) return rc;
+  if (n_out != 1 || n_in < 1) { set_error("row_reduce: needs >=1 input and exactly one output"); return CDR_ERR_BAD_ARG; }
+  // the [rows, cols] view comes from the first full-size input
+  int full = -1;
+  for (int i = 0; i < n_in; ++i)
+    if (p->chain.input_mode[i] == CDR_IN_FULL) { full = i; break; }
+  if (full < 0) { set_error("row_reduce: no full-size input"); return CDR_ERR_BAD_ARG; }
+  const cdr_tensor& x = ins[full];
+  if (x.rank < 1) { set_error("row_reduce: input rank 0"); return CDR_ERR_BAD_ARG; }
+  const int64_t cols = x.shape[x.rank - 1];
+  const int64_t rows = cols ? numel(x) / cols : 0;
+  const cdr_tensor& out = outs[0];
+  if (numel(out) != rows || !is_contiguous(out)) {
+    set_error("row_reduce: output must be contiguous with %lld elements", (long long)rows);
+    return CDR_ERR_BAD_ARG;
+  }
+  if (out.dtype != CDR_F32 && out.dtype != CDR_BF16 && out.dtype != CDR_F16) {
+    set_error("row_reduce: output dtype %d unsupported", out.dtype);
+    return CDR_ERR_UNSUPPORTED;
+  }
+  if (int rc = check_reduce_inputs(ins, n_in, p, rows, cols, "row_reduce")) return rc;
+  if (rows == 0) return CDR_OK;
+  if (!out.data) { set_error("row_reduce: output pointer is null"); return CDR_ERR_BAD_ARG; }
+  if (cols == 0) { set_error("row_reduce: reduction over an empty dimension"); return CDR_ERR_UNSUPPORTED; }
+
+  // named fast path: sum/mean, one dtype, aligned, whole vectors per row
+  const int dt = x.dtype;
+  bool same = true;
+  for (int i = 0; i < n_in; ++i) same &= ins[i].dtype == dt && aligned16(ins[i].data);
+  const int V = 16 / dtype_size(dt);
+  if (same && (dt == CDR_F32 || dt == CDR_BF16) && cols % V == 0 &&
+      (p->reduce_op == CDR_RED_SUM || p->reduce_op == CDR_RED_MEAN)) {
+    int fidx = 0, ridx[2] = {0, 0};
+    const RowChain c = match_row_chain(p->chain, dt, &fidx, ridx);
+    if (c != kRNone) {
+      RowArgs a{};
+      a.full = ins[fidx].data; a.row[0] = ins[ridx[0]].data; a.row[1] = ins[ridx[1]].data;
+      a.out = out.data; a.out_dtype = out.dtype; a.mean = p->reduce_op == CDR_RED_MEAN;
+      a.rows = rows; a.cols = cols;
+      int rc = CDR_ERR_UNSUPPORTED;
+      if (c == kRIdentity && dt == CDR_F32) rc = launch_named_row<WordIdentityF32>(a, stream);
+      else if (c == kRIdentity && dt == CDR_BF16) rc = launch_named_row<WordIdentityBF16>(a, stream);
+      else if (c == kRMulAddRelu && dt == CDR_F32) rc = launch_named_row<WordMulAddReluF32>(a, stream);
+      else if (c == kRMulAddRelu && dt == CDR_BF16) rc = launch_named_row<WordMulAddReluBF16>(a, stream);
+      if (rc != CDR_ERR_UNSUPPORTED) return rc;
+    }
+  }
+
+  GenArgs g{};
+  fill_gen_args(g, ins, n_in, out, p, rows, cols);
+  int64_t grid = rows;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (grid > cap) grid = cap;
+  row_reduce_generic_kernel<256><<<static_cast<unsigned>(grid), 256, 0, stream>>>(g);
+  CDR_CUDA_TRY(cudaGetLastError());
+  return CDR_OK;
+}
+
+// scratch layout of the full reduction: [ticket: 256 B][partials: one float per CTA]
+static int full_reduce_grid() { return sm_count() * 4; }
+
+int full_reduce_workspace(const cdr_tensor*, int, size_t* bytes) {
+  *bytes = 256 + sizeof(float) * static_cast<size_t>(full_reduce_grid());
+  return CDR_OK;
+}
+
+int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
+                       const cdr_reduce_params* p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (!p) { set_error("full_reduce: params is null"); return CDR_ERR_BAD_ARG; }
+  if (int rc = validate_ew_program(&p->chain, n_in, n_out)) return rc;
+  if (n_out != 1 || n_in < 1) { set_error("full_reduce: needs >=1 input and exactly one output"); return CDR_ERR_BAD_ARG; }
+  int full = -1;
+  for (int i = 0; i < n_in; ++i)
+    if (p->chain.input_mode[i] == CDR_IN_FULL) { full = i; break; }
+  if (full < 0) { set_error("full_reduce: no full-size input"); return CDR_ERR_BAD_ARG; }
+  const cdr_tensor& x = ins[full];
+  const int64_t cols = x.rank > 0 ? x.shape[x.rank - 1] : 1;
+  const int64_t n = numel(x);
+  const int64_t rows = cols ? n / cols : 0;
+  if (numel(outs[0]) != 1 || !outs[0].data) { set_error("full_reduce: output must hold one element"); return CDR_ERR_BAD_ARG; }
+  if (outs[0].dtype != CDR_F32 && outs[0].dtype != CDR_BF16 && outs[0].dtype != CDR_F16) {
+    set_error("full_reduce: output dtype %d unsupported", outs[0].dtype);
+    return CDR_ERR_UNSUPPORTED;
+  }
+  if (int rc = check_reduce_inputs(ins, n_in, p, rows, cols, "full_reduce")) return rc;
+  if (n == 0) { set_error("full_reduce: reduction over an empty tensor"); return CDR_ERR_UNSUPPORTED; }
+  size_t need = 0;
+  full_reduce_workspace(ins, n_in, &need);
+  if (!ws || ws_bytes < need) {
+    set_error("full_reduce: workspace of %zu bytes required, got %zu", need, ws ? ws_bytes : (size_t)0);
+    return CDR_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(ws) & 255u) { set_error("full_reduce: workspace must be 256-byte aligned"); return CDR_ERR_MISALIGNED; }
+  FullArgs a{};
+  fill_gen_args(a.g, ins, n_in, outs[0], p, rows, cols);
+  a.ticket = static_cast<unsigned int*>(ws);
+  a.partials = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
+  int64_t grid = (n + 255) / 256;
+  if (grid > full_reduce_grid()) grid = full_reduce_grid();
+  CDR_CUDA_TRY(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned int), stream));
+  full_reduce_kernel<256><<<static_cast<unsigned>(grid), 256, 0, stream>>>(a);
+  CDR_CUDA_TRY(cudaGetLastError());
+  return CDR_OK;
+}
+
+}  // namespace cdr

@@ -1,0 +1,353 @@
+"""GPU parity: the CUDA kernel templates, called through the C ABI, against the golden
+vectors, the C oracle and the reference's executed path (eager on CPU) on identical seeded
+inputs.  Tolerances are the benchmark's: bit-exact for integer work and for the fp32/bf16
++,-,*,/ chains, max-abs/rel <= 1e-5 for fp32 transcendental/reduction results, <= 2e-2 bf16."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import abi_util as abi
+from abi_util import COL, FULL, ROW, SCALAR
+from conftest import assert_close, bf16_bits_to_tensor, load_golden, tensor_to_bf16_bits
+from conductor_b200.codegen.kernel_templates import CdrReduceParams
+from conductor_b200.codegen.operator_registry import EwOp, ReduceOp, Template
+from oracle import reference_path as rp
+from oracle import scalar
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F32_TOL, BF16_TOL = 1e-5, 2e-2
+
+
+def bits_equal(a: torch.Tensor, b: torch.Tensor) -> bool:
+    a, b = a.detach().cpu().contiguous(), b.detach().cpu().contiguous()
+    if a.dtype != b.dtype or a.shape != b.shape:
+        return False
+    return torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+
+
+def cuda(*ts):
+    return [t.to(DEV) for t in ts]
+
+
+# ---------------------------------------------------------------- K1 elementwise
+def test_mul_add_golden_bit_exact(executor):
+    g = load_golden("c1_mul_add")
+    a, b, c = cuda(g["a"], g["b"], g["c"])
+    out = torch.empty_like(a)
+    abi.launch(Template.ELEMENTWISE, [a, b, c], [out], abi.mul_add_program())
+    assert bits_equal(out, g["out"])
+
+
+@pytest.mark.parametrize("shape", [(1,), (3,), (4,), (257,), (1000, 3), (129, 1024), (7, 5, 33)])
+def test_mul_add_ragged_sizes_bit_exact(executor, shape):
+    gen = torch.Generator().manual_seed(11)
+    a, b, c = (torch.randn(shape, generator=gen) for _ in range(3))
+    want = torch.from_numpy(scalar.mul_add_f32(a.numpy(), b.numpy(), c.numpy()))
+    assert torch.equal(want, a * b + c)                      # oracle == eager, bit for bit
+    da, db, dc = cuda(a, b, c)
+    out = torch.empty_like(da)
+    abi.launch(Template.ELEMENTWISE, [da, db, dc], [out], abi.mul_add_program())
+    assert bits_equal(out, want)
+
+
+def test_mul_add_misaligned_pointers(executor):
+    gen = torch.Generator().manual_seed(12)
+    base = [torch.randn(4099, generator=gen).to(DEV) for _ in range(3)]
+    a, b, c = (t[1:4098] for t in base)                      # data_ptr is 4 bytes off 16-byte alignment
+    out_base = torch.zeros(4099, device=DEV)
+    out = out_base[3:4100]
+    abi.launch(Template.ELEMENTWISE, [a, b, c], [out], abi.mul_add_program())
+    assert bits_equal(out, (a.cpu() * b.cpu() + c.cpu()))
+    assert out_base[:3].abs().sum().item() == 0               # nothing written before the view
+
+
+def test_elementwise_empty(executor):
+    a = torch.empty(0, 16, device=DEV)
+    out = torch.empty_like(a)
+    abi.launch(Template.ELEMENTWISE, [a, a, a], [out], abi.mul_add_program())
+
+
+def test_mul_add_bf16_bit_exact(executor):
+    gen = torch.Generator().manual_seed(13)
+    a, b, c = (torch.randn(333, 264, generator=gen).bfloat16() for _ in range(3))
+    want = bf16_bits_to_tensor(scalar.mul_add_bf16(*(tensor_to_bf16_bits(t) for t in (a, b, c))))
+    assert bits_equal(want, a * b + c)
+    da, db, dc = cuda(a, b, c)
+    out = torch.empty_like(da)
+    abi.launch(Template.ELEMENTWISE, [da, db, dc], [out], abi.mul_add_program(torch.bfloat16))
+    assert bits_equal(out, want)
+
+
+def test_addcdiv_and_relu_named_chains(executor):
+    gen = torch.Generator().manual_seed(14)
+    a, b = torch.randn(64, 300, generator=gen), torch.randn(64, 300, generator=gen)
+    c = torch.rand(64, 300, generator=gen) + 0.5
+    da, db, dc = cuda(a, b, c)
+    out = torch.empty_like(da)
+    prog = abi.ew_program(3, [(EwOp.ADDCDIV, 0, 1, 2, 1.0, torch.float32)], [3])
+    abi.launch(Template.ELEMENTWISE, [da, db, dc], [out], prog)
+    assert bits_equal(out, torch.from_numpy(scalar.addcdiv_f32(a.numpy(), b.numpy(), c.numpy(), 1.0)))
+    assert bits_equal(out, torch.addcdiv(a, b, c, value=1.0))
+    x = torch.randn(128, 256, generator=gen)
+    x[0, :4] = torch.tensor([float("nan"), -0.0, float("inf"), -float("inf")])
+    dx = x.to(DEV)
+    out = torch.empty_like(dx)
+    abi.launch(Template.ELEMENTWISE, [dx], [out], abi.ew_program(1, [(EwOp.RELU, 0, 0, 0, 0, torch.float32)], [1]))
+    assert_close(out, torch.relu(x), 0.0, "relu")
+    assert torch.equal(out.cpu()[1:], torch.from_numpy(scalar.relu_f32(x.numpy()))[1:])
+
+
+def test_interpreted_program_with_broadcasts(executor):
+    # (sigmoid(x * w + 1.5) - col) / s : row, column and scalar broadcasts, unary math
+    gen = torch.Generator().manual_seed(15)
+    x = torch.randn(37, 64, generator=gen)
+    w = torch.randn(64, generator=gen)
+    col = torch.randn(37, 1, generator=gen)
+    s = torch.tensor(3.0)
+    want = (torch.sigmoid(x * w + 1.5) - col) / s
+    prog = abi.ew_program(4, [
+        (EwOp.MUL, 0, 1, 0, 0, torch.float32), (EwOp.ADD_IMM, 4, 0, 0, 1.5, torch.float32),
+        (EwOp.SIGMOID, 5, 0, 0, 0, torch.float32), (EwOp.SUB, 6, 2, 0, 0, torch.float32),
+        (EwOp.DIV, 7, 3, 0, 0, torch.float32)], [8], [FULL, ROW, COL, SCALAR])
+    dx, dw, dcol, ds = cuda(x, w, col, s)
+    out = torch.empty_like(dx)
+    abi.launch(Template.ELEMENTWISE, [dx, dw, dcol, ds], [out], prog)
+    assert_close(out, want, F32_TOL, "interpreted chain")
+    # same program, ragged row length -> scalar path
+    x2, w2 = torch.randn(37, 63, generator=gen), torch.randn(63, generator=gen)
+    want2 = (torch.sigmoid(x2 * w2 + 1.5) - col) / s
+    dx2, dw2 = cuda(x2, w2)
+    out2 = torch.empty_like(dx2)
+    abi.launch(Template.ELEMENTWISE, [dx2, dw2, dcol, ds], [out2], prog)
+    assert_close(out2, want2, F32_TOL, "interpreted chain, scalar path")
+
+
+def test_two_outputs(executor):
+    gen = torch.Generator().manual_seed(16)
+    a, b = torch.randn(50, 40, generator=gen), torch.randn(50, 40, generator=gen)
+    prog = abi.ew_program(2, [(EwOp.ADD, 0, 1, 0, 0, torch.float32), (EwOp.MUL, 2, 0, 0, 0, torch.float32)], [2, 3])
+    da, db = cuda(a, b)
+    o1, o2 = torch.empty_like(da), torch.empty_like(da)
+    abi.launch(Template.ELEMENTWISE, [da, db], [o1, o2], prog)
+    assert bits_equal(o1, a + b) and bits_equal(o2, (a + b) * a)
+
+
+def test_integer_chain_bit_exact(executor):
+    rng = np.random.default_rng(2)
+    a = rng.integers(-10, 11, (6, 17, 64), dtype=np.int32)
+    b = rng.integers(-2**31, 2**31 - 1, (6, 17, 64), dtype=np.int32)        # wraps
+    da, db = torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV)
+    out = torch.empty_like(da)
+    abi.launch(Template.ELEMENTWISE, [da, db], [out], abi.ew_program(2, [(EwOp.ADD, 0, 1, 0, 0, torch.int32)], [2]))
+    assert np.array_equal(out.cpu().numpy(), scalar.add_i32(a, b))
+    assert np.array_equal(out.cpu().numpy(), (torch.from_numpy(a) + torch.from_numpy(b)).numpy())
+    a64 = torch.from_numpy(rng.integers(-2**40, 2**40, (1000,), dtype=np.int64))
+    d64 = a64.to(DEV)
+    out64 = torch.empty_like(d64)
+    prog = abi.ew_program(1, [(EwOp.MUL, 0, 0, 0, 0, torch.int64), (EwOp.ADD_IMM, 1, 0, 0, 7, torch.int64)], [2])
+    abi.launch(Template.ELEMENTWISE, [d64], [out64], prog)
+    assert torch.equal(out64.cpu(), a64 * a64 + 7)
+
+
+def test_bad_arguments_return_status_not_crash(executor):
+    a = torch.randn(8, 8, device=DEV)
+    out = torch.empty(8, 9, device=DEV)
+    assert abi.launch(Template.ELEMENTWISE, [a, a, a], [out], abi.mul_add_program(), check=False) == -1
+    assert abi.launch(99, [a], [a], abi.mul_add_program(), check=False) == -2
+    bad = abi.ew_program(3, [(EwOp.MUL, 0, 7, 0, 0, torch.float32)], [3])     # reads an undefined register
+    assert abi.launch(Template.ELEMENTWISE, [a, a, a], [torch.empty_like(a)], bad, check=False) == -1
+    assert b"register" in executor.lib.cdr_last_error()
+
+
+# ---------------------------------------------------------------- K2 row reduce
+def reduce_params(chain, op):
+    p = CdrReduceParams()
+    p.chain = chain
+    p.reduce_op = op
+    return p
+
+
+def mar_chain(dtype):
+    return abi.ew_program(3, [(EwOp.MUL, 0, 1, 0, 0, dtype), (EwOp.ADD, 3, 2, 0, 0, dtype),
+                              (EwOp.RELU, 4, 0, 0, 0, dtype)], [5], [FULL, ROW, ROW])
+
+
+def test_reduce_mean_golden(executor):
+    g = load_golden("c2_reduce_mean")
+    x, w, b = cuda(g["x"], g["w"], g["b"])
+    out = torch.empty(x.shape[0], device=DEV)
+    abi.launch(Template.ROW_REDUCE, [x, w, b], [out], reduce_params(mar_chain(torch.bfloat16), ReduceOp.MEAN))
+    assert_close(out, g["out"], F32_TOL, "reduce_mean golden")
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 256), (33, 512), (64, 4096), (7, 2048), (19, 8200), (3, 16384),
+                                       (9, 100), (4, 20000)])
+def test_reduce_mean_shapes(executor, rows, cols):
+    x, w, b = rp.inputs_reduce_mean(rows, cols, seed=21)
+    want = torch.from_numpy(scalar.mean_relu_mul_add_bf16(*(tensor_to_bf16_bits(t) for t in (x, w, b))))
+    assert_close(rp.run_reference(rp.reduce_mean_fusion, [x, w, b]), want, F32_TOL, "oracle vs reference path")
+    dx, dw, db = cuda(x, w, b)
+    out = torch.empty(rows, device=DEV)
+    abi.launch(Template.ROW_REDUCE, [dx, dw, db], [out], reduce_params(mar_chain(torch.bfloat16), ReduceOp.MEAN))
+    assert_close(out, want, F32_TOL, f"reduce_mean {rows}x{cols}")
+
+
+def test_row_sum_max_fp32(executor):
+    gen = torch.Generator().manual_seed(22)
+    x = torch.randn(45, 1000, generator=gen)
+    dx = x.to(DEV)
+    ident = abi.ew_program(1, [], [0])
+    for op, want in ((ReduceOp.SUM, torch.from_numpy(scalar.row_sum_f32(x.numpy()))),
+                     (ReduceOp.MEAN, torch.from_numpy(scalar.row_sum_f32(x.numpy(), mean=True))),
+                     (ReduceOp.MAX, x.amax(-1)), (ReduceOp.MIN, x.amin(-1))):
+        out = torch.empty(45, device=DEV)
+        abi.launch(Template.ROW_REDUCE, [dx], [out], reduce_params(ident, op))
+        assert_close(out, want, F32_TOL, f"row reduce op {op}")
+
+
+def test_full_reduce_with_workspace(executor):
+    gen = torch.Generator().manual_seed(23)
+    x = torch.randn(300, 517, generator=gen)
+    dx = x.to(DEV)
+    out = torch.empty((), device=DEV)
+    p = reduce_params(abi.ew_program(1, [(EwOp.MUL, 0, 0, 0, 0, torch.float32)], [1]), ReduceOp.SUM)
+    n = abi.workspace_bytes(Template.FULL_REDUCE, [dx], [out], p)
+    assert n > 0
+    assert abi.launch(Template.FULL_REDUCE, [dx], [out], p, check=False) == -6        # no workspace
+    ws = torch.empty(n, dtype=torch.uint8, device=DEV)
+    for _ in range(2):                                                               # reusable scratch
+        abi.launch(Template.FULL_REDUCE, [dx], [out], p, workspace=ws)
+        assert_close(out, (x.double() * x.double()).sum().float(), F32_TOL, "sum of squares")
+
+
+# ---------------------------------------------------------------- K3 softmax
+def test_softmax_golden(executor):
+    g = load_golden("c3_softmax")
+    logits, grad, y = cuda(g["logits"], g["grad"], g["y"])
+    out = torch.empty_like(logits)
+    abi.launch(Template.SOFTMAX_FWD, [logits], [out])
+    assert_close(out, g["y"], F32_TOL, "softmax fwd golden")
+    dx = torch.empty_like(logits)
+    abi.launch(Template.SOFTMAX_BWD, [grad, y], [dx])
+    assert_close(dx, g["dx"], F32_TOL, "softmax bwd golden")
+
+
+def test_softmax_known_answers(executor):
+    ones = torch.ones(256, 512, device=DEV)
+    out = torch.empty_like(ones)
+    abi.launch(Template.SOFTMAX_FWD, [ones], [out])
+    assert (out - 1.0 / 512).abs().max().item() <= 1e-6
+    y = torch.full((16, 128), 0.5, device=DEV)
+    dy = torch.ones(16, 128, device=DEV)
+    dx = torch.empty_like(y)
+    abi.launch(Template.SOFTMAX_BWD, [dy, y], [dx])
+    assert (dx + 31.5).abs().max().item() <= 1e-6
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4), (3, 32), (17, 100), (5, 1000), (33, 1024), (9, 8192), (2, 16384),
+                                       (2, 32768), (2, 40000), (4, 8191)])
+def test_softmax_shapes(executor, rows, cols):
+    logits, grad = rp.inputs_softmax(rows, cols, seed=31)
+    want = torch.from_numpy(scalar.softmax_f32(logits.numpy()))
+    assert_close(torch.softmax(logits, -1), want, F32_TOL, "oracle vs eager")
+    dl, dg = cuda(logits, grad)
+    out = torch.empty_like(dl)
+    abi.launch(Template.SOFTMAX_FWD, [dl], [out])
+    assert_close(out, want, F32_TOL, f"softmax fwd {rows}x{cols}")
+    assert (out.sum(-1) - 1).abs().max().item() < 1e-4
+    dx = torch.empty_like(dl)
+    abi.launch(Template.SOFTMAX_BWD, [dg, out], [dx])
+    want_dx = torch.from_numpy(scalar.softmax_backward_f32(out.cpu().numpy(), grad.numpy()))
+    assert_close(dx, want_dx, F32_TOL, f"softmax bwd {rows}x{cols}")
+
+
+def test_softmax_bwd_matches_jacobian_form(executor):
+    logits, grad = rp.inputs_softmax(8, 256, seed=32)
+    y = torch.softmax(logits, -1)
+    want = torch.from_numpy(scalar.softmax_backward_f32(y.numpy(), grad.numpy(), jacobian=True))
+    dg, dy = cuda(grad, y)
+    dx = torch.empty_like(dy)
+    abi.launch(Template.SOFTMAX_BWD, [dg, dy], [dx])
+    assert_close(dx, want, F32_TOL, "softmax bwd vs O(n^2) Jacobian")
+
+
+def test_softmax_special_values(executor):
+    x = torch.randn(6, 512)
+    x[0, :] = -float("inf")                    # all -inf -> NaN row, as eager
+    x[1, 5:] = -float("inf")                   # partly masked
+    x[2, 7] = float("inf")                     # inf - inf -> NaN row
+    x[3, 9] = float("nan")
+    x[4] = 1e30
+    want = torch.softmax(x, -1)
+    dx = x.to(DEV)
+    out = torch.empty_like(dx)
+    abi.launch(Template.SOFTMAX_FWD, [dx], [out])
+    assert_close(out, want, F32_TOL, "softmax special values")
+
+
+def test_softmax_bf16(executor):
+    gen = torch.Generator().manual_seed(33)
+    x = (3 * torch.randn(40, 1024, generator=gen)).bfloat16()
+    g = torch.randn(40, 1024, generator=gen).bfloat16()
+    y = torch.softmax(x, -1)
+    dxr = torch._softmax_backward_data(g, y, -1, torch.bfloat16)
+    dx_, dg_, dy_ = cuda(x, g, y)
+    out = torch.empty_like(dx_)
+    abi.launch(Template.SOFTMAX_FWD, [dx_], [out])
+    assert_close(out.float(), y.float(), BF16_TOL, "softmax fwd bf16")
+    dx = torch.empty_like(dx_)
+    abi.launch(Template.SOFTMAX_BWD, [dg_, dy_], [dx])
+    assert_close(dx.float(), dxr.float(), BF16_TOL, "softmax bwd bf16")
+
+
+# ---------------------------------------------------------------- host-pointer entry point
+def test_execute_host_round_trip(executor):
+    g = load_golden("c1_mul_add")
+    out = torch.empty_like(g["a"])
+    rc = abi.execute_host(Template.ELEMENTWISE, [g["a"], g["b"], g["c"]], [out], abi.mul_add_program())
+    assert rc == 0, executor.lib.cdr_last_error()
+    assert bits_equal(out, g["out"])
+    g3 = load_golden("c3_softmax")
+    y = torch.empty_like(g3["logits"])
+    assert abi.execute_host(Template.SOFTMAX_FWD, [g3["logits"]], [y]) == 0
+    assert_close(y, g3["y"], F32_TOL, "host softmax")
+    assert executor.lib.cdr_release_host_arena(-1) == 0
+
+
+# ---------------------------------------------------------------- full benchmark sizes
+def test_full_size_mul_add_bit_exact(executor):
+    a, b, c = rp.inputs_mul_add()
+    want = rp.run_reference(rp.mul_add, [a, b, c])
+    da, db, dc = cuda(a, b, c)
+    out = torch.empty_like(da)
+    abi.launch(Template.ELEMENTWISE, [da, db, dc], [out], abi.mul_add_program())
+    assert bits_equal(out, want)
+
+
+def test_full_size_reduce_mean(executor):
+    x, w, b = rp.inputs_reduce_mean()
+    want = rp.run_reference(rp.reduce_mean_fusion, [x, w, b])
+    dx, dw, db = cuda(x, w, b)
+    out = torch.empty(x.shape[0], device=DEV)
+    abi.launch(Template.ROW_REDUCE, [dx, dw, db], [out], reduce_params(mar_chain(torch.bfloat16), ReduceOp.MEAN))
+    assert_close(out, want, F32_TOL, "full-size reduce_mean")
+
+
+def test_full_size_softmax(executor):
+    logits, grad = rp.inputs_softmax()
+    y_ref = rp.run_reference(rp.softmax_forward, [logits])
+    dl = logits.to(DEV)
+    y = torch.empty_like(dl)
+    abi.launch(Template.SOFTMAX_FWD, [dl], [y])
+    assert_close(y, y_ref, F32_TOL, "full-size softmax fwd")
+    assert (y.sum(-1) - 1).abs().max().item() < 1e-4          # rows are distributions
+    del dl
+    dx_ref = rp.run_reference(rp.softmax_backward, [grad, y_ref])
+    dg = grad.to(DEV)
+    dx = torch.empty_like(dg)
+    abi.launch(Template.SOFTMAX_BWD, [dg, y], [dx])
+    assert_close(dx, dx_ref, F32_TOL, "full-size softmax bwd")
+    assert dx.sum(-1).abs().max().item() < 1e-3               # softmax gradients sum to zero per row
