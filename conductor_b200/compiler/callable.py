@@ -127,6 +127,13 @@ class Callable:
                 result.append(item)
         return result
 
+    # ------------------------------------------------------------------ CUDA graphs
+    def capture(self, *device_tensors) -> "GraphedCall":
+        """Record one run of the plan on `device_tensors` into a CUDA graph.  Replaying it
+        re-runs every kernel of the plan on the same buffers with one driver call, which is
+        what keeps microsecond-scale plans from being launch-bound."""
+        return GraphedCall(self, device_tensors)
+
     # reference API (callable.py:96-152)
     def get_artifact(self) -> CompiledArtifact:
         return self.artifact
@@ -136,3 +143,33 @@ class Callable:
 
     def __repr__(self) -> str:
         return f"Callable({self.artifact.entry_point}, kernels={sum(1 for l in self.launches if l.template)})"
+
+
+class GraphedCall:
+    """A plan captured in a CUDA graph for fixed input buffers (see :meth:`Callable.capture`).
+
+    ``replay()`` enqueues the whole plan on the current stream; ``outputs`` are the tensors
+    the replay writes (they are reused by every replay)."""
+
+    def __init__(self, fn: Callable, device_tensors):
+        tensors = list(device_tensors)
+        if not tensors or any(t.device.type != "cuda" for t in tensors):
+            raise DeviceError("CUDA graphs capture device-resident inputs only")
+        self.fn = fn
+        self.inputs = tensors
+        device = tensors[0].device
+        env = dict(zip(fn.dag.inputs, tensors))
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.device(device), torch.cuda.stream(side):
+            fn._run_plan(dict(env), device)            # warm-up: lazy initialisation, constants
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.device(device), torch.cuda.graph(self.graph):
+            self.outputs = tuple(fn._run_plan(dict(env), device))
+        self.n_kernels = sum(1 for l in fn.launches if l.template)
+
+    def replay(self):
+        self.graph.replay()
+        return self.outputs

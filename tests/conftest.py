@@ -84,10 +84,10 @@ def assert_close(actual, expected, tol, what=""):
     assert not nan_mismatch.any(), f"{what}: NaN pattern differs"
     mask = ~torch.isnan(e)
     diff = (a[mask] - e[mask]).abs()
-    ok = (diff <= tol) | (diff <= tol * e[mask].abs())
+    ok = (a[mask] == e[mask]) | (diff <= tol) | (diff <= tol * e[mask].abs())
     if not ok.all():
         bad = (~ok).nonzero()
         i = bad[0].item()
         raise AssertionError(
             f"{what}: {int((~ok).sum())} of {ok.numel()} elements outside tol={tol}; "
-            f"first: got {a[mask][i].item()!r}, want {e[mask][i].item()!r}; max abs {diff.max().item():.3e}")
+            f"first: got {a[mask][i].item()!r}, want {e[mask][i].item()!r}; max abs {diff[~torch.isnan(diff)].max().item():.3e}")

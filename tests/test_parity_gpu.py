@@ -57,7 +57,7 @@ def test_mul_add_misaligned_pointers(executor):
     gen = torch.Generator().manual_seed(12)
     base = [torch.randn(4099, generator=gen).to(DEV) for _ in range(3)]
     a, b, c = (t[1:4098] for t in base)                      # data_ptr is 4 bytes off 16-byte alignment
-    out_base = torch.zeros(4099, device=DEV)
+    out_base = torch.zeros(4101, device=DEV)
     out = out_base[3:4100]
     abi.launch(Template.ELEMENTWISE, [a, b, c], [out], abi.mul_add_program())
     assert bits_equal(out, (a.cpu() * b.cpu() + c.cpu()))
