@@ -132,7 +132,12 @@ class Callable:
         """Record one run of the plan on `device_tensors` into a CUDA graph.  Replaying it
         re-runs every kernel of the plan on the same buffers with one driver call, which is
         what keeps microsecond-scale plans from being launch-bound."""
-        return GraphedCall(self, device_tensors)
+        return GraphedCall(self, [tuple(device_tensors)])
+
+    def capture_sequence(self, input_sets) -> "GraphedCall":
+        """Record one run of the plan per entry of `input_sets` (tuples of device tensors)
+        back to back in a single CUDA graph: one driver call replays the whole sequence."""
+        return GraphedCall(self, [tuple(t) for t in input_sets])
 
     # reference API (callable.py:96-152)
     def get_artifact(self) -> CompiledArtifact:
@@ -146,29 +151,32 @@ class Callable:
 
 
 class GraphedCall:
-    """A plan captured in a CUDA graph for fixed input buffers (see :meth:`Callable.capture`).
+    """One or more runs of a plan captured in a CUDA graph for fixed input buffers (see
+    :meth:`Callable.capture`, :meth:`Callable.capture_sequence`).
 
-    ``replay()`` enqueues the whole plan on the current stream; ``outputs`` are the tensors
-    the replay writes (they are reused by every replay)."""
+    ``replay()`` enqueues the recorded runs on the current stream.  ``outputs`` holds the
+    output tuple of the first run, ``all_outputs`` one tuple per run; the tensors are reused by
+    every replay."""
 
-    def __init__(self, fn: Callable, device_tensors):
-        tensors = list(device_tensors)
-        if not tensors or any(t.device.type != "cuda" for t in tensors):
+    def __init__(self, fn: Callable, input_sets):
+        if not input_sets or any(not ts or any(t.device.type != "cuda" for t in ts) for ts in input_sets):
             raise DeviceError("CUDA graphs capture device-resident inputs only")
         self.fn = fn
-        self.inputs = tensors
-        device = tensors[0].device
-        env = dict(zip(fn.dag.inputs, tensors))
+        self.input_sets = input_sets
+        device = input_sets[0][0].device
+        envs = [dict(zip(fn.dag.inputs, ts)) for ts in input_sets]
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.device(device), torch.cuda.stream(side):
-            fn._run_plan(dict(env), device)            # warm-up: lazy initialisation, constants
+            fn._run_plan(dict(envs[0]), device)        # warm-up: lazy initialisation, constants
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.device(device), torch.cuda.graph(self.graph):
-            self.outputs = tuple(fn._run_plan(dict(env), device))
-        self.n_kernels = sum(1 for l in fn.launches if l.template)
+            self.all_outputs = [tuple(fn._run_plan(dict(env), device)) for env in envs]
+        self.outputs = self.all_outputs[0]
+        self.runs = len(input_sets)
+        self.n_kernels = self.runs * sum(1 for l in fn.launches if l.template)
 
     def replay(self):
         self.graph.replay()

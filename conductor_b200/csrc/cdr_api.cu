@@ -33,6 +33,22 @@ int cuda_fail(cudaError_t e, const char* what) {
   return CDR_ERR_CUDA;
 }
 
+// One status word per device; kernels get its address as an argument.
+__device__ int g_status_word = 0;
+namespace {
+int* g_status_ptr[64] = {nullptr};
+}
+int* device_status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
 int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
@@ -134,6 +150,17 @@ int cdr_device_count(void) {
   cudaError_t e = cudaGetDeviceCount(&n);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
   return n;
+}
+
+int cdr_device_status(int* status_out, int clear) {
+  if (!status_out) { set_error("status_out is null"); return CDR_ERR_BAD_ARG; }
+  *status_out = 0;
+  int* p = device_status_ptr();
+  if (!p) { set_error("device status word unavailable"); return CDR_ERR_CUDA; }
+  CDR_CUDA_TRY(cudaDeviceSynchronize());
+  CDR_CUDA_TRY(cudaMemcpy(status_out, p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (clear && *status_out) CDR_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
+  return *status_out ? CDR_ERR_TIMEOUT : CDR_OK;
 }
 
 int cdr_workspace_bytes(int template_id, const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,

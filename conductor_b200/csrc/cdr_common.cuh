@@ -57,6 +57,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// Device pointer of the current device's status word (0 = ok; set by a kernel whose bounded
+// wait gave up).  nullptr if it cannot be obtained; kernels accept that.
+int* device_status_ptr();
 
 // Per-template launchers (defined in the template's .cu file).
 int launch_elementwise(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,

@@ -11,7 +11,7 @@
 //   forward : every thread forms a partial (max m_t, sum s_t of exp(x - m_t)) over its
 //             slice, partials are merged with the online-softmax recurrence
 //             s = s_a * exp(m_a - m) + s_b * exp(m_b - m) through warp shuffles and one
-//             shared-memory hop, then y = exp(x - m_t) * exp(m_t - m) / s.
+//             shared-memory hop, then y = exp(x - m_t) * (exp(m_t - m) / s).
 //   backward: dx = y * (g - sum(g * y)), the O(n) form of the reference's O(n^2) Jacobian
 //             product.
 // exp is the accurate expf (no fast-math), division is IEEE.
@@ -112,8 +112,8 @@ __global__ void __launch_bounds__((TPR > 256 ? TPR : 256)) softmax_fwd_kernel(co
     ms = acc;
   }
   // rows with no finite element (all -inf) give 0/0 = NaN, as eager does
-  const float scale = (m_t == -INFINITY ? 0.0f : expf(m_t - ms.m));
-  const float denom = ms.s;
+  // y = e * (exp(m_t - m) / s): one division per thread, one multiply per element
+  const float factor = __fdiv_rn(m_t == -INFINITY ? 0.0f : expf(m_t - ms.m), ms.s);
 
   T* dst = static_cast<T*>(a.out) + (live ? row : 0) * a.cols;
 #pragma unroll
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__((TPR > 256 ? TPR : 256)) softmax_fwd_kernel(co
     if (live && v < vec_per_row) {
       float y[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) y[e] = __fdiv_rn(x[j][e] * scale, denom);
+      for (int e = 0; e < V; ++e) y[e] = x[j][e] * factor;
       st_stream16(dst + v * V, Pack16<T>::pack(y));
     }
   }

@@ -196,6 +196,12 @@ CDR_API const char* cdr_last_error(void);
  * Replaces the device probe in conductor/compiler/topscc_utils.py:27-29. */
 CDR_API int cdr_device_count(void);
 
+/* Wait for the current device and read its status word: kernels whose bounded device-side
+ * waits gave up record (1 << 8 | site) there.  Returns CDR_OK (word is 0) or CDR_ERR_TIMEOUT
+ * with the word in *status_out; `clear` != 0 resets it.  Replaces the device-side
+ * `future` misuse detection of the reference runtime header (choreo-headers/choreo.h:1013-1112). */
+CDR_API int cdr_device_status(int* status_out, int clear);
+
 /* Bytes of device workspace cdr_launch() needs for this call (0 for most
  * templates).  Replaces the fixed `memory_pool_size_mb` of the reference runtime
  * configuration (conductor/utils/config.py:66-72). */
