@@ -94,7 +94,18 @@ class Callable:
                 env[buf] = self._stage_in(i, t, device) if t.device.type == "cpu" else t
             outputs = self._run_plan(env, device)
             if host_mode:
-                outputs = [o.cpu() if isinstance(o, torch.Tensor) else o for o in outputs]
+                # device -> pinned host (blocks come from torch's caching host allocator, so a
+                # steady-state call allocates nothing), then one wait for the whole plan
+                host = []
+                for o in outputs:
+                    if isinstance(o, torch.Tensor) and o.device.type == "cuda":
+                        h = torch.empty(o.shape, dtype=o.dtype, pin_memory=True)
+                        h.copy_(o, non_blocking=True)
+                        host.append(h)
+                    else:
+                        host.append(o)
+                torch.cuda.current_stream(device).synchronize()
+                outputs = host
         self.calls += 1
         return tuple(outputs)
 

@@ -1,0 +1,118 @@
+"""The built library loads, exports every symbol include/conductor_b200.h declares, and its
+struct layouts agree with what a C compiler makes of the header.  No compute calls: CPU only."""
+import ctypes
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from conductor_b200.codegen import kernel_templates as kt
+from conductor_b200.compiler import loader
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "conductor_b200.h"
+
+
+def declared_functions():
+    text = HEADER.read_text()
+    return sorted(set(re.findall(r"CDR_API\s+[\w\s\*]+?\b(cdr_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("cdr_abi_version", "cdr_launch", "cdr_execute_host", "cdr_workspace_bytes", "cdr_status_string",
+                 "cdr_last_error", "cdr_device_count", "cdr_device_status", "cdr_release_host_arena"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    lib = ctypes.CDLL(str(built_library))
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert set(declared_functions()) == set(loader.SYMBOLS), "loader.SYMBOLS and the header disagree"
+
+
+def test_loader_binds_and_checks_abi_version(built_library):
+    lib = loader.load_library()
+    assert lib.cdr_abi_version() == loader.ABI_VERSION
+    assert lib.cdr_status_string(0) == b"ok"
+    assert b"unsupported" in lib.cdr_status_string(-2)
+    assert lib.cdr_last_error() is not None
+
+
+def test_argument_errors_need_no_gpu(built_library):
+    lib = loader.load_library()
+    n = ctypes.c_size_t(7)
+    # unknown template -> UNSUPPORTED before any CUDA call
+    assert lib.cdr_workspace_bytes(99, None, 0, None, 0, None, 0, ctypes.byref(n)) == -2
+    assert b"unknown template" in lib.cdr_last_error()
+    # wrong parameter block size -> BAD_ARG
+    p = kt.CdrGemmParams(0, 0)
+    assert lib.cdr_workspace_bytes(1, None, 0, None, 0, ctypes.cast(ctypes.byref(p), ctypes.c_void_p),
+                                   ctypes.sizeof(p), ctypes.byref(n)) == -1
+    assert lib.cdr_workspace_bytes(1, None, 0, None, 0, None, 0, None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from conductor_b200.utils.exceptions import DeviceError
+
+    monkeypatch.setenv("CONDUCTOR_B200_LIB", str(tmp_path / "nope.so"))
+    loader.unload_library()
+    try:
+        with pytest.raises(DeviceError):
+            loader.load_library()
+    finally:
+        monkeypatch.delenv("CONDUCTOR_B200_LIB")
+        loader.unload_library()
+        loader.load_library()
+
+
+def test_struct_layouts_match_the_c_compiler(tmp_path):
+    src = tmp_path / "sizes.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "conductor_b200.h"\n'
+        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(cdr_tensor), sizeof(cdr_ew_instr),"
+        " sizeof(cdr_ew_params), sizeof(cdr_reduce_params), sizeof(cdr_gemm_params), sizeof(cdr_attn_params),"
+        " offsetof(cdr_tensor, shape), offsetof(cdr_ew_params, instr), offsetof(cdr_reduce_params, reduce_op));"
+        "return 0;}\n")
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c99", "-I", str(HEADER.parent), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    want = [ctypes.sizeof(kt.CdrTensor), ctypes.sizeof(kt.CdrEwInstr), ctypes.sizeof(kt.CdrEwParams),
+            ctypes.sizeof(kt.CdrReduceParams), ctypes.sizeof(kt.CdrGemmParams), ctypes.sizeof(kt.CdrAttnParams),
+            kt.CdrTensor.shape.offset, kt.CdrEwParams.instr.offset, kt.CdrReduceParams.reduce_op.offset]
+    assert got == want
+
+
+def test_backend_registration_and_aliases():
+    import torch
+
+    import conductor
+
+    assert "gcu" in torch._dynamo.list_backends(None)
+    assert conductor.get_gcu_backend() is conductor.get_gcu_backend()
+    assert isinstance(conductor.get_gcu_backend(), conductor.GCUBackend)
+    assert conductor.register_gcu_backend() is True
+    from conductor.utils.exceptions import CompilationError, ConductorError, ExecutionError  # noqa: F401
+    import conductor_b200.utils.exceptions as impl
+
+    assert ExecutionError is impl.ExecutionError and issubclass(CompilationError, ConductorError)
+    assert conductor.get_config().runtime.device == "gcu"
+
+
+def test_cpu_only_call_raises_device_error_not_fallback():
+    """Without a CUDA device the compiled callable must refuse to run (no CPU path)."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    import conductor  # noqa: F401
+    from conductor.utils.exceptions import DeviceError
+
+    torch._dynamo.reset()
+    fn = torch.compile(lambda a, b, c: a * b + c, backend="gcu")
+    with pytest.raises(Exception) as info:
+        fn(torch.randn(4, 4), torch.randn(4, 4), torch.randn(4, 4))
+    assert "DeviceError" in repr(info.value) or isinstance(info.value, DeviceError) or "no CUDA device" in str(info.value)
+    torch._dynamo.reset()

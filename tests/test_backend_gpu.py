@@ -1,0 +1,121 @@
+"""End-to-end through the plugin surface: `torch.compile(fn, backend='gcu')` on CUDA tensors and
+on CPU tensors (the reference's calling convention), compared with the reference's executed path
+(eager on CPU) on identical seeded inputs."""
+import pytest
+import torch
+
+import conductor  # noqa: F401
+from conftest import assert_close
+from examples import workloads as wl
+from oracle import reference_path as rp
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def compiled(fn):
+    torch._dynamo.reset()
+    return torch.compile(fn, backend="gcu")
+
+
+def run_both(fn, inputs):
+    """(result with CUDA inputs, result with CPU inputs, reference result)."""
+    want = rp.run_reference(fn, inputs)
+    f = compiled(fn)
+    with torch.no_grad():
+        on_gpu = f(*[t.to(DEV) for t in inputs])
+        assert on_gpu.device.type == "cuda"
+        on_cpu = f(*inputs)
+        assert on_cpu.device.type == "cpu"
+    return on_gpu, on_cpu, want
+
+
+def test_mul_add_bit_exact_both_conventions():
+    on_gpu, on_cpu, want = run_both(wl.mul_add, wl.inputs_mul_add(300, 257, seed=41))
+    assert torch.equal(on_gpu.cpu(), want) and torch.equal(on_cpu, want)
+
+
+def test_reduce_mean_fusion():
+    on_gpu, on_cpu, want = run_both(wl.reduce_mean_fusion, wl.inputs_reduce_mean(100, 4096, seed=42))
+    assert_close(on_gpu, want, 1e-5, "reduce_mean gpu")
+    assert_close(on_cpu, want, 1e-5, "reduce_mean host")
+
+
+def test_softmax_forward_and_both_backward_forms():
+    logits, grad = wl.inputs_softmax(64, 8192, seed=43)
+    y_gpu, y_cpu, y_want = run_both(wl.softmax_forward, [logits])
+    assert_close(y_gpu, y_want, 1e-5, "softmax fwd")
+    assert_close(y_cpu, y_want, 1e-5, "softmax fwd host")
+    for fn in (wl.softmax_backward, wl.softmax_backward_written_out):
+        dx_gpu, _, dx_want = run_both(fn, [grad, y_want])
+        assert_close(dx_gpu, dx_want, 1e-5, fn.__name__)
+
+
+def test_unfused_graph_matches_fused():
+    from conductor_b200.utils.config import get_config
+
+    a, b, c = wl.inputs_mul_add(64, 128, seed=44)
+    cfg = get_config()
+    cfg.compilation.enable_fusion = False
+    try:
+        out = compiled(wl.mul_add)(a.to(DEV), b.to(DEV), c.to(DEV))
+    finally:
+        cfg.compilation.enable_fusion = True
+    assert torch.equal(out.cpu(), a * b + c)
+
+
+def test_multi_cluster_graph_with_shared_temporary():
+    def model(x, y):
+        t = x + y
+        s = t.sum(-1, keepdim=True)
+        return (t - s) * x, torch.relu(t)
+
+    x, y = torch.randn(33, 200), torch.randn(33, 200)
+    want = rp.run_reference(model, [x, y])
+    got = compiled(model)(x.to(DEV), y.to(DEV))
+    assert isinstance(got, tuple) and len(got) == 2
+    assert_close(got[0], want[0], 1e-5, "diamond")
+    assert torch.equal(got[1].cpu(), want[1])
+
+
+def test_graph_capture_replays_the_plan():
+    from conductor_b200.compiler.gcu_backend import get_gcu_backend
+
+    x, w, b = (t.to(DEV) for t in wl.inputs_reduce_mean(256, 4096, seed=45))
+    f = compiled(wl.reduce_mean_fusion)
+    want = f(x, w, b).clone()
+    plan = list(get_gcu_backend()._compiled_functions.values())[-1]
+    g = plan.capture(x, w, b)
+    (out,) = g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    x.mul_(2)                                   # same buffer, new contents: replay sees them
+    (out2,) = g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out2, f(x, w, b))
+    seq = plan.capture_sequence([(x, w, b), (x, w, b)])
+    seq.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(seq.all_outputs[1][0], seq.all_outputs[0][0]) and seq.n_kernels == 2
+
+
+def test_wrong_shape_at_call_time_raises():
+    from conductor.utils.exceptions import ExecutionError
+    from conductor_b200.compiler.gcu_backend import get_gcu_backend
+
+    a, b, c = (t.to(DEV) for t in wl.inputs_mul_add(8, 8, seed=46))
+    compiled(wl.mul_add)(a, b, c)
+    plan = list(get_gcu_backend()._compiled_functions.values())[-1]
+    with pytest.raises(ExecutionError):
+        plan(a[:4], b[:4], c[:4])
+
+
+def test_device_status_word_is_clean():
+    import ctypes
+
+    from conductor_b200.compiler.loader import load_library
+
+    st = ctypes.c_int(-1)
+    with torch.cuda.device(0):
+        assert load_library().cdr_device_status(ctypes.byref(st), 1) == 0
+    assert st.value == 0

@@ -1,0 +1,184 @@
+"""Clustering and template selection on the five benchmark graphs (as Dynamo traces them) and
+on edge cases; CPU only -- nothing is launched."""
+import ctypes
+
+import pytest
+import torch
+
+import conductor  # noqa: F401  registers 'gcu'
+from conductor.compiler.jit_compiler import ChoreoJITCompiler
+from conductor.optimization.fusion import FusionCluster, FusionHeuristics, FusionType, LocalPriorityFusionEngine
+from conductor.optimization.graph_analyzer import GraphAnalyzer
+from conductor.utils.exceptions import UnsupportedOperationError
+from conductor_b200.codegen.kernel_templates import IN_COL, IN_FULL, IN_ROW, IN_SCALAR, classify_broadcast
+from conductor_b200.codegen.operator_registry import EwOp, ReduceOp, Template
+from examples import workloads as wl
+
+
+def compile_with_dynamo(fn, inputs):
+    """Trace `fn` with Dynamo and run this package's compile pipeline on the graph it hands a
+    backend; returns the CompiledArtifact (nothing executes)."""
+    box = {}
+
+    def backend(gm, example_inputs):
+        from conductor_b200.utils.config import get_config
+
+        box["artifact"] = ChoreoJITCompiler().compile_graph(gm, example_inputs)
+        return gm.forward
+
+    torch._dynamo.reset()
+    with torch.no_grad():
+        torch.compile(fn, backend=backend)(*inputs)
+    torch._dynamo.reset()
+    return box["artifact"]
+
+
+def assert_unsupported(fn, inputs):
+    """Dynamo wraps what a backend raises in BackendCompilerFailed; the cause must be ours."""
+    with pytest.raises(Exception) as info:
+        compile_with_dynamo(fn, inputs)
+    exc = info.value
+    inner = getattr(exc, "inner_exception", None) or exc.__cause__ or exc
+    assert isinstance(inner, UnsupportedOperationError), repr(exc)
+
+
+def kernels(artifact):
+    return [l for l in artifact.launches if l.template]
+
+
+def test_c1_mul_add_is_one_elementwise_cluster():
+    art = compile_with_dynamo(wl.mul_add, wl.inputs_mul_add(8, 16))
+    (k,) = kernels(art)
+    assert k.template == Template.ELEMENTWISE and k.name == "elementwise[mul,add]"
+    c = k.cluster
+    assert [b.name for b in c.external_inputs] == ["l_a_", "l_b_", "l_c_"]
+    assert len(c.external_outputs) == 1 and len(c.internal_buffers) == 1
+    assert c.internal_buffers[0].scope.value == "local"
+    p = k.params
+    assert (p.n_inputs, p.n_instr, p.n_outputs, p.out_reg[0]) == (3, 2, 1, 4)
+    assert (p.instr[0].op, p.instr[1].op) == (EwOp.MUL, EwOp.ADD)
+    assert c.validate_fusion_safety()
+
+
+def test_c2_reduce_mean_is_one_reduction_cluster():
+    art = compile_with_dynamo(wl.reduce_mean_fusion, wl.inputs_reduce_mean(8, 64))
+    (k,) = kernels(art)
+    assert k.template == Template.ROW_REDUCE and k.name == "reduction[mul,add,relu,reduce_mean]"
+    p = k.params
+    assert p.reduce_op == ReduceOp.MEAN
+    assert [p.chain.input_mode[i] for i in range(3)] == [IN_FULL, IN_ROW, IN_ROW]
+    assert [p.chain.instr[i].op for i in range(p.chain.n_instr)] == [EwOp.MUL, EwOp.ADD, EwOp.RELU]
+    assert all(p.chain.instr[i].round_to == 1 for i in range(3))           # every op rounds to bf16
+    assert k.out_dtypes == [torch.float32] and k.out_shapes == [(8,)]
+    assert len(k.cluster.internal_buffers) == 3
+
+
+def test_float_cast_before_mean_is_folded_away():
+    fn = lambda x, w, b: torch.relu(x * w + b).float().mean(-1)  # noqa: E731
+    (k,) = kernels(compile_with_dynamo(fn, wl.inputs_reduce_mean(8, 64)))
+    assert k.template == Template.ROW_REDUCE and k.params.chain.n_instr == 3
+
+
+def test_c3_softmax_forward_and_backward():
+    logits, grad = wl.inputs_softmax(4, 32)
+    (k,) = kernels(compile_with_dynamo(wl.softmax_forward, [logits]))
+    assert k.template == Template.SOFTMAX_FWD
+    y = torch.softmax(logits, -1)
+    (k,) = kernels(compile_with_dynamo(wl.softmax_backward, [grad, y]))
+    assert k.template == Template.SOFTMAX_BWD and [b.name for b in k.inputs] == ["l_grad_", "l_y_"]
+    (k,) = kernels(compile_with_dynamo(wl.softmax_backward_written_out, [grad, y]))
+    assert k.template == Template.SOFTMAX_BWD and k.name == "softmax[mul,sum,sub,mul]"
+    assert [b.name for b in k.inputs] == ["l_grad_", "l_y_"]
+
+
+def test_softmax_over_other_dim_is_refused():
+    assert_unsupported(lambda x: torch.softmax(x, 0), [torch.randn(4, 8)])
+
+
+def test_c4_mlp_two_gemm_epilogue_clusters():
+    mlp = wl.make_mlp(32, 64, 32)
+    ks = kernels(compile_with_dynamo(mlp, wl.inputs_mlp(16, 32)))
+    assert [k.name for k in ks] == ["gemm_epilogue[linear,relu]", "gemm_epilogue[linear]"]
+    assert (ks[0].params.activation, ks[0].params.has_bias) == (1, 1)
+    assert (ks[1].params.activation, ks[1].params.has_bias) == (0, 1)
+    assert ks[0].outputs[0] is ks[1].inputs[0] and ks[0].outputs[0].scope.value == "shared"
+    assert ks[0].out_shapes == [(16, 64)] and ks[1].out_shapes == [(16, 32)]
+
+
+def test_c5_attention_cluster():
+    (k,) = kernels(compile_with_dynamo(wl.causal_attention, wl.inputs_attention(1, 2, 16, 32)))
+    assert k.template == Template.ATTENTION and k.params.causal == 1
+    assert abs(k.params.scale - 32 ** -0.5) < 1e-7
+
+
+def test_unknown_op_raises_instead_of_falling_back():
+    assert_unsupported(lambda x: torch.cumsum(x, 0), [torch.randn(4)])
+
+
+def test_fusion_disabled_gives_one_kernel_per_node():
+    from conductor_b200.utils.config import get_config
+
+    cfg = get_config()
+    cfg.compilation.enable_fusion = False
+    try:
+        ks = kernels(compile_with_dynamo(wl.mul_add, wl.inputs_mul_add(8, 16, seed=3)))
+        assert [k.name for k in ks] == ["elementwise[mul]", "elementwise[add]"]
+    finally:
+        cfg.compilation.enable_fusion = True
+
+
+def test_diamond_graph_stays_acyclic():
+    def model(x, y):
+        t = x + y
+        s = t.sum(-1, keepdim=True)      # reduction between two elementwise groups
+        return (t - s) * x
+
+    art = compile_with_dynamo(model, [torch.randn(4, 8), torch.randn(4, 8)])
+    names = [k.name for k in kernels(art)]
+    assert len(names) == 3 and names[1].startswith("reduction[")
+    produced = set()
+    for k in kernels(art):                                   # every input is produced earlier
+        for b in k.inputs:
+            assert b.is_input or b in produced
+        produced.update(k.outputs)
+
+
+def test_scalars_lower_to_immediates():
+    (k,) = kernels(compile_with_dynamo(lambda x: (x * 2.0 + 1.0) / 3.0 - x, [torch.randn(4, 4)]))
+    ops = [k.params.instr[i].op for i in range(k.params.n_instr)]
+    assert ops[:2] == [EwOp.MUL_IMM, EwOp.ADD_IMM] and EwOp.DIV in ops and ops[-1] == EwOp.SUB
+
+
+def test_broadcast_classification():
+    assert classify_broadcast((4, 8), (4, 8)) == IN_FULL
+    assert classify_broadcast((8,), (4, 8)) == IN_ROW
+    assert classify_broadcast((1, 8), (4, 8)) == IN_ROW
+    assert classify_broadcast((4, 1), (4, 8)) == IN_COL
+    assert classify_broadcast((), (4, 8)) == IN_SCALAR
+    assert classify_broadcast((2, 3, 1), (2, 3, 5)) == IN_COL
+    with pytest.raises(UnsupportedOperationError):
+        classify_broadcast((4, 1, 8), (4, 3, 8))
+
+
+def test_heuristics_and_cluster_api():
+    h = FusionHeuristics()
+    assert h.can_fuse_elementwise("mul", "add") and h.can_fuse_elementwise("add", "relu")
+    assert h.can_fuse_elementwise("relu", "reduce_mean") and h.can_fuse_elementwise("linear", "relu")
+    assert not h.can_fuse_elementwise("softmax", "add") and not h.can_fuse_elementwise("nope", "add")
+    import torch.fx as fx
+
+    dag = GraphAnalyzer().parse_fx_graph(fx.symbolic_trace(lambda a, b, c: a * b + c), [torch.randn(64, 64)] * 3)
+    (c,) = LocalPriorityFusionEngine().identify_fusion_opportunities(dag)
+    assert isinstance(c, FusionCluster) and c.cluster_type is FusionType.ELEMENTWISE
+    assert c.estimate_performance_gain() > 0 and c.get_fusion_priority() > 300
+    assert "elementwise[mul,add]" in c.generate_fused_dsl()
+    assert h.check_memory_constraints(c)
+
+
+def test_params_struct_sizes_match_header():
+    from conductor_b200.codegen import kernel_templates as kt
+
+    assert ctypes.sizeof(kt.CdrTensor) == 8 + 4 + 4 + 64 + 64
+    assert ctypes.sizeof(kt.CdrEwInstr) == 24
+    assert ctypes.sizeof(kt.CdrEwParams) == 16 + 32 + 16 + 24 * 24
+    assert ctypes.sizeof(kt.CdrReduceParams) == ctypes.sizeof(kt.CdrEwParams) + 8
