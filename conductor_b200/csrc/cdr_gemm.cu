@@ -1,7 +1,315 @@
+// K4 -- GEMM with fused bias + activation epilogue:  out[M,N] = act(x[M,K] @ W[N,K]^T + bias[N]).
+//
+// Reference definitions: the naive triple loop of choreo-op/matmul-gcu-only-test.co:8-16 and the
+// string kernel conductor/codegen/device_kernels.py:84-103; the executed path is eager
+// torch.nn.functional.linear (+ relu) in bf16 with fp32 accumulation.
+//
+// Tensor-core bound.  Blackwell-native structure, one persistent CTA per SM:
+//   warp 0     TMA producer: 128x64 tile of x and 256x64 tile of W per k-block into a 4-stage
+//              shared-memory ring (128-byte swizzle; both operands are K-major as stored)
+//   warp 1     MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16) x4 per k-block,
+//              accumulating in tensor memory; tcgen05.commit releases the ring stage
+//   warps 2-5  epilogue: tcgen05.ld the fp32 accumulator (lane = output row), add bias, ReLU,
+//              round to bf16, store
+// The accumulator is double buffered in TMEM (2 x 256 columns), so the epilogue of tile i runs
+// under the MMAs of tile i+1.  Tiles are walked M-fastest so that concurrently running CTAs
+// share the same weight tile in L2.  No load is multicast; every mbarrier wait is bounded.
+#include <cuda.h>
+
 #include "cdr_common.cuh"
+#include "cdr_sm100.cuh"
+
 namespace cdr {
-int launch_gemm_epilogue(const cdr_tensor*, int, const cdr_tensor*, int, const cdr_gemm_params*, cudaStream_t) {
-  set_error("gemm_epilogue: not built yet");
-  return CDR_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int ACC_STAGES = 2;
+constexpr int TMEM_COLS = ACC_STAGES * BN;  // 512: all of tensor memory
+constexpr int NUM_THREADS = 192;
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmArgs {
+  CUtensorMap tmap_a;  // x  [M, K], box 64 x 128
+  CUtensorMap tmap_b;  // W  [N, K], box 64 x 256
+  const void* bias;    // [N] or nullptr
+  void* out;           // [M, N]
+  int M, N, K;
+  int relu;
+  int is_bf16;
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
+template <bool BF16>
+__device__ __forceinline__ float load_elem(const void* p, int i) {
+  if (BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+template <bool BF16>
+__device__ __forceinline__ void store_elem(void* p, size_t i, float v) {
+  if (BF16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __grid_constant__ GemmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == 0 && lane == 0) {
+    sm100::prefetch_tensormap(&a.tmap_a);
+    sm100::prefetch_tensormap(&a.tmap_b);
+    for (int s = 0; s < STAGES; ++s) {
+      sm100::mbar_init(&full[s], 1);
+      sm100::mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < ACC_STAGES; ++s) {
+      sm100::mbar_init(&acc_full[s], 1);
+      sm100::mbar_init(&acc_empty[s], 4);  // one arrival per epilogue warp
+    }
+    sm100::fence_barrier_init();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(tmem_slot, TMEM_COLS);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = a.tiles_m * a.tiles_n;
+  const int kblocks = (a.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % a.tiles_m) * BM, n0 = (tile / a.tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!sm100::mbar_wait(&empty[s], ph ^ 1)) { sm100::report_timeout(a.status, 10); ok = false; break; }
+          sm100::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+          unsigned char* st = smem + s * STAGE_BYTES;
+          sm100::tma_load_2d(st, &a.tmap_a, kb * BK, m0, &full[s]);
+          sm100::tma_load_2d(st + A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = sm100::umma_idesc_f16(BM, BN, BF16, false, false);
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        const uint32_t as = tile_iter % ACC_STAGES, aph = (tile_iter / ACC_STAGES) & 1;
+        if (!sm100::mbar_wait(&acc_empty[as], aph ^ 1)) { sm100::report_timeout(a.status, 11); break; }
+        sm100::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!sm100::mbar_wait(&full[s], ph)) { sm100::report_timeout(a.status, 12); ok = false; break; }
+          sm100::tc_fence_after();
+          const uint32_t a_addr = sm100::smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
+            const uint64_t bdesc = sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
+            sm100::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          sm100::umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+        }
+        if (ok) sm100::umma_commit(&acc_full[as]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t tile_iter = 0;
+    const bool vec_ok = (a.N % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
+      const int m0 = (tile % a.tiles_m) * BM, n0 = (tile / a.tiles_m) * BN;
+      const uint32_t as = tile_iter % ACC_STAGES, aph = (tile_iter / ACC_STAGES) & 1;
+      if (!sm100::mbar_wait(&acc_full[as], aph)) { sm100::report_timeout(a.status, 13); break; }
+      sm100::tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_base = tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        sm100::tmem_ld32(t_base + c * 32, r);
+        sm100::tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < a.M && col0 < a.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(r[j]);
+            if (a.bias != nullptr && col0 + j < a.N) x += load_elem<BF16>(a.bias, col0 + j);
+            v[j] = x;
+          }
+          const size_t off = static_cast<size_t>(row) * a.N + col0;
+          if (vec_ok && col0 + 32 <= a.N) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + off * 2);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t w[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                float lo = v[g * 8 + h * 2], hi = v[g * 8 + h * 2 + 1];
+                if (a.relu) { lo = lo > 0.0f ? lo : (lo != lo ? lo : 0.0f); hi = hi > 0.0f ? hi : (hi != hi ? hi : 0.0f); }
+                w[h] = pack2<BF16>(lo, hi);
+              }
+              dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < a.N; ++j) {
+              float x = v[j];
+              if (a.relu) x = x > 0.0f ? x : (x != x ? x : 0.0f);
+              store_elem<BF16>(a.out, off + j, x);
+            }
+          }
+        }
+      }
+      sm100::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tc_fence_after();
+    sm100::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+// Row-major 2-D tensor [rows, cols] of 16-bit elements, box = box_cols x box_rows, 128-byte swizzle.
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int is_bf16, int64_t rows, int64_t cols, int box_rows,
+                       int box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return CDR_ERR_CUDA; }
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d", static_cast<int>(r)); return CDR_ERR_CUDA; }
+  return CDR_OK;
+}
+
+int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
+                         const cdr_gemm_params* p, cudaStream_t stream) {
+  if (!p) { set_error("gemm_epilogue: params is null"); return CDR_ERR_BAD_ARG; }
+  const int want_in = p->has_bias ? 3 : 2;
+  if (n_in != want_in || n_out != 1) {
+    set_error("gemm_epilogue: expects %d inputs and 1 output, got %d and %d", want_in, n_in, n_out);
+    return CDR_ERR_BAD_ARG;
+  }
+  if (p->activation != CDR_ACT_NONE && p->activation != CDR_ACT_RELU) {
+    set_error("gemm_epilogue: unknown activation %d", p->activation);
+    return CDR_ERR_UNSUPPORTED;
+  }
+  const cdr_tensor &x = ins[0], &w = ins[1], &out = outs[0];
+  if (x.rank < 1 || w.rank != 2) { set_error("gemm_epilogue: x needs rank >= 1 and W rank 2"); return CDR_ERR_BAD_ARG; }
+  const int64_t K = x.shape[x.rank - 1];
+  const int64_t M = K ? numel(x) / K : 0;
+  const int64_t N = w.shape[0];
+  if (w.shape[1] != K) { set_error("gemm_epilogue: x has K=%lld, W has K=%lld", (long long)K, (long long)w.shape[1]); return CDR_ERR_BAD_ARG; }
+  if (numel(out) != M * N) { set_error("gemm_epilogue: output must hold %lld elements", (long long)(M * N)); return CDR_ERR_BAD_ARG; }
+  const int dt = x.dtype;
+  if (dt != CDR_BF16 && dt != CDR_F16) { set_error("gemm_epilogue: dtype %d unsupported (bf16 and f16 only)", dt); return CDR_ERR_UNSUPPORTED; }
+  if (w.dtype != dt || out.dtype != dt || (p->has_bias && ins[2].dtype != dt)) {
+    set_error("gemm_epilogue: x, W, bias and output must share one dtype");
+    return CDR_ERR_UNSUPPORTED;
+  }
+  if (!is_contiguous(x) || !is_contiguous(w) || !is_contiguous(out) || (p->has_bias && !is_contiguous(ins[2]))) {
+    set_error("gemm_epilogue: tensors must be contiguous");
+    return CDR_ERR_BAD_ARG;
+  }
+  if (p->has_bias && numel(ins[2]) != N) { set_error("gemm_epilogue: bias must hold N=%lld elements", (long long)N); return CDR_ERR_BAD_ARG; }
+  if (M == 0 || N == 0) return CDR_OK;
+  if (K == 0) { set_error("gemm_epilogue: K == 0"); return CDR_ERR_UNSUPPORTED; }
+  if (!x.data || !w.data || !out.data || (p->has_bias && !ins[2].data)) { set_error("gemm_epilogue: null pointer"); return CDR_ERR_BAD_ARG; }
+  if (K % 8 != 0) { set_error("gemm_epilogue: K=%lld must be a multiple of 8 (16-byte row pitch for TMA)", (long long)K); return CDR_ERR_UNSUPPORTED; }
+  if (!aligned16(x.data) || !aligned16(w.data)) { set_error("gemm_epilogue: x and W must be 16-byte aligned"); return CDR_ERR_MISALIGNED; }
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) { set_error("gemm_epilogue: extent too large"); return CDR_ERR_UNSUPPORTED; }
+
+  GemmArgs a;
+  if (int rc = make_tensor_map_2d(&a.tmap_a, x.data, dt == CDR_BF16, M, K, BM, BK)) return rc;
+  if (int rc = make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, BN, BK)) return rc;
+  a.bias = p->has_bias ? ins[2].data : nullptr;
+  a.out = out.data;
+  a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
+  a.relu = p->activation == CDR_ACT_RELU;
+  a.is_bf16 = dt == CDR_BF16;
+  a.tiles_m = static_cast<int>((M + BM - 1) / BM);
+  a.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  a.status = device_status_ptr();
+  const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
+  int grid = sm_count();
+  if (grid > tiles) grid = static_cast<int>(tiles);
+
+  static bool configured_dev[64] = {false};
+  int dev = 0;
+  CDR_CUDA_TRY(cudaGetDevice(&dev));
+  bool& configured = configured_dev[dev & 63];
+  if (!configured) {
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(SMEM_BYTES)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(SMEM_BYTES)));
+    configured = true;
+  }
+  if (dt == CDR_BF16) gemm_epilogue_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a);
+  else gemm_epilogue_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a);
+  CDR_CUDA_TRY(cudaGetLastError());
+  return CDR_OK;
+}
+
 }  // namespace cdr

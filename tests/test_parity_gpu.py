@@ -351,3 +351,71 @@ def test_full_size_softmax(executor):
     abi.launch(Template.SOFTMAX_BWD, [dg, y], [dx])
     assert_close(dx, dx_ref, F32_TOL, "full-size softmax bwd")
     assert dx.sum(-1).abs().max().item() < 1e-3               # softmax gradients sum to zero per row
+
+
+# ---------------------------------------------------------------- K4 GEMM + bias + ReLU
+from conductor_b200.codegen.kernel_templates import CdrAttnParams, CdrGemmParams  # noqa: E402
+
+
+def gemm(x, w, bias=None, relu=False):
+    ins = [x, w] + ([bias] if bias is not None else [])
+    out = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+    abi.launch(Template.GEMM_EPILOGUE, ins, [out], CdrGemmParams(1 if relu else 0, 1 if bias is not None else 0))
+    return out
+
+
+def test_mlp_golden(executor):
+    g = load_golden("c4_mlp")
+    x, w1, b1, w2, b2 = cuda(g["x"], g["w1"], g["b1"], g["w2"], g["b2"])
+    h = gemm(x, w1, b1, relu=True)
+    out = gemm(h, w2, b2)
+    assert_close(out.float(), g["out"].float(), BF16_TOL, "mlp golden")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (1, 8, 8), (33, 40, 72), (200, 520, 136),
+                                   (384, 768, 1024), (130, 257, 64), (1024, 1024, 4096)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_gemm_shapes_against_oracle(executor, M, N, K, relu):
+    gen = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    x = torch.randn(M, K, generator=gen).bfloat16()
+    w = (torch.randn(N, K, generator=gen) / K ** 0.5).bfloat16()
+    b = torch.randn(N, generator=gen).bfloat16()
+    if M * N * K <= 1 << 26:
+        want = bf16_bits_to_tensor(scalar.linear_bf16(*(tensor_to_bf16_bits(t) for t in (x, w, b)), relu=relu)).float()
+    else:                                     # the scalar oracle would take minutes: eager CPU instead
+        want = torch.nn.functional.linear(x, w, b)
+        want = (torch.relu(want) if relu else want).float()
+    out = gemm(*cuda(x, w, b), relu=relu)
+    assert_close(out.float(), want, BF16_TOL, f"gemm {M}x{N}x{K}")
+
+
+def test_gemm_without_bias_fp16_and_3d_input(executor):
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(4, 50, 96, generator=gen).half()
+    w = (torch.randn(72, 96, generator=gen) / 10).half()
+    out = gemm(*cuda(x, w))
+    assert out.shape == (4, 50, 72)
+    assert_close(out.float(), (x.float() @ w.float().T), BF16_TOL, "fp16 gemm")
+
+
+def test_gemm_rejects_what_it_cannot_run(executor):
+    x = torch.randn(8, 12, device=DEV).bfloat16()         # K=12: row pitch not a multiple of 16 bytes
+    w = torch.randn(8, 12, device=DEV).bfloat16()
+    out = torch.empty(8, 8, device=DEV, dtype=torch.bfloat16)
+    assert abi.launch(Template.GEMM_EPILOGUE, [x, w], [out], CdrGemmParams(0, 0), check=False) == -2
+    xf = torch.randn(8, 16, device=DEV)
+    assert abi.launch(Template.GEMM_EPILOGUE, [xf, xf], [torch.empty(8, 8, device=DEV)], CdrGemmParams(0, 0),
+                      check=False) == -2
+
+
+def test_full_size_mlp_through_backend(executor):
+    import conductor  # noqa: F401
+
+    mlp = rp.make_mlp()
+    (x,) = rp.inputs_mlp()
+    want = rp.run_reference(mlp, [x])
+    torch._dynamo.reset()
+    with torch.no_grad():
+        out = torch.compile(mlp.to(DEV), backend="gcu")(x.to(DEV))
+    assert_close(out.float(), want.float(), BF16_TOL, "full-size MLP")
+    mlp.cpu()
