@@ -201,6 +201,10 @@ def time_reference(wl: Workload, steps: int, warmup: int):
     torch.set_num_threads(cores)
     inputs = wl.make(0)
     fn = wl.fn
+    if wl.module is not None:
+        import copy
+
+        fn = copy.deepcopy(wl.module).cpu()
     torch._dynamo.reset()
     compiled = torch.compile(fn, backend=rp.reference_backend)
     with torch.no_grad():
@@ -268,6 +272,17 @@ def gpu_arm(args, wl: Workload):
     backend = get_gcu_backend()
     plan = list(backend._compiled_functions.values())[-1]
     kernels_per_step = sum(1 for l in plan.launches if l.template)
+    # the graph's placeholders include lifted module parameters: run every pool entry once
+    # through the public API and keep the placeholder tuples the plan actually received
+    plan.record_inputs = True
+    placeholder_pool = []
+    with torch.no_grad():
+        for inp in dev_pool:
+            compiled(*inp)
+            placeholder_pool.append(plan.last_inputs)
+    plan.record_inputs = False
+    torch.cuda.synchronize()
+    dev_pool = placeholder_pool
 
     # One CUDA graph per pool slot (one step each) and one "sequence" graph holding SEQ steps
     # that walk the pool: K timed steps = K // SEQ sequence replays + K % SEQ single replays.
@@ -342,6 +357,14 @@ def gpu_arm(args, wl: Workload):
 
     # ---- e2e: public API, host tensors in pinned memory, H2D + kernels + D2H every step
     e2e_steps = max(3, min(args.steps, 200 if batch_bytes < (1 << 28) else 20))
+    if wl.module is not None:
+        # the reference's convention: model and inputs live on the host; the callable keeps
+        # device copies of the parameters and stages the activations every call
+        import copy
+
+        host_module = copy.deepcopy(wl.module).cpu()
+        torch._dynamo.reset()
+        compiled = torch.compile(host_module, backend="gcu")
     with torch.no_grad():
         for i in range(3):
             out = compiled(*pinned_pool[i % 2])

@@ -35,7 +35,12 @@ class Callable:
         self._executor = None
         self._const_cache: dict[tuple, torch.Tensor] = {}
         self._pinned: dict[int, torch.Tensor] = {}
+        self._param_cache: dict[tuple, tuple] = {}
         self.calls = 0
+        # when set, every call stores the placeholder tensors it ran on (graph capture needs the
+        # full list, including module parameters Dynamo lifted into placeholders)
+        self.record_inputs = False
+        self.last_inputs: Optional[tuple] = None
 
     # ------------------------------------------------------------------ helpers
     def _exec(self):
@@ -65,6 +70,16 @@ class Callable:
     def _stage_in(self, idx: int, t: torch.Tensor, device) -> torch.Tensor:
         """Host -> device through a reusable pinned buffer (pageable tensors) or directly
         (already pinned)."""
+        if isinstance(t, torch.nn.Parameter):
+            # module parameters Dynamo lifted into placeholders: keep a device copy until the
+            # parameter is modified in place (its version counter moves) or replaced
+            key = (idx, device)
+            hit = self._param_cache.get(key)
+            if hit is not None and hit[0] is t and hit[1] == t._version:
+                return hit[2]
+            dev_t = t.detach().to(device).contiguous()
+            self._param_cache[key] = (t, t._version, dev_t)
+            return dev_t
         if t.is_pinned():
             return t.to(device, non_blocking=True)
         t = t.contiguous()
@@ -107,6 +122,8 @@ class Callable:
                 torch.cuda.current_stream(device).synchronize()
                 outputs = host
         self.calls += 1
+        if self.record_inputs:
+            self.last_inputs = tuple(env[b] for b in dag.inputs)
         return tuple(outputs)
 
     def _run_plan(self, env: dict, device) -> list:
