@@ -36,6 +36,8 @@ SYMBOLS = {
     "cdr_execute_host": (_c.c_int, [_c.c_int, _TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,
                                     _c.c_int]),
     "cdr_release_host_arena": (_c.c_int, [_c.c_int]),
+    "cdr_full_reduce_noalloc": (_c.c_int, [_TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,
+                                           _c.c_void_p]),
 }
 
 

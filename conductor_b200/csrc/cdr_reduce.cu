@@ -531,3 +531,78 @@ int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
 }
 
 }  // namespace cdr
+
+// =====================================================================================
+// cdr_full_reduce_noalloc: the full reduction for callers that must not allocate.
+//
+// Some hosts cannot call cudaMalloc on the hot path: an inference server or another
+// framework's memory pool that reserved all of HBM at start-up (so a driver allocation would
+// fail, or is forbidden by the host's policy), and latency-critical loops that cannot absorb
+// the device-wide synchronisation an allocation implies.  For them the scratch the full
+// reduction needs (one ticket counter plus one fp32 partial per CTA) lives in a fixed array
+// inside this library's device image instead of in a caller-provided workspace.
+//
+//  * Capacity: kStaticPartials partial sums, i.e. kStaticScratchBytes = 256 + 4*1024 = 4352
+//    bytes, held by every GPU that loads the library until the process exits.  The reduction
+//    uses 4 CTAs per SM, so this covers devices with up to 256 SMs; a launch that would need
+//    more slots is rejected with CDR_ERR_UNSUPPORTED and a message naming both numbers.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress)
+//    and caches it; make that first call before starting any stream capture.
+//  * All calls on a device share the array.  The ticket is cleared at the start of every
+//    call; partials are overwritten.  Two calls whose kernels overlap on the GPU (different
+//    streams, no ordering between them) race on it: serialise them.
+//  * No cudaMalloc, cudaFree or allocating library call happens in here.
+// =====================================================================================
+namespace cdr {
+namespace {
+
+constexpr int kStaticPartials = 1024;
+constexpr size_t kStaticScratchBytes = 256 + sizeof(float) * kStaticPartials;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+void* g_static_scratch_ptr[64] = {nullptr};
+
+// Device address of the scratch array on the current device (looked up once per device).
+int static_scratch_address(void** out) {
+  int dev = 0;
+  CDR_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { set_error("full_reduce_noalloc: device %d out of range", dev); return CDR_ERR_BAD_ARG; }
+  if (!g_static_scratch_ptr[dev]) {
+    void* p = nullptr;
+    CDR_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return CDR_OK;
+}
+
+}  // namespace
+}  // namespace cdr
+
+extern "C" CDR_API int cdr_full_reduce_noalloc(const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,
+                                               int n_outputs, const void* params, size_t params_bytes,
+                                               void* cuda_stream) {
+  using namespace cdr;
+  if (n_inputs < 0 || n_outputs < 0 || (n_inputs > 0 && !inputs) || (n_outputs > 0 && !outputs)) {
+    set_error("full_reduce_noalloc: tensor list is null or has a negative count");
+    return CDR_ERR_BAD_ARG;
+  }
+  if (!params || params_bytes != sizeof(cdr_reduce_params)) {
+    set_error("full_reduce_noalloc: expects a %zu-byte cdr_reduce_params block", sizeof(cdr_reduce_params));
+    return CDR_ERR_BAD_ARG;
+  }
+  size_t need = 0;
+  full_reduce_workspace(inputs, n_inputs, &need);
+  if (need > kStaticScratchBytes) {
+    set_error("full_reduce_noalloc: this device needs %zu bytes of scratch (%zu partial sums), the built-in array "
+              "holds %zu bytes (%d partial sums); use cdr_launch with a caller workspace instead",
+              need, (need - 256) / sizeof(float), kStaticScratchBytes, kStaticPartials);
+    return CDR_ERR_UNSUPPORTED;
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  return launch_full_reduce(inputs, n_inputs, outputs, n_outputs, static_cast<const cdr_reduce_params*>(params),
+                            scratch, kStaticScratchBytes, static_cast<cudaStream_t>(cuda_stream));
+}

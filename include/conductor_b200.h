@@ -230,6 +230,26 @@ CDR_API int cdr_execute_host(int template_id, const cdr_tensor* host_inputs, int
  * Replaces GCUKernelExecutor.unload_kernel (conductor/compiler/executor.py:64-90). */
 CDR_API int cdr_release_host_arena(int device);
 
+/* CDR_T_FULL_REDUCE without a caller workspace and without any allocation.  (No counterpart
+ * in the reference: it has no allocation-free calling mode.)
+ *
+ * For hosts that cannot call cudaMalloc while running: servers or framework pools that
+ * reserved all device memory up front, and loops that cannot afford the device-wide
+ * synchronisation an allocation brings.  The scratch the reduction needs (a ticket counter and
+ * one fp32 partial per CTA) is a fixed array inside the library's device image: 4352 bytes =
+ * 256 + 4 * 1024 partial sums, resident on every GPU that loads the library until exit.  The
+ * reduction runs 4 CTAs per SM, so devices with up to 256 SMs fit; otherwise the call returns
+ * CDR_ERR_UNSUPPORTED and cdr_last_error() names the needed and available sizes.
+ *
+ * inputs / outputs / params are exactly those of cdr_launch(CDR_T_FULL_REDUCE, ...); the
+ * caller still owns them.  The first call on a device resolves the array's device address and
+ * should therefore be made before any stream capture begins.  Every call on a device shares the
+ * one array: the ticket is cleared at the start of each call, and calls whose kernels could
+ * overlap on the GPU (different streams without ordering) race and must be serialised. */
+CDR_API int cdr_full_reduce_noalloc(const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,
+                                    int n_outputs, const void* params, size_t params_bytes,
+                                    void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
