@@ -243,6 +243,23 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int is_bf16, int64_t 
   return CDR_OK;
 }
 
+// Row-major 3-D tensor [d2, d1, d0] (d0 contiguous) of 16-bit elements, box = box0 x box1 x 1,
+// 128-byte swizzle; rows beyond d1 read as zeros.
+int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t d0, int64_t d1, int64_t d2,
+                       int box0, int box1) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return CDR_ERR_CUDA; }
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d0), static_cast<cuuint64_t>(d1), static_cast<cuuint64_t>(d2)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(d0) * 2, static_cast<cuuint64_t>(d0) * d1 * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(box0), static_cast<cuuint32_t>(box1), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (3-D) failed with %d", static_cast<int>(r)); return CDR_ERR_CUDA; }
+  return CDR_OK;
+}
+
 int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                          const cdr_gemm_params* p, cudaStream_t stream) {
   if (!p) { set_error("gemm_epilogue: params is null"); return CDR_ERR_BAD_ARG; }
