@@ -75,7 +75,7 @@ def main(ref_root: str) -> None:
     (xm,) = rp.inputs_mlp(32, 64, seed=4)
     cases["c4_mlp"] = dict(x=xm, w1=mlp[0].weight.detach(), b1=mlp[0].bias.detach(), w2=mlp[2].weight.detach(),
                            b2=mlp[2].bias.detach(), out=run(mlp, [xm]))
-    q, k, v = rp.inputs_attention(1, 2, 64, 32, seed=5)
+    q, k, v = rp.inputs_attention(1, 2, 96, 64, seed=5)
     cases["c5_attention"] = dict(q=q, k=k, v=v, out=run(rp.causal_attention, [q, k, v]))
     for name, tensors in cases.items():
         np.savez_compressed(HERE / f"{name}.npz", **{k: bits(t) for k, t in tensors.items()})
