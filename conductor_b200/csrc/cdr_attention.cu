@@ -5,15 +5,18 @@
 // choreo-op/flashattention-gcu-only-test.co:75-122 (d_i = d_prev*e^(m_prev-m) + e^(s-m)); the
 // executed path is eager torch.nn.functional.scaled_dot_product_attention in bf16.
 //
-// Tensor-core bound.  One CTA per (batch*head, 128-query tile); key/value blocks of 128:
-//   warp 0     TMA producer: Q once, then K_j and V_j into two-stage rings (128-byte swizzle)
-//   warp 1     MMA issuer: S_j = Q K_j^T (tcgen05.mma, fp32 in TMEM, double buffered so that
-//              S_{j+1} is computed while the softmax of block j runs) and O += P_j V_j
-//   warps 2-5  softmax: one query row per thread; tcgen05.ld the S row, running max / sum in the
-//              log2 domain, P_j = exp2(..) rounded to bf16 and written to shared memory in the
-//              swizzled K-major layout the second MMA reads; the O accumulator stays in TMEM
-//              and is rescaled (tcgen05.ld/st) only when the running max grew by more than 2^8,
-//              which keeps P within bf16 range and is exact after the final division by the sum
+// Tensor-core bound.  One CTA per (batch*head, 256-query tile), handled as two 128-row halves
+// A and B that share every K/V block (halving operand traffic per flop) and ping-pong on the
+// tensor core: while the softmax warps of one half work, the MMAs of the other half run.
+//   warp 0      TMA producer: both Q halves once, then K_j and V_j into two-stage rings
+//   warp 1      MMA issuer:  S_h = Q_h K_j^T (fp32 in TMEM) and O_h += P_h V_j, where P_h is
+//               read straight from TMEM (it overwrites the S_h columns as packed bf16)
+//   warps 2-5   softmax of half A, warps 6-9 of half B: one query row per thread; tcgen05.ld
+//               the S row, running max / sum in the log2 domain, P = exp2(..) stored back to
+//               TMEM with tcgen05.st; the O accumulator stays in TMEM and is rescaled only when
+//               the running max grew by more than 2^8 (exact after the final division)
+// TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511.  MMAs of one CTA execute in
+// issue order, so reusing the S_h columns for S_h(j+1) after P_h(j) needs no extra barrier.
 // Causal work is triangular, so CTAs are numbered heaviest tile first.  No load is multicast;
 // every wait is bounded and reports through the device status word.
 #include <cuda.h>
@@ -29,9 +32,9 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t 
 
 namespace {
 
-constexpr int BQ = 128, BKV = 128;
-constexpr int ATT_THREADS = 192;
-constexpr int TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, ATT_TMEM_COLS = 512;
+constexpr int BQ = 256, BH_ROWS = 128, BKV = 128;   // query tile, rows per half, keys per block
+constexpr int ATT_THREADS = 320;
+constexpr int TMEM_S = 0, TMEM_O = 256, ATT_TMEM_COLS = 512;   // + 128 * half
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnArgs {
@@ -45,19 +48,30 @@ struct AttnArgs {
 
 template <int HD>
 struct AttnSmem {
-  static constexpr int TILE_BYTES = 128 * HD * 2;      // Q, K or V tile
-  static constexpr int P_BYTES = BQ * BKV * 2;
-  static constexpr int Q_OFF = 0;
-  static constexpr int K_OFF = TILE_BYTES;             // 2 stages
+  static constexpr int TILE_BYTES = 128 * HD * 2;      // one Q half, K block or V block
+  static constexpr int Q_OFF = 0;                      // 2 halves
+  static constexpr int K_OFF = 2 * TILE_BYTES;         // 2 stages
   static constexpr int V_OFF = K_OFF + 2 * TILE_BYTES; // 2 stages
-  static constexpr int P_OFF = V_OFF + 2 * TILE_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int BAR_OFF = V_OFF + 2 * TILE_BYTES;
   static constexpr size_t TOTAL = BAR_OFF + 256 + 1024;
 };
 
-// barrier indices inside the barrier block
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SEMPTY = 11, B_PFULL = 13,
-       B_PVDONE = 14, B_COUNT = 15 };
+// barrier indices; the [2] ones are indexed by ring stage or by half
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13,
+       B_COUNT = 15 };
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b) {
+  if (BF16) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
+  __half2 t = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
 
 template <int HD, bool BF16>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
@@ -73,20 +87,23 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   const int bh = static_cast<int>(blockIdx.x) % a.BH;
   const int q0 = q_tile * BQ;
   const int kv_total = (a.S + BKV - 1) / BKV;
-  int n_blocks = kv_total;
-  if (a.causal) {
-    const int lim = (q0 + BQ + BKV - 1) / BKV;
-    n_blocks = lim < kv_total ? lim : kv_total;
+  // key blocks each half attends to
+  int nblk[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row0 = q0 + h * BH_ROWS;
+    if (row0 >= a.S) nblk[h] = 0;
+    else if (a.causal) { const int lim = row0 / BKV + 1; nblk[h] = lim < kv_total ? lim : kv_total; }
+    else nblk[h] = kv_total;
   }
+  const int n_iter = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
 
   if (warp == 0 && lane == 0) {
     sm100::prefetch_tensormap(&a.tmap_q);
     sm100::prefetch_tensormap(&a.tmap_k);
     sm100::prefetch_tensormap(&a.tmap_v);
-    for (int i = 0; i < B_COUNT; ++i) {
-      const bool four = (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL);  // one arrival per softmax warp
-      sm100::mbar_init(&bars[i], four ? 4 : 1);
-    }
+    for (int i = 0; i < B_COUNT; ++i)
+      sm100::mbar_init(&bars[i], (i == B_PFULL || i == B_PFULL + 1) ? 4 : 1);  // P: one arrival per softmax warp
     sm100::fence_barrier_init();
   }
   if (warp == 1) {
@@ -101,187 +118,192 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      sm100::mbar_arrive_expect_tx(&bars[B_QFULL], L::TILE_BYTES);
+      const int active = (nblk[0] > 0) + (nblk[1] > 0);
+      sm100::mbar_arrive_expect_tx(&bars[B_QFULL], active * L::TILE_BYTES);
+      for (int h = 0; h < 2; ++h)
+        if (nblk[h] > 0)
 #pragma unroll
-      for (int h = 0; h < HD / 64; ++h)
-        sm100::tma_load_3d(smem + L::Q_OFF + h * (128 * 128), &a.tmap_q, h * 64, q0, bh, &bars[B_QFULL]);
-      for (int j = 0; j < n_blocks; ++j) {
+          for (int d = 0; d < HD / 64; ++d)
+            sm100::tma_load_3d(smem + L::Q_OFF + h * L::TILE_BYTES + d * (128 * 128), &a.tmap_q, d * 64,
+                               q0 + h * BH_ROWS, bh, &bars[B_QFULL]);
+      for (int j = 0; j < n_iter; ++j) {
         const int st = j & 1, use = j >> 1;
         if (use > 0 && !sm100::mbar_wait(&bars[B_KEMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 20); break; }
         sm100::mbar_arrive_expect_tx(&bars[B_KFULL + st], L::TILE_BYTES);
 #pragma unroll
-        for (int h = 0; h < HD / 64; ++h)
-          sm100::tma_load_3d(smem + L::K_OFF + st * L::TILE_BYTES + h * (128 * 128), &a.tmap_k, h * 64, j * BKV, bh,
+        for (int d = 0; d < HD / 64; ++d)
+          sm100::tma_load_3d(smem + L::K_OFF + st * L::TILE_BYTES + d * (128 * 128), &a.tmap_k, d * 64, j * BKV, bh,
                              &bars[B_KFULL + st]);
         if (use > 0 && !sm100::mbar_wait(&bars[B_VEMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 21); break; }
         sm100::mbar_arrive_expect_tx(&bars[B_VFULL + st], L::TILE_BYTES);
 #pragma unroll
-        for (int h = 0; h < HD / 64; ++h)
-          sm100::tma_load_3d(smem + L::V_OFF + st * L::TILE_BYTES + h * (128 * 128), &a.tmap_v, h * 64, j * BKV, bh,
+        for (int d = 0; d < HD / 64; ++d)
+          sm100::tma_load_3d(smem + L::V_OFF + st * L::TILE_BYTES + d * (128 * 128), &a.tmap_v, d * 64, j * BKV, bh,
                              &bars[B_VFULL + st]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = sm100::umma_idesc_f16(BQ, BKV, BF16, false, false);
-      constexpr uint32_t idesc_o = sm100::umma_idesc_f16(BQ, HD, BF16, false, true);  // V is MN-major
-      const uint32_t q_addr = sm100::smem_u32(smem + L::Q_OFF);
-      const uint32_t p_addr = sm100::smem_u32(smem + L::P_OFF);
+      constexpr uint32_t idesc_s = sm100::umma_idesc_f16(BH_ROWS, BKV, BF16, false, false);
+      constexpr uint32_t idesc_o = sm100::umma_idesc_f16(BH_ROWS, HD, BF16, false, true);  // V is MN-major
       bool ok = sm100::mbar_wait(&bars[B_QFULL], 0);
       if (!ok) sm100::report_timeout(a.status, 22);
 
-      auto issue_s = [&](int j) -> bool {
-        const int st = j & 1, use = j >> 1;
-        if (!sm100::mbar_wait(&bars[B_KFULL + st], use & 1)) { sm100::report_timeout(a.status, 23); return false; }
-        if (use > 0 && !sm100::mbar_wait(&bars[B_SEMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 24); return false; }
-        sm100::tc_fence_after();
-        const uint32_t k_addr = sm100::smem_u32(smem + L::K_OFF + st * L::TILE_BYTES);
-        const uint32_t d = tmem_base + (st ? TMEM_S1 : TMEM_S0);
+      // S_h(j) = Q_h K_j^T; the caller has already waited for K_j
+      auto issue_s = [&](int h, int j) {
+        const uint32_t q_addr = sm100::smem_u32(smem + L::Q_OFF + h * L::TILE_BYTES);
+        const uint32_t k_addr = sm100::smem_u32(smem + L::K_OFF + (j & 1) * L::TILE_BYTES);
+        const uint32_t d = tmem_base + TMEM_S + h * 128;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * (128 * 128) + (kk % 4) * 32;
           sm100::umma_f16_ss(d, sm100::umma_desc_k_sw128(q_addr + off), sm100::umma_desc_k_sw128(k_addr + off), idesc_s,
                              kk > 0 ? 1u : 0u);
         }
-        sm100::umma_commit(&bars[B_KEMPTY + st]);
-        sm100::umma_commit(&bars[B_SFULL + st]);
-        return true;
+        sm100::umma_commit(&bars[B_SFULL + h]);
       };
 
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks) { ok = issue_s(j + 1); if (!ok) break; }
-        const int st = j & 1, use = j >> 1;
-        if (!sm100::mbar_wait(&bars[B_VFULL + st], use & 1)) { sm100::report_timeout(a.status, 25); break; }
-        if (!sm100::mbar_wait(&bars[B_PFULL], j & 1)) { sm100::report_timeout(a.status, 26); break; }
+      if (ok && n_iter > 0) {
+        ok = sm100::mbar_wait(&bars[B_KFULL + 0], 0);
+        if (!ok) sm100::report_timeout(a.status, 23);
+      }
+      if (ok && n_iter > 0) {
         sm100::tc_fence_after();
+        for (int h = 0; h < 2; ++h)
+          if (nblk[h] > 0) issue_s(h, 0);
+        sm100::umma_commit(&bars[B_KEMPTY + 0]);
+      }
+      for (int j = 0; j < n_iter && ok; ++j) {
+        const int st = j & 1, use = j >> 1;
+        const bool next = j + 1 < n_iter;
+        if (!sm100::mbar_wait(&bars[B_VFULL + st], use & 1)) { sm100::report_timeout(a.status, 25); break; }
+        if (next && !sm100::mbar_wait(&bars[B_KFULL + ((j + 1) & 1)], ((j + 1) >> 1) & 1)) { sm100::report_timeout(a.status, 24); break; }
         const uint32_t v_addr = sm100::smem_u32(smem + L::V_OFF + st * L::TILE_BYTES);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (j < nblk[h]) {
+            if (!sm100::mbar_wait(&bars[B_PFULL + h], j & 1)) { sm100::report_timeout(a.status, 26); ok = false; break; }
+            sm100::tc_fence_after();
+            const uint32_t p_tmem = tmem_base + TMEM_S + h * 128;   // packed bf16 pairs: 8 columns per 16 keys
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint32_t p_off = (kk / 4) * (128 * 128) + (kk % 4) * 32;
-          const uint64_t pdesc = sm100::umma_desc_k_sw128(p_addr + p_off);
-          const uint64_t vdesc = sm100::umma_desc_mn_sw128(v_addr + kk * (16 * 128), 128 * 128);
-          sm100::umma_f16_ss(tmem_base + TMEM_O, pdesc, vdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < BKV / 16; ++kk) {
+              const uint64_t vdesc = sm100::umma_desc_mn_sw128(v_addr + kk * (16 * 128), 128 * 128);
+              sm100::umma_f16_ts(tmem_base + TMEM_O + h * 128, p_tmem + kk * 8, vdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            sm100::umma_commit(&bars[B_PVDONE + h]);
+          }
+          if (next && j + 1 < nblk[h]) issue_s(h, j + 1);
         }
+        if (!ok) break;
         sm100::umma_commit(&bars[B_VEMPTY + st]);
-        sm100::umma_commit(&bars[B_PVDONE]);
+        if (next) sm100::umma_commit(&bars[B_KEMPTY + ((j + 1) & 1)]);
       }
     }
   } else {
     // ------------------------------------------------------------ softmax / correction / epilogue
-    const int q = warp & 3;
-    const int row_in_tile = q * 32 + lane;
-    const int row = q0 + row_in_tile;
+    const int g = (warp - 2) >> 2;       // half this warp group serves
+    const int q = warp & 3;              // TMEM lane quadrant
+    const int n_my = nblk[g];
+    const int row_in_half = q * 32 + lane;
+    const int row = q0 + g * BH_ROWS + row_in_half;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
-    unsigned char* p_smem = smem + L::P_OFF;
-    float m_ref = -INFINITY, l_sum = 0.0f;
+    const uint32_t s_taddr = tmem_base + TMEM_S + g * 128 + lane_sel;
+    const uint32_t o_taddr = tmem_base + TMEM_O + g * 128 + lane_sel;
+    float m_ref = -INFINITY, l0 = 0.0f, l1 = 0.0f;
     bool ok = true;
 
-    for (int j = 0; j < n_blocks; ++j) {
-      const int st = j & 1, use = j >> 1;
-      if (!sm100::mbar_wait(&bars[B_SFULL + st], use & 1)) { sm100::report_timeout(a.status, 27); ok = false; break; }
+    for (int j = 0; j < n_my; ++j) {
+      if (!sm100::mbar_wait(&bars[B_SFULL + g], j & 1)) { sm100::report_timeout(a.status, 27); ok = false; break; }
       sm100::tc_fence_after();
       uint32_t sr[4][32];
-      const uint32_t s_addr = tmem_base + (st ? TMEM_S1 : TMEM_S0) + lane_sel;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) sm100::tmem_ld32(s_addr + c * 32, sr[c]);
+      for (int c = 0; c < 4; ++c) sm100::tmem_ld32(s_taddr + c * 32, sr[c]);
       sm100::tmem_ld_wait();
-      sm100::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&bars[B_SEMPTY + st]);  // this S buffer may be overwritten
 
       const int key0 = j * BKV;
-      const bool need_mask = (a.causal && key0 + BKV - 1 > q0) || (key0 + BKV > a.S);
+      const bool need_mask = (a.causal && key0 + BKV - 1 > q0 + g * BH_ROWS) || (key0 + BKV > a.S);
       float bmax = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(sr[c][i]);
-          if (need_mask) {
+          for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
+            float v = __uint_as_float(sr[c][i]);
             if (key >= a.S || (a.causal && key > row)) v = -INFINITY;
             sr[c][i] = __float_as_uint(v);
+            bmax = fmaxf(bmax, v);
           }
-          bmax = fmaxf(bmax, v);
-        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, __uint_as_float(sr[c][i]));
+      }
       bmax *= a.scale_log2;  // scale > 0: max commutes with the scaling
 
-      // block j-1's P V must be complete before O is touched or the P buffer rewritten
-      if (j > 0 && !sm100::mbar_wait(&bars[B_PVDONE], (j - 1) & 1)) { sm100::report_timeout(a.status, 28); ok = false; break; }
-      sm100::tc_fence_after();
-
+      // S_h(j) was issued after P_h(j-1) V_(j-1), and MMAs complete in order: O_h is stable here
       if (j == 0) {
         m_ref = bmax;
       } else if (__any_sync(0xffffffffu, bmax > m_ref + kRescaleThreshold)) {
         const float m_new = fmaxf(m_ref, bmax);
-        const float alpha = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - m_new);
-        l_sum *= alpha;
+        const float alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
+        l0 *= alpha;
+        l1 *= alpha;
         m_ref = m_new;
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
-          sm100::tmem_ld32(tmem_base + TMEM_O + lane_sel + c * 32, o);
+          sm100::tmem_ld32(o_taddr + c * 32, o);
           sm100::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          sm100::tmem_st32(tmem_base + TMEM_O + lane_sel + c * 32, o);
+          sm100::tmem_st32(o_taddr + c * 32, o);
         }
-        sm100::tmem_st_wait();
       }
 
-      // P = exp2(s*c - m), bf16, written as the K-major swizzled A operand of the second MMA
+      // P = exp2(s*c - m) as packed 16-bit pairs, stored over the S columns this row just read
       const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        uint32_t pw[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t w[4];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sr[c][g * 8 + h * 2]), a.scale_log2, neg_m));
-            const float p1 = exp2f(fmaf(__uint_as_float(sr[c][g * 8 + h * 2 + 1]), a.scale_log2, neg_m));
-            l_sum += p0 + p1;
-            if (BF16) { __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1); w[h] = *reinterpret_cast<uint32_t*>(&t); }
-            else { __half2 t = __floats2half2_rn(p0, p1); w[h] = *reinterpret_cast<uint32_t*>(&t); }
-          }
-          const int key = c * 32 + g * 8;                 // first of 8 keys in this 16-byte chunk
-          const int half = key >> 6, chunk = (key & 63) >> 3;
-          unsigned char* dst = p_smem + half * (128 * 128) + row_in_tile * 128 + ((chunk ^ (row_in_tile & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i]), a.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i + 1]), a.scale_log2, neg_m));
+          l0 += p0;
+          l1 += p1;
+          pw[i] = pack_pair<BF16>(p0, p1);
         }
+        sm100::tmem_st16(s_taddr + c * 16, pw);
       }
-      sm100::fence_proxy_async_smem();   // generic-proxy writes of P -> visible to the MMA (async proxy)
+      sm100::tmem_st_wait();
       sm100::tc_fence_before();
       __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&bars[B_PFULL]);
+      if (lane == 0) sm100::mbar_arrive(&bars[B_PFULL + g]);
     }
 
     // ---- epilogue: O / l, rounded to the output type
-    if (ok && n_blocks > 0) {
-      if (!sm100::mbar_wait(&bars[B_PVDONE], (n_blocks - 1) & 1)) { sm100::report_timeout(a.status, 29); ok = false; }
+    if (ok && n_my > 0) {
+      if (!sm100::mbar_wait(&bars[B_PVDONE + g], (n_my - 1) & 1)) { sm100::report_timeout(a.status, 29); ok = false; }
     }
-    if (ok) {
+    if (ok && n_my > 0) {
       sm100::tc_fence_after();
-      const float inv = 1.0f / l_sum;
+      const float inv = 1.0f / (l0 + l1);
       unsigned char* orow = static_cast<unsigned char*>(a.out) + (static_cast<size_t>(bh) * a.S + row) * (HD * 2);
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
-        sm100::tmem_ld32(tmem_base + TMEM_O + lane_sel + c * 32, o);
+        sm100::tmem_ld32(o_taddr + c * 32, o);
         sm100::tmem_ld_wait();
         if (row < a.S) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int gq = 0; gq < 4; ++gq) {
             uint32_t w[4];
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const float x0 = __uint_as_float(o[g * 8 + h * 2]) * inv, x1 = __uint_as_float(o[g * 8 + h * 2 + 1]) * inv;
-              if (BF16) { __nv_bfloat162 t = __floats2bfloat162_rn(x0, x1); w[h] = *reinterpret_cast<uint32_t*>(&t); }
-              else { __half2 t = __floats2half2_rn(x0, x1); w[h] = *reinterpret_cast<uint32_t*>(&t); }
-            }
-            *reinterpret_cast<uint4*>(orow + c * 64 + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int t = 0; t < 4; ++t)
+              w[t] = pack_pair<BF16>(__uint_as_float(o[gq * 8 + t * 2]) * inv, __uint_as_float(o[gq * 8 + t * 2 + 1]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 64 + gq * 16) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
@@ -297,7 +319,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
 }
 
 }  // namespace
-
 // ---------------------------------------------------------------- host side
 int attention_workspace(const cdr_tensor*, int, size_t* bytes) {
   *bytes = 0;  // O, the running max and the running sum never leave TMEM / registers
