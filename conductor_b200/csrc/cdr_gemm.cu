@@ -208,6 +208,169 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
   }
 }
 
+// ---------------------------------------------------------------- CTA-pair variant
+// Two CTAs of a cluster (one TPC) share a 256 x 256 output tile: each owns 128 of its rows
+// (its own accumulator in its own TMEM) and stages 128 rows of x plus HALF of the weight tile;
+// tcgen05.mma.cta_group::2 reads both halves, so every SM fetches 32 KB per k-block instead of
+// 48 KB for the same math -- operand bandwidth from L2, not the tensor pipe, limited the 1-CTA
+// form.  The even CTA of the pair issues the MMAs; completion is multicast to both CTAs'
+// barriers; each CTA loads its own tiles (no multicast load).
+constexpr int P_BM = 256, P_BN = 256;                 // pair tile
+constexpr int P_A_BYTES = 128 * BK * 2;               // per CTA: 128 rows of x
+constexpr int P_B_BYTES = 128 * BK * 2;               // per CTA: 128 of the 256 weight rows
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KB
+constexpr int P_STAGES = 6;
+constexpr size_t P_SMEM_BYTES = static_cast<size_t>(P_STAGES) * P_STAGE_BYTES + 1024 + 256;
+
+template <bool BF16>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(const __grid_constant__ GemmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint64_t* empty = full + P_STAGES;
+  uint64_t* acc_full = empty + P_STAGES;
+  uint64_t* acc_empty = acc_full + ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = sm100::cluster_ctarank();     // 0 = leader (issues MMAs), 1 = peer
+  const int pair = static_cast<int>(blockIdx.x >> 1), n_pairs = static_cast<int>(gridDim.x >> 1);
+
+  if (warp == 0 && lane == 0) {
+    sm100::prefetch_tensormap(&a.tmap_a);
+    sm100::prefetch_tensormap(&a.tmap_b);
+    for (int s = 0; s < P_STAGES; ++s) {
+      sm100::mbar_init(&full[s], 1);    // used in the leader only: its producer's arrive.expect_tx
+      sm100::mbar_init(&empty[s], 1);   // one multicast commit per phase, in both CTAs
+    }
+    for (int s = 0; s < ACC_STAGES; ++s) {
+      sm100::mbar_init(&acc_full[s], 1);   // multicast commit, both CTAs
+      sm100::mbar_init(&acc_empty[s], 8);  // leader only: 4 epilogue warps of each CTA
+    }
+    sm100::fence_barrier_init();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    sm100::tmem_relinquish_pair();
+  }
+  sm100::tc_fence_before();
+  sm100::cluster_sync_all();   // both CTAs' barriers exist before anything signals them remotely
+  sm100::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = a.tiles_m * a.tiles_n;       // 256 x 256 tiles
+  const int kblocks = (a.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        const int m0 = (tile % a.tiles_m) * P_BM + static_cast<int>(rank) * 128;
+        const int n0 = (tile / a.tiles_m) * P_BN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1;
+          if (!sm100::mbar_wait(&empty[s], ph ^ 1)) { sm100::report_timeout(a.status, 30); ok = false; break; }
+          if (rank == 0) sm100::mbar_arrive_expect_tx(&full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
+          unsigned char* st = smem + s * P_STAGE_BYTES;
+          sm100::tma_load_2d_pair(st, &a.tmap_a, kb * BK, m0, &full[s]);
+          sm100::tma_load_2d_pair(st + P_A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = sm100::umma_idesc_f16(P_BM, P_BN, BF16, false, false);
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++tile_iter) {
+        const uint32_t as = tile_iter % ACC_STAGES, aph = (tile_iter / ACC_STAGES) & 1;
+        if (!sm100::mbar_wait(&acc_empty[as], aph ^ 1)) { sm100::report_timeout(a.status, 31); break; }
+        sm100::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1;
+          if (!sm100::mbar_wait(&full[s], ph)) { sm100::report_timeout(a.status, 32); ok = false; break; }
+          sm100::tc_fence_after();
+          const uint32_t a_addr = sm100::smem_u32(smem + s * P_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + P_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
+            const uint64_t bdesc = sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
+            sm100::umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          sm100::umma_commit_pair(&empty[s], 3);   // frees the stage in both CTAs
+        }
+        if (ok) sm100::umma_commit_pair(&acc_full[as], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    uint32_t tile_iter = 0;
+    const bool vec_ok = (a.N % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+    const uint32_t leader_acc_empty = sm100::mapa_u32(sm100::smem_u32(&acc_empty[0]), 0);
+    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++tile_iter) {
+      const int m0 = (tile % a.tiles_m) * P_BM + static_cast<int>(rank) * 128, n0 = (tile / a.tiles_m) * P_BN;
+      const uint32_t as = tile_iter % ACC_STAGES, aph = (tile_iter / ACC_STAGES) & 1;
+      if (!sm100::mbar_wait(&acc_full[as], aph)) { sm100::report_timeout(a.status, 33); break; }
+      sm100::tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_base = tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        sm100::tmem_ld32(t_base + c * 32, r);
+        sm100::tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < a.M && col0 < a.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(r[j]);
+            if (a.bias != nullptr && col0 + j < a.N) x += load_elem<BF16>(a.bias, col0 + j);
+            v[j] = x;
+          }
+          const size_t off = static_cast<size_t>(row) * a.N + col0;
+          if (vec_ok && col0 + 32 <= a.N) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + off * 2);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t w[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                float lo = v[g * 8 + h * 2], hi = v[g * 8 + h * 2 + 1];
+                if (a.relu) { lo = lo > 0.0f ? lo : (lo != lo ? lo : 0.0f); hi = hi > 0.0f ? hi : (hi != hi ? hi : 0.0f); }
+                w[h] = pack2<BF16>(lo, hi);
+              }
+              dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < a.N; ++j) {
+              float x = v[j];
+              if (a.relu) x = x > 0.0f ? x : (x != x ? x : 0.0f);
+              store_elem<BF16>(a.out, off + j, x);
+            }
+          }
+        }
+      }
+      sm100::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive_remote(leader_acc_empty + as * 8);   // the leader's barrier, from either CTA
+    }
+  }
+
+  sm100::tc_fence_before();
+  sm100::cluster_sync_all();   // neither CTA leaves while its peer may still signal it
+  if (warp == 1) {
+    sm100::tc_fence_after();
+    sm100::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -305,24 +468,54 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
   a.relu = p->activation == CDR_ACT_RELU;
   a.is_bf16 = dt == CDR_BF16;
-  a.tiles_m = static_cast<int>((M + BM - 1) / BM);
-  a.tiles_n = static_cast<int>((N + BN - 1) / BN);
   a.status = device_status_ptr();
-  const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
-  int grid = sm_count();
-  if (grid > tiles) grid = static_cast<int>(tiles);
-
-  static bool configured_dev[64] = {false};
   int dev = 0;
   CDR_CUDA_TRY(cudaGetDevice(&dev));
+  static bool configured_dev[64] = {false};
   bool& configured = configured_dev[dev & 63];
   if (!configured) {
     CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(SMEM_BYTES)));
     CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(SMEM_BYTES)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(P_SMEM_BYTES)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(P_SMEM_BYTES)));
     configured = true;
   }
+
+  if (M >= P_BM && N >= P_BN) {
+    // CTA-pair kernel: 256 x 256 tiles, clusters of two CTAs, at most one cluster per TPC.
+    // Each CTA stages only 128 of the tile's 256 weight rows: the W box is 64 x 128 here.
+    if (int rc = make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, 128, BK)) return rc;
+    a.tiles_m = static_cast<int>((M + P_BM - 1) / P_BM);
+    a.tiles_n = static_cast<int>((N + P_BN - 1) / P_BN);
+    const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
+    int pairs = sm_count() / 2;
+    if (pairs > tiles) pairs = static_cast<int>(tiles);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (dt == CDR_BF16) CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_pair_kernel<true>, a));
+    else CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_pair_kernel<false>, a));
+    return CDR_OK;
+  }
+
+  a.tiles_m = static_cast<int>((M + BM - 1) / BM);
+  a.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
+  int grid = sm_count();
+  if (grid > tiles) grid = static_cast<int>(tiles);
   if (dt == CDR_BF16) gemm_epilogue_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a);
   else gemm_epilogue_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a);
   CDR_CUDA_TRY(cudaGetLastError());
