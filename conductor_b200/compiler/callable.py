@@ -26,12 +26,15 @@ logger = get_logger(__name__)
 
 class Callable:
     def __init__(self, artifact: CompiledArtifact, graph_module: Optional[torch.fx.GraphModule] = None,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, batch_size: Optional[int] = None):
         self.artifact = artifact
         self.graph_module = graph_module      # kept for introspection only; never executed
         self.dag = artifact.dag
         self.launches: list[KernelLaunch] = artifact.launches
         self.default_device = device
+        # when set, tensors whose leading extent equals it may arrive with fewer rows (one shard
+        # of the batch); outputs with that leading extent are sized to the rows actually given
+        self.batch_size = batch_size
         self._executor = None
         self._const_cache: dict[tuple, torch.Tensor] = {}
         self._pinned: dict[int, torch.Tensor] = {}
@@ -102,12 +105,18 @@ class Callable:
         env: dict = {}
         with torch.cuda.device(device):
             for i, (buf, t) in enumerate(zip(dag.inputs, tensors)):
-                if buf.shape is not None and tuple(t.shape) != buf.shape:
+                if buf.shape is not None and tuple(t.shape) != buf.shape and not self._is_shard(t, buf):
                     raise ExecutionError(
                         f"input {i} has shape {tuple(t.shape)}, compiled for {buf.shape}",
                         kernel_name=self.artifact.entry_point)
                 env[buf] = self._stage_in(i, t, device) if t.device.type == "cpu" else t
-            outputs = self._run_plan(env, device)
+            rows = None
+            if self.batch_size is not None:
+                for buf, t in zip(dag.inputs, tensors):
+                    if buf.shape and buf.shape[0] == self.batch_size and t.dim() > 0 and t.shape[0] != self.batch_size:
+                        rows = t.shape[0]
+                        break
+            outputs = self._run_plan(env, device, rows)
             if host_mode:
                 # device -> pinned host (blocks come from torch's caching host allocator, so a
                 # steady-state call allocates nothing), then one wait for the whole plan
@@ -126,7 +135,16 @@ class Callable:
             self.last_inputs = tuple(env[b] for b in dag.inputs)
         return tuple(outputs)
 
-    def _run_plan(self, env: dict, device) -> list:
+    def _is_shard(self, t: torch.Tensor, buf) -> bool:
+        return (self.batch_size is not None and buf.shape and buf.shape[0] == self.batch_size and t.dim() == len(buf.shape)
+                and tuple(t.shape[1:]) == buf.shape[1:] and 0 < t.shape[0] <= self.batch_size)
+
+    def _shard_shape(self, shape, rows):
+        if rows is None or not shape or shape[0] != self.batch_size:
+            return tuple(shape)
+        return (rows,) + tuple(shape[1:])
+
+    def _run_plan(self, env: dict, device, rows: Optional[int] = None) -> list:
         ex = self._exec()
         for launch in self.launches:
             ins = []
@@ -138,9 +156,13 @@ class Callable:
                     t = env[b] = self._constant_on(b, device)
                 ins.append(t)
             if launch.template == 0:                       # alias: reshape, no kernel
-                env[launch.outputs[0]] = ins[0].reshape(launch.out_shapes[0])
+                env[launch.outputs[0]] = ins[0].reshape(self._shard_shape(launch.out_shapes[0], rows))
                 continue
-            outs = ex.execute(launch, ins)
+            outs = None
+            if rows is not None:
+                outs = [torch.empty(self._shard_shape(sh, rows), dtype=dt, device=device)
+                        for sh, dt in zip(launch.out_shapes, launch.out_dtypes)]
+            outs = ex.execute(launch, ins, outs)
             for b, t in zip(launch.outputs, outs):
                 env[b] = t
         result = []

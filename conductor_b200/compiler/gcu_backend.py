@@ -36,7 +36,7 @@ class GCUBackend:
         if cfg.runtime.devices > 1:
             from .sharding import ShardedCallable
 
-            compiled_fn = ShardedCallable(artifact, graph_module, n_devices=cfg.runtime.devices)
+            compiled_fn = ShardedCallable.from_artifact(artifact, graph_module, n_devices=cfg.runtime.devices)
         else:
             compiled_fn = GCUCallable(artifact, graph_module)
         if cfg.cache.enabled:
