@@ -9,7 +9,7 @@
 //              shared-memory ring (128-byte swizzle; both operands are K-major as stored)
 //   warp 1     MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16) x4 per k-block,
 //              accumulating in tensor memory; tcgen05.commit releases the ring stage
-//   warps 2-5  epilogue: tcgen05.ld the fp32 accumulator (lane = output row), add bias, ReLU,
+//   warps 2-9  epilogue (two per TMEM lane quadrant, 128 columns each): tcgen05.ld the fp32 accumulator (lane = output row), add bias, ReLU,
 //              round to bf16, store
 // The accumulator is double buffered in TMEM (2 x 256 columns), so the epilogue of tile i runs
 // under the MMAs of tile i+1.  Tiles are walked M-fastest so that concurrently running CTAs
@@ -29,7 +29,9 @@ constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = ACC_STAGES * BN;  // 512: all of tensor memory
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;              // two per TMEM lane quadrant, 128 accumulator columns each
+constexpr int EPI_CHUNKS = BN / 32 / 2;   // 32-column chunks per epilogue warp
 constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct GemmArgs {
@@ -64,6 +66,70 @@ __device__ __forceinline__ void store_elem(void* p, size_t i, float v) {
   else static_cast<__half*>(p)[i] = __float2half_rn(v);
 }
 
+// Epilogue of one 128 x 256 accumulator tile for the thread that owns `row`: TMEM -> registers in
+// 32-column chunks (the load of chunk c+1 is in flight while chunk c is processed), + bias,
+// round to the output type, ReLU on the packed pairs (NaN-propagating max), 16-byte stores.
+// Bias values are fetched with warp-uniform 128-bit loads issued before the TMEM wait.
+template <bool BF16>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base, int row, int n0, bool vec_ok,
+                                              int c_begin) {
+  uint32_t r[2][32];
+  sm100::tmem_ld32(t_base + c_begin * 32, r[0]);
+  const bool bias_vec = a.bias != nullptr && vec_ok && (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0;
+#pragma unroll
+  for (int cc = 0; cc < EPI_CHUNKS; ++cc) {
+    const int c = c_begin + cc;
+    const int col0 = n0 + c * 32;
+    const bool full_chunk = vec_ok && col0 + 32 <= a.N;
+    uint4 bq[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (bias_vec && full_chunk) {
+      const uint4* bp = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.bias) + static_cast<size_t>(col0) * 2);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) bq[g] = __ldg(bp + g);
+    }
+    sm100::tmem_ld_wait();
+    if (cc + 1 < EPI_CHUNKS) sm100::tmem_ld32(t_base + (c + 1) * 32, r[(cc + 1) & 1]);
+    const uint32_t* rc = r[cc & 1];
+    if (row < a.M && col0 < a.N) {
+      const size_t off = static_cast<size_t>(row) * a.N + col0;
+      if (full_chunk && (bias_vec || a.bias == nullptr)) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + off * 2);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t bw[4] = {bq[g].x, bq[g].y, bq[g].z, bq[g].w};
+          uint32_t w[4];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            float b0, b1;
+            if (BF16) { b0 = __uint_as_float(bw[h] << 16); b1 = __uint_as_float(bw[h] & 0xffff0000u); }
+            else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&bw[h])); b0 = f.x; b1 = f.y; }
+            w[h] = pack2<BF16>(__uint_as_float(rc[g * 8 + h * 2]) + b0, __uint_as_float(rc[g * 8 + h * 2 + 1]) + b1);
+            if (a.relu) {
+              if (BF16) {
+                const __nv_bfloat162 z = __float2bfloat162_rn(0.0f);
+                __nv_bfloat162 t = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&w[h]), z);
+                w[h] = *reinterpret_cast<uint32_t*>(&t);
+              } else {
+                const __half2 z = __float2half2_rn(0.0f);
+                __half2 t = __hmax2_nan(*reinterpret_cast<__half2*>(&w[h]), z);
+                w[h] = *reinterpret_cast<uint32_t*>(&t);
+              }
+            }
+          }
+          dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        for (int j = 0; j < 32 && col0 + j < a.N; ++j) {
+          float x = __uint_as_float(rc[j]);
+          if (a.bias != nullptr) x += load_elem<BF16>(a.bias, col0 + j);
+          if (a.relu) x = x > 0.0f ? x : (x != x ? x : 0.0f);
+          store_elem<BF16>(a.out, off + j, x);
+        }
+      }
+    }
+  }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __grid_constant__ GemmArgs a) {
   extern __shared__ unsigned char smem_raw[];
@@ -84,7 +150,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     }
     for (int s = 0; s < ACC_STAGES; ++s) {
       sm100::mbar_init(&acc_full[s], 1);
-      sm100::mbar_init(&acc_empty[s], 4);  // one arrival per epilogue warp
+      sm100::mbar_init(&acc_empty[s], EPI_WARPS);  // one arrival per epilogue warp
     }
     sm100::fence_barrier_init();
   }
@@ -146,7 +212,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t tile_iter = 0;
     const bool vec_ok = (a.N % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
@@ -157,43 +223,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
       sm100::tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_base = tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        sm100::tmem_ld32(t_base + c * 32, r);
-        sm100::tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < a.M && col0 < a.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(r[j]);
-            if (a.bias != nullptr && col0 + j < a.N) x += load_elem<BF16>(a.bias, col0 + j);
-            v[j] = x;
-          }
-          const size_t off = static_cast<size_t>(row) * a.N + col0;
-          if (vec_ok && col0 + 32 <= a.N) {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + off * 2);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint32_t w[4];
-#pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                float lo = v[g * 8 + h * 2], hi = v[g * 8 + h * 2 + 1];
-                if (a.relu) { lo = lo > 0.0f ? lo : (lo != lo ? lo : 0.0f); hi = hi > 0.0f ? hi : (hi != hi ? hi : 0.0f); }
-                w[h] = pack2<BF16>(lo, hi);
-              }
-              dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < a.N; ++j) {
-              float x = v[j];
-              if (a.relu) x = x > 0.0f ? x : (x != x ? x : 0.0f);
-              store_elem<BF16>(a.out, off + j, x);
-            }
-          }
-        }
-      }
+      epilogue_tile<BF16>(a, t_base, row, n0, vec_ok, ((warp - 2) >> 2) * EPI_CHUNKS);
       sm100::tc_fence_before();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&acc_empty[as]);
@@ -245,7 +275,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
     }
     for (int s = 0; s < ACC_STAGES; ++s) {
       sm100::mbar_init(&acc_full[s], 1);   // multicast commit, both CTAs
-      sm100::mbar_init(&acc_empty[s], 8);  // leader only: 4 epilogue warps of each CTA
+      sm100::mbar_init(&acc_empty[s], 2 * EPI_WARPS);  // leader only: the epilogue warps of both CTAs
     }
     sm100::fence_barrier_init();
   }
@@ -308,7 +338,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
     const int q = warp & 3;
     uint32_t tile_iter = 0;
     const bool vec_ok = (a.N % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
@@ -320,43 +350,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
       sm100::tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_base = tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        sm100::tmem_ld32(t_base + c * 32, r);
-        sm100::tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < a.M && col0 < a.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(r[j]);
-            if (a.bias != nullptr && col0 + j < a.N) x += load_elem<BF16>(a.bias, col0 + j);
-            v[j] = x;
-          }
-          const size_t off = static_cast<size_t>(row) * a.N + col0;
-          if (vec_ok && col0 + 32 <= a.N) {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + off * 2);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint32_t w[4];
-#pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                float lo = v[g * 8 + h * 2], hi = v[g * 8 + h * 2 + 1];
-                if (a.relu) { lo = lo > 0.0f ? lo : (lo != lo ? lo : 0.0f); hi = hi > 0.0f ? hi : (hi != hi ? hi : 0.0f); }
-                w[h] = pack2<BF16>(lo, hi);
-              }
-              dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < a.N; ++j) {
-              float x = v[j];
-              if (a.relu) x = x > 0.0f ? x : (x != x ? x : 0.0f);
-              store_elem<BF16>(a.out, off + j, x);
-            }
-          }
-        }
-      }
+      epilogue_tile<BF16>(a, t_base, row, n0, vec_ok, ((warp - 2) >> 2) * EPI_CHUNKS);
       sm100::tc_fence_before();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive_remote(leader_acc_empty + as * 8);   // the leader's barrier, from either CTA
