@@ -362,6 +362,10 @@ int launch_named_variant(const RowArgs& a, cudaStream_t s) {
   const int64_t n_blocks = (a.rows + RB - 1) / RB;
   int64_t grid = static_cast<int64_t>(sm_count()) * per_sm;
   if (grid > n_blocks) grid = n_blocks;
+  // every CTA gets the same number of row blocks: a last, sparsely populated round would run
+  // latency-bound and cost as much as a full one
+  const int64_t rounds = (n_blocks + grid - 1) / grid;
+  grid = (n_blocks + rounds - 1) / rounds;
   kern<<<static_cast<unsigned>(grid), NT, 0, s>>>(a);
   CDR_CUDA_TRY(cudaGetLastError());
   return CDR_OK;
