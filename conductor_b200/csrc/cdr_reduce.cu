@@ -91,7 +91,7 @@ __device__ __forceinline__ void store_result(void* out, int dt, int64_t i, float
 // A shared-memory ring filled by bulk (TMA) copies was measured too and lost (27-29 us): the
 // consumer side, not bytes in flight, limits this kernel.
 template <class Chain, int NT, int VPT, int RB, bool EXACT>
-__global__ void __launch_bounds__(NT) row_reduce_named_kernel(const __grid_constant__ RowArgs a) {
+__global__ void __launch_bounds__(NT, (768 / NT > 0 ? 768 / NT : 1)) row_reduce_named_kernel(const __grid_constant__ RowArgs a) {
   using T = typename Chain::elem;
   using idx_t = typename std::conditional<EXACT, int32_t, int64_t>::type;
   constexpr int V = 16 / sizeof(T);
@@ -354,9 +354,14 @@ RowChain match_row_chain(const cdr_ew_params& p, int dt, int* full_idx, int* row
 template <class Chain, int NT, int VPT, int RB, bool EXACT>
 int launch_named_variant(const RowArgs& a, cudaStream_t s) {
   auto kern = row_reduce_named_kernel<Chain, NT, VPT, RB, EXACT>;
-  int per_sm = 0;
-  CDR_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, 0));
-  if (per_sm < 1) per_sm = 1;
+  // the occupancy query costs microseconds of host time: ask once per kernel instance
+  static int cached_per_sm = 0;
+  if (cached_per_sm == 0) {
+    int q = 0;
+    CDR_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, NT, 0));
+    cached_per_sm = q < 1 ? 1 : q;
+  }
+  int per_sm = cached_per_sm;
   // 768 resident threads per SM measured best (3 CTAs of 256: 22.6 us; 4: 23.1; 6: 24.6)
   if (per_sm > 768 / NT && NT <= 768) per_sm = 768 / NT;
   const int64_t n_blocks = (a.rows + RB - 1) / RB;
