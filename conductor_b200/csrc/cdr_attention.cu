@@ -46,19 +46,20 @@ struct AttnArgs {
   int* status;
 };
 
+constexpr int KV_STAGES = 5;   // one ring for K and V tiles: K_0 V_0 K_1 V_1 ... (2.5 key blocks in flight)
+
 template <int HD>
 struct AttnSmem {
   static constexpr int TILE_BYTES = 128 * HD * 2;      // one Q half, K block or V block
   static constexpr int Q_OFF = 0;                      // 2 halves
-  static constexpr int K_OFF = 2 * TILE_BYTES;         // 2 stages
-  static constexpr int V_OFF = K_OFF + 2 * TILE_BYTES; // 2 stages
-  static constexpr int BAR_OFF = V_OFF + 2 * TILE_BYTES;
+  static constexpr int KV_OFF = 2 * TILE_BYTES;        // KV_STAGES tiles
+  static constexpr int BAR_OFF = KV_OFF + KV_STAGES * TILE_BYTES;
   static constexpr size_t TOTAL = BAR_OFF + 256 + 1024;
 };
 
-// barrier indices; the [2] ones are indexed by ring stage or by half
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13,
-       B_COUNT = 15 };
+// barrier indices; ring barriers are indexed by stage, the others by half
+enum { B_QFULL = 0, B_FULL = 1, B_EMPTY = B_FULL + KV_STAGES, B_SFULL = B_EMPTY + KV_STAGES, B_PFULL = B_SFULL + 2,
+       B_PVDONE = B_PFULL + 2, B_COUNT = B_PVDONE + 2 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -126,20 +127,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
           for (int d = 0; d < HD / 64; ++d)
             sm100::tma_load_3d(smem + L::Q_OFF + h * L::TILE_BYTES + d * (128 * 128), &a.tmap_q, d * 64,
                                q0 + h * BH_ROWS, bh, &bars[B_QFULL]);
-      for (int j = 0; j < n_iter; ++j) {
-        const int st = j & 1, use = j >> 1;
-        if (use > 0 && !sm100::mbar_wait(&bars[B_KEMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 20); break; }
-        sm100::mbar_arrive_expect_tx(&bars[B_KFULL + st], L::TILE_BYTES);
+      // ring tile i: K_j for i = 2j, V_j for i = 2j + 1
+      for (int i = 0; i < 2 * n_iter; ++i) {
+        const int st = i % KV_STAGES, use = i / KV_STAGES;
+        if (use > 0 && !sm100::mbar_wait(&bars[B_EMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 20); break; }
+        sm100::mbar_arrive_expect_tx(&bars[B_FULL + st], L::TILE_BYTES);
+        const void* tmap = (i & 1) ? static_cast<const void*>(&a.tmap_v) : static_cast<const void*>(&a.tmap_k);
 #pragma unroll
         for (int d = 0; d < HD / 64; ++d)
-          sm100::tma_load_3d(smem + L::K_OFF + st * L::TILE_BYTES + d * (128 * 128), &a.tmap_k, d * 64, j * BKV, bh,
-                             &bars[B_KFULL + st]);
-        if (use > 0 && !sm100::mbar_wait(&bars[B_VEMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 21); break; }
-        sm100::mbar_arrive_expect_tx(&bars[B_VFULL + st], L::TILE_BYTES);
-#pragma unroll
-        for (int d = 0; d < HD / 64; ++d)
-          sm100::tma_load_3d(smem + L::V_OFF + st * L::TILE_BYTES + d * (128 * 128), &a.tmap_v, d * 64, j * BKV, bh,
-                             &bars[B_VFULL + st]);
+          sm100::tma_load_3d(smem + L::KV_OFF + st * L::TILE_BYTES + d * (128 * 128), tmap, d * 64, (i >> 1) * BKV, bh,
+                             &bars[B_FULL + st]);
       }
     }
   } else if (warp == 1) {
@@ -153,7 +150,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       // S_h(j) = Q_h K_j^T; the caller has already waited for K_j
       auto issue_s = [&](int h, int j) {
         const uint32_t q_addr = sm100::smem_u32(smem + L::Q_OFF + h * L::TILE_BYTES);
-        const uint32_t k_addr = sm100::smem_u32(smem + L::K_OFF + (j & 1) * L::TILE_BYTES);
+        const uint32_t k_addr = sm100::smem_u32(smem + L::KV_OFF + ((2 * j) % KV_STAGES) * L::TILE_BYTES);
         const uint32_t d = tmem_base + TMEM_S + h * 128;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
@@ -164,22 +161,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         sm100::umma_commit(&bars[B_SFULL + h]);
       };
 
-      if (ok && n_iter > 0) {
-        ok = sm100::mbar_wait(&bars[B_KFULL + 0], 0);
-        if (!ok) sm100::report_timeout(a.status, 23);
-      }
+      auto wait_tile = [&](int i, int site) -> bool {
+        if (sm100::mbar_wait(&bars[B_FULL + i % KV_STAGES], (i / KV_STAGES) & 1)) return true;
+        sm100::report_timeout(a.status, site);
+        return false;
+      };
+      if (ok && n_iter > 0) ok = wait_tile(0, 23);
       if (ok && n_iter > 0) {
         sm100::tc_fence_after();
         for (int h = 0; h < 2; ++h)
           if (nblk[h] > 0) issue_s(h, 0);
-        sm100::umma_commit(&bars[B_KEMPTY + 0]);
+        sm100::umma_commit(&bars[B_EMPTY + 0]);          // K_0 free once both S(0) are done
       }
       for (int j = 0; j < n_iter && ok; ++j) {
-        const int st = j & 1, use = j >> 1;
         const bool next = j + 1 < n_iter;
-        if (!sm100::mbar_wait(&bars[B_VFULL + st], use & 1)) { sm100::report_timeout(a.status, 25); break; }
-        if (next && !sm100::mbar_wait(&bars[B_KFULL + ((j + 1) & 1)], ((j + 1) >> 1) & 1)) { sm100::report_timeout(a.status, 24); break; }
-        const uint32_t v_addr = sm100::smem_u32(smem + L::V_OFF + st * L::TILE_BYTES);
+        const int vt = 2 * j + 1, kt = 2 * j + 2;       // ring tiles of V_j and K_(j+1)
+        if (!wait_tile(vt, 25)) break;
+        bool k_ready = false;
+        const uint32_t v_addr = sm100::smem_u32(smem + L::KV_OFF + (vt % KV_STAGES) * L::TILE_BYTES);
         for (int h = 0; h < 2 && ok; ++h) {
           if (j < nblk[h]) {
             if (!sm100::mbar_wait(&bars[B_PFULL + h], j & 1)) { sm100::report_timeout(a.status, 26); ok = false; break; }
@@ -192,11 +191,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
             }
             sm100::umma_commit(&bars[B_PVDONE + h]);
           }
-          if (next && j + 1 < nblk[h]) issue_s(h, j + 1);
+          if (next && j + 1 < nblk[h]) {
+            if (!k_ready) { ok = wait_tile(kt, 24); if (!ok) break; k_ready = true; sm100::tc_fence_after(); }
+            issue_s(h, j + 1);
+          }
         }
         if (!ok) break;
-        sm100::umma_commit(&bars[B_VEMPTY + st]);
-        if (next) sm100::umma_commit(&bars[B_KEMPTY + ((j + 1) & 1)]);
+        sm100::umma_commit(&bars[B_EMPTY + vt % KV_STAGES]);
+        if (next) sm100::umma_commit(&bars[B_EMPTY + kt % KV_STAGES]);
       }
     }
   } else {
@@ -235,10 +237,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
             bmax = fmaxf(bmax, v);
           }
       } else {
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, __uint_as_float(sr[c][i]));
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[c][i]));
+        bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       }
       bmax *= a.scale_log2;  // scale > 0: max commutes with the scaling
 
