@@ -40,6 +40,7 @@ class Callable:
         self._pinned: dict[int, torch.Tensor] = {}
         self._param_cache: dict[tuple, tuple] = {}
         self.calls = 0
+        self._warned_no_grad = False
         # when set, every call stores the placeholder tensors it ran on (graph capture needs the
         # full list, including module parameters Dynamo lifted into placeholders)
         self.record_inputs = False
@@ -65,7 +66,7 @@ class Callable:
         key = (id(buf), device)
         t = self._const_cache.get(key)
         src = buf.constant_value
-        if t is None or t._version != getattr(src, "_version", 0) and False:
+        if t is None:
             t = src.detach().to(device).contiguous()
             self._const_cache[key] = t
         return t
@@ -116,7 +117,19 @@ class Callable:
                     if buf.shape and buf.shape[0] == self.batch_size and t.dim() > 0 and t.shape[0] != self.batch_size:
                         rows = t.shape[0]
                         break
-            outputs = self._run_plan(env, device, rows)
+            outputs = None
+            if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+                from .autograd import SoftmaxFunction, differentiable_kind
+
+                if not host_mode and rows is None and differentiable_kind(self.launches) == "softmax":
+                    # forward through an autograd.Function whose backward is the softmax-backward template
+                    outputs = [SoftmaxFunction.apply(env[dag.inputs[0]], self._exec(), self.launches[0])]
+                elif not self._warned_no_grad:
+                    self._warned_no_grad = True
+                    logger.warning("%s: inputs require grad but this plan has no backward; outputs are detached",
+                                   self.artifact.entry_point)
+            if outputs is None:
+                outputs = self._run_plan(env, device, rows)
             if host_mode:
                 # device -> pinned host (blocks come from torch's caching host allocator, so a
                 # steady-state call allocates nothing), then one wait for the whole plan

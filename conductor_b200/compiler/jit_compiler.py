@@ -18,6 +18,7 @@ import torch
 from ..codegen.kernel_templates import KernelLaunch, KernelTemplateSelector
 from ..optimization.fusion import FusionCluster, LocalPriorityFusionEngine, schedule_clusters
 from ..optimization.graph_analyzer import ComputationDAG, GraphAnalyzer
+from ..utils.cache import CompilationCache
 from ..utils.config import get_config
 from ..utils.exceptions import CompilationError, ConductorError
 from ..utils.logging import get_logger
@@ -51,7 +52,7 @@ class ChoreoJITCompiler:
         self.graph_analyzer = GraphAnalyzer()
         self.fusion_engine = LocalPriorityFusionEngine()
         self.template_selector = KernelTemplateSelector()
-        self._cache: dict[str, CompiledArtifact] = {}
+        self.cache = CompilationCache(enabled=self.config.cache.enabled)
         self.stats = {"compiled": 0, "cache_hits": 0, "seconds": 0.0}
 
     # ------------------------------------------------------------------ hashing
@@ -74,9 +75,11 @@ class ChoreoJITCompiler:
         t0 = time.perf_counter()
         cfg = self.config
         graph_hash = self._generate_graph_hash(graph_module, example_inputs)
-        if cfg.cache.enabled and graph_hash in self._cache:
+        self.cache.enabled = cfg.cache.enabled
+        cached = self.cache.get(graph_hash)
+        if cached is not None:
             self.stats["cache_hits"] += 1
-            return self._cache[graph_hash]
+            return cached
         try:
             tensors = list(example_inputs) if example_inputs is not None else None
             dag = self.graph_analyzer.parse_fx_graph(
@@ -103,8 +106,7 @@ class ChoreoJITCompiler:
             metadata={"graph_hash": graph_hash, "plan": plan_text, "dsl_content": plan_text,
                       "n_clusters": len(clusters), "n_nodes": len(dag.nodes)},
             launches=launches, dag=dag, clusters=ordered)
-        if cfg.cache.enabled:
-            self._cache[graph_hash] = artifact
+        self.cache.put(graph_hash, artifact)
         self.stats["compiled"] += 1
         self.stats["seconds"] += time.perf_counter() - t0
         logger.info("compiled %s: %d nodes -> %d kernels", name, len(dag.nodes),
@@ -125,4 +127,4 @@ class ChoreoJITCompiler:
             f.write(str(gm.graph) + "\n\n" + self.graph_analyzer.describe(dag) + "\n\n" + plan_text + "\n")
 
     def clear_cache(self) -> None:
-        self._cache.clear()
+        self.cache.clear()

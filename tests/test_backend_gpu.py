@@ -122,3 +122,54 @@ def test_device_status_word_is_clean():
     with torch.cuda.device(0):
         assert load_library().cdr_device_status(ctypes.byref(st), 1) == 0
     assert st.value == 0
+
+
+def test_softmax_is_differentiable_through_the_backend():
+    """loss.backward() through a gcu-compiled softmax runs the softmax-backward template."""
+    logits, grad = wl.inputs_softmax(48, 1024, seed=48)
+    x_ref = logits.clone().requires_grad_(True)
+    y_ref = torch.softmax(x_ref, -1)
+    y_ref.backward(grad)
+    x = logits.to(DEV).requires_grad_(True)
+    y = compiled(wl.softmax_forward)(x)
+    assert y.requires_grad
+    y.backward(grad.to(DEV))
+    assert_close(y, y_ref, 1e-5, "softmax fwd under autograd")
+    assert_close(x.grad, x_ref.grad, 1e-5, "softmax grad")
+
+
+def test_wider_elementwise_and_reduction_coverage():
+    gen = torch.Generator().manual_seed(49)
+    x = torch.randn(64, 96, generator=gen)
+    y = torch.rand(64, 96, generator=gen) + 0.5
+    cases = {
+        "sub_div": lambda a, b: (a - b) / b,
+        "unary_math": lambda a, b: torch.tanh(a) + torch.sigmoid(a) * torch.exp(-b) - torch.sqrt(b) + torch.log(b),
+        "abs_neg_trig": lambda a, b: torch.abs(a) - torch.neg(b) + torch.sin(a) * torch.cos(b),
+        "max_min": lambda a, b: torch.maximum(a, b) - torch.minimum(a, b),
+        "addcmul": lambda a, b: torch.addcmul(a, a, b, value=0.25),
+        "row_sum": lambda a, b: (a * b).sum(-1),
+        "row_amax": lambda a, b: torch.amax(a + b, dim=-1),
+        "reduce_then_scale": lambda a, b: a / a.abs().sum(-1, keepdim=True),
+        "full_mean": lambda a, b: (a * b).mean(),
+    }
+    for name, fn in cases.items():
+        want = rp.run_reference(fn, [x, y])
+        got = compiled(fn)(x.to(DEV), y.to(DEV))
+        assert_close(got, want, 2e-5 if name in ("reduce_then_scale",) else 1e-5, name)
+
+
+def test_integer_graph_is_bit_exact():
+    a = torch.randint(-1000, 1000, (33, 65), dtype=torch.int32)
+    b = torch.randint(-2**31, 2**31 - 1, (33, 65), dtype=torch.int32)
+    fn = lambda p, q: (p + q) * p - q  # noqa: E731
+    got = compiled(fn)(a.to(DEV), b.to(DEV))
+    assert got.dtype == torch.int32 and torch.equal(got.cpu(), fn(a, b))
+
+
+def test_bf16_chain_with_cast_is_bit_exact():
+    x, w, b = wl.inputs_reduce_mean(40, 512, seed=50)
+    fn = lambda x, w, b: torch.relu(x * w + b).float() * 2.0  # noqa: E731
+    want = rp.run_reference(fn, [x, w, b])
+    got = compiled(fn)(x.to(DEV), w.to(DEV), b.to(DEV))
+    assert got.dtype == torch.float32 and torch.equal(got.cpu(), want)

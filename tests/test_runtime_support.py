@@ -1,0 +1,105 @@
+"""Config, compile cache, debug dump and exception surface (CPU only)."""
+import json
+
+import pytest
+import torch
+import torch.fx as fx
+
+from conductor.compiler.jit_compiler import ChoreoJITCompiler
+from conductor.utils.cache import CompilationCache
+from conductor.utils.config import ConductorConfig, get_config, reset_config, set_config
+from conductor.utils.exceptions import (CompilationError, ConductorError, DeviceError, ExecutionError,
+                                        UnsupportedOperationError)
+
+
+def traced(fn=lambda a, b, c: a * b + c):
+    return fx.symbolic_trace(fn)
+
+
+def test_config_defaults_env_and_file(monkeypatch, tmp_path):
+    cfg = ConductorConfig.load()
+    assert not cfg.debug.enabled and cfg.cache.enabled and cfg.compilation.enable_fusion
+    assert cfg.runtime.device == "gcu" and cfg.runtime.devices == 1 and cfg.logging.level == "WARNING"
+    monkeypatch.setenv("CONDUCTOR_DEBUG", "1")
+    monkeypatch.setenv("CONDUCTOR_DISABLE_CACHE", "true")
+    monkeypatch.setenv("CONDUCTOR_LOG_LEVEL", "info")
+    monkeypatch.setenv("CONDUCTOR_DEVICES", "4")
+    cfg = ConductorConfig.load()
+    assert cfg.debug.enabled and not cfg.cache.enabled and cfg.logging.level == "INFO" and cfg.runtime.devices == 4
+    for k in ("CONDUCTOR_DEBUG", "CONDUCTOR_DISABLE_CACHE", "CONDUCTOR_LOG_LEVEL", "CONDUCTOR_DEVICES"):
+        monkeypatch.delenv(k)
+    path = tmp_path / "conductor_config.json"
+    path.write_text(json.dumps({"compilation": {"enable_fusion": False, "unknown_key": 1}, "cache": {"max_size_mb": 7}}))
+    cfg = ConductorConfig.load(str(path))
+    assert not cfg.compilation.enable_fusion and cfg.cache.max_size_mb == 7
+    assert cfg.to_dict()["compilation"]["timeout_seconds"] == 300
+
+
+def test_compilation_cache_lru():
+    c = CompilationCache(max_entries=2)
+    c.put("a", 1)
+    c.put("b", 2)
+    assert c.get("a") == 1                      # touch a: b becomes the eviction candidate
+    c.put("c", 3)
+    assert c.get("b") is None and c.get("a") == 1 and c.get("c") == 3 and len(c) == 2
+    st = c.get_stats()
+    assert st["hits"] == 3 and st["misses"] == 1 and st["evictions"] == 1
+    off = CompilationCache(enabled=False)
+    off.put("x", 1)
+    assert off.get("x") is None and "x" not in off
+
+
+def test_compile_cache_hits_and_key_covers_dtype():
+    comp = ChoreoJITCompiler()
+    gm = traced()
+    f32 = [torch.randn(4, 4)] * 3
+    a1 = comp.compile_graph(gm, f32)
+    a2 = comp.compile_graph(gm, f32)
+    assert a1 is a2 and comp.stats["cache_hits"] == 1 and comp.stats["compiled"] == 1
+    bf16 = [t.bfloat16() for t in f32]
+    a3 = comp.compile_graph(traced(), bf16)
+    assert a3 is not a1 and a3.launches[0].params.instr[0].round_to == 1          # rounds to bf16
+    assert comp._generate_graph_hash(gm, f32) != comp._generate_graph_hash(gm, bf16)
+    assert comp._generate_graph_hash(gm, f32) != comp._generate_graph_hash(gm, [torch.randn(4, 8)] * 3)
+    comp.clear_cache()
+    assert comp.compile_graph(gm, f32) is not a1
+
+
+def test_debug_dump_is_opt_in(tmp_path):
+    cfg = ConductorConfig.load()
+    cfg.debug.enabled = True
+    cfg.debug.dump_dir = str(tmp_path / "dump")
+    set_config(cfg)
+    try:
+        art = ChoreoJITCompiler().compile_graph(traced(), [torch.randn(4, 4)] * 3)
+        files = list((tmp_path / "dump").glob("*.plan.txt"))
+        assert len(files) == 1
+        text = files[0].read_text()
+        assert "elementwise<elementwise[mul,add]>" in text and "buffers:" in text and art.entry_point in files[0].name
+    finally:
+        reset_config()
+    assert not get_config().debug.enabled
+
+
+def test_artifact_metadata():
+    art = ChoreoJITCompiler().compile_graph(traced(), [torch.randn(4, 4)] * 3)
+    assert art.artifact_type == "kernel_plan" and art.entry_point.startswith("kernel_") and art.is_valid()
+    assert art.metadata["n_clusters"] == 1 and art.metadata["n_nodes"] == 2
+    assert art.path.endswith("libconductor_b200.so")
+    assert "plan kernel_" in art.metadata["plan"]
+
+
+def test_exception_hierarchy_and_fields():
+    assert issubclass(CompilationError, ConductorError) and issubclass(DeviceError, ConductorError)
+    e = UnsupportedOperationError("cumsum", "no template")
+    assert e.operation == "cumsum" and "cumsum" in str(e) and "no template" in str(e)
+    x = ExecutionError("boom", kernel_name="k", status=-5)
+    assert x.status == -5 and x.kernel_name == "k" and "status=-5" in str(x)
+    c = CompilationError("bad", dsl_code="plan", compiler_output="line1\nerror: x\n")
+    assert c.get_compiler_errors() == ["error: x"]
+
+
+def test_validation_failure_is_a_compilation_error():
+    comp = ChoreoJITCompiler()
+    with pytest.raises((CompilationError, ValueError)):
+        comp.compile_graph(traced(), [torch.randn(4, 4)])            # wrong number of example inputs
