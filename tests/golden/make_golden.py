@@ -2,7 +2,7 @@
 
 Run in the build container, where the reference checkout is mounted read-only:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference is copied to a temporary directory first (its DebugArtifactManager creates
 ``debug_dir/`` next to the package on import, conductor/utils/artifacts.py:28-44), imported
@@ -84,4 +84,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and "CONDUCTOR_REFERENCE_ROOT" not in os.environ:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference>")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["CONDUCTOR_REFERENCE_ROOT"])
