@@ -55,6 +55,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// 256-bit global store (sm_100): p must be 32-byte aligned
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 template <bool BF16>
 __device__ __forceinline__ float load_elem(const void* p, int i) {
   if (BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
@@ -93,30 +100,39 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base
     if (row < a.M && col0 < a.N) {
       const size_t off = static_cast<size_t>(row) * a.N + col0;
       if (full_chunk && (bias_vec || a.bias == nullptr)) {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + off * 2);
+        unsigned char* dst = static_cast<unsigned char*>(a.out) + off * 2;
+        const bool wide = ((a.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 31u) == 0);  // 32-byte aligned rows
+        uint32_t w[16];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const uint32_t bw[4] = {bq[g].x, bq[g].y, bq[g].z, bq[g].w};
-          uint32_t w[4];
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
             float b0, b1;
             if (BF16) { b0 = __uint_as_float(bw[h] << 16); b1 = __uint_as_float(bw[h] & 0xffff0000u); }
             else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&bw[h])); b0 = f.x; b1 = f.y; }
-            w[h] = pack2<BF16>(__uint_as_float(rc[g * 8 + h * 2]) + b0, __uint_as_float(rc[g * 8 + h * 2 + 1]) + b1);
+            uint32_t v = pack2<BF16>(__uint_as_float(rc[g * 8 + h * 2]) + b0, __uint_as_float(rc[g * 8 + h * 2 + 1]) + b1);
             if (a.relu) {
               if (BF16) {
                 const __nv_bfloat162 z = __float2bfloat162_rn(0.0f);
-                __nv_bfloat162 t = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&w[h]), z);
-                w[h] = *reinterpret_cast<uint32_t*>(&t);
+                __nv_bfloat162 t = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&v), z);
+                v = *reinterpret_cast<uint32_t*>(&t);
               } else {
                 const __half2 z = __float2half2_rn(0.0f);
-                __half2 t = __hmax2_nan(*reinterpret_cast<__half2*>(&w[h]), z);
-                w[h] = *reinterpret_cast<uint32_t*>(&t);
+                __half2 t = __hmax2_nan(*reinterpret_cast<__half2*>(&v), z);
+                v = *reinterpret_cast<uint32_t*>(&t);
               }
             }
+            w[g * 4 + h] = v;
           }
-          dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (wide) {   // two 256-bit stores: every store fills a whole 32-byte sector
+          st_global_v8(dst, w);
+          st_global_v8(dst + 32, w + 8);
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            reinterpret_cast<uint4*>(dst)[g] = make_uint4(w[g * 4], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]);
         }
       } else {
         for (int j = 0; j < 32 && col0 + j < a.N; ++j) {
