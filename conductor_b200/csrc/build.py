@@ -24,6 +24,7 @@ LIB_PATH = CSRC / LIB_NAME
 SOURCES = {
     "cdr_api.cu": [],
     "cdr_elementwise.cu": ["--fmad=false"],
+    "cdr_jit.cu": [],
     "cdr_reduce.cu": ["--fmad=false"],
     "cdr_softmax.cu": ["--fmad=false"],
     "cdr_gemm.cu": [],
@@ -76,7 +77,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             list(pool.map(lambda sf: _compile(sf[0], sf[1], verbose), todo))
     objs = [str(CSRC / (Path(s).stem + ".o")) for s in SOURCES]
     if todo or not LIB_PATH.exists():
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *objs, "-cudart", "shared", "-lcuda"]
+        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *objs, "-cudart", "shared", "-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

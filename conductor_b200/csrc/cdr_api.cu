@@ -11,9 +11,15 @@
 #include <new>
 #include <vector>
 
+#include <string>
+
 #include "cdr_common.cuh"
 
 namespace cdr {
+
+std::string jit_elementwise_source(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E);
+std::vector<char> jit_compile(const std::string& src, std::string* log);
+int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out);
 
 namespace {
 thread_local char g_error[512] = {0};
@@ -161,6 +167,42 @@ int cdr_device_status(int* status_out, int clear) {
   CDR_CUDA_TRY(cudaMemcpy(status_out, p, sizeof(int), cudaMemcpyDeviceToHost));
   if (clear && *status_out) CDR_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
   return *status_out ? CDR_ERR_TIMEOUT : CDR_OK;
+}
+
+int cdr_elementwise_source(const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs, int n_outputs,
+                           const void* params, size_t params_bytes, char* buffer, size_t buffer_bytes, int compile) {
+  g_error[0] = 0;
+  if (int rc = check_lists(inputs, n_inputs, outputs, n_outputs)) return rc;
+  if (int rc = check_params(CDR_T_ELEMENTWISE, params, params_bytes)) return rc;
+  const cdr_ew_params* p = static_cast<const cdr_ew_params*>(params);
+  if (int rc = validate_ew_program(p, n_inputs, n_outputs)) return rc;
+  if (!buffer || buffer_bytes == 0) { set_error("buffer is null or empty"); return CDR_ERR_BAD_ARG; }
+  int in_dt[CDR_EW_MAX_INPUTS] = {0}, out_dt[CDR_EW_MAX_OUTPUTS] = {0};
+  bool any16 = false;
+  for (int i = 0; i < n_inputs; ++i) { in_dt[i] = inputs[i].dtype; any16 |= dtype_size(in_dt[i]) == 2; }
+  for (int o = 0; o < n_outputs; ++o) { out_dt[o] = outputs[o].dtype; any16 |= dtype_size(out_dt[o]) == 2; }
+  for (int i = 0; i < n_inputs + n_outputs; ++i) {
+    const int dt = i < n_inputs ? in_dt[i] : out_dt[i - n_inputs];
+    if (dt != CDR_F32 && dt != CDR_BF16 && dt != CDR_F16) { set_error("only floating-point chains are instantiated at run time"); return CDR_ERR_UNSUPPORTED; }
+  }
+  std::string src;
+  try {
+    src = jit_elementwise_source(*p, in_dt, out_dt, any16 ? 8 : 4);
+    const size_t n = src.size() < buffer_bytes - 1 ? src.size() : buffer_bytes - 1;
+    memcpy(buffer, src.data(), n);
+    buffer[n] = 0;
+    if (compile) {
+      std::string log;
+      if (jit_compile(src, &log).empty()) {
+        set_error("NVRTC: %s", log.empty() ? "compilation failed" : log.c_str());
+        return CDR_ERR_UNSUPPORTED;
+      }
+    }
+  } catch (const std::exception& e) {
+    set_error("source generation failed: %s", e.what());
+    return CDR_ERR_BAD_ARG;
+  }
+  return CDR_OK;
 }
 
 int cdr_workspace_bytes(int template_id, const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,

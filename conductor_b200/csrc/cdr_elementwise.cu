@@ -21,6 +21,9 @@
 
 namespace cdr {
 
+int launch_elementwise_jit(const void* const* in, void* const* out, const int* in_dt, const int* out_dt,
+                           const cdr_ew_params& p, int64_t n_units, int64_t cols, int E, cudaStream_t stream);
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -495,7 +498,27 @@ int launch_elementwise(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
   }
 
   int64_t done = 0;
-  if (vec_ok && n >= E) {
+  // A program without an ahead-of-time instance is instantiated at run time (NVRTC); inputs may
+  // then have different float dtypes.  CDR_ERR_UNSUPPORTED from the JIT means "not available".
+  {
+    bool any16 = false, jit_ok = true;
+    for (int i = 0; i < n_in; ++i) any16 |= dtype_size(ins[i].dtype) == 2;
+    for (int o = 0; o < n_out; ++o) any16 |= dtype_size(outs[o].dtype) == 2;
+    const int EJ = any16 ? 8 : 4;
+    for (int o = 0; o < n_out; ++o) jit_ok &= aligned16(outs[o].data);
+    for (int i = 0; i < n_in; ++i) {
+      const int m = p->input_mode[i];
+      if (m == CDR_IN_FULL || m == CDR_IN_ROW) jit_ok &= aligned16(ins[i].data);
+      if (m == CDR_IN_ROW || m == CDR_IN_COL) jit_ok &= (cols % EJ == 0);
+    }
+    const bool named = vec_ok && in_dt == out_dt && match_named(*p, in_dt) != kNone;
+    if (jit_ok && !named && n >= EJ) {
+      const int rc = launch_elementwise_jit(a.in, a.out, a.in_dtype, a.out_dtype, *p, n / EJ, cols, EJ, stream);
+      if (rc == CDR_OK) done = (n / EJ) * EJ;
+      else if (rc != CDR_ERR_UNSUPPORTED) return rc;
+    }
+  }
+  if (done == 0 && vec_ok && n >= E) {
     const int64_t n_units = n / E;
     const NamedChain c = (in_dt == out_dt) ? match_named(*p, in_dt) : kNone;
     int rc = CDR_ERR_UNSUPPORTED;

@@ -1,0 +1,296 @@
+// Runtime instantiation of the elementwise-chain template for programs that have no
+// ahead-of-time instance.
+//
+// The reference prints a whole Choreo program per graph and shells out to a compiler
+// (conductor/compiler/jit_compiler.py:235-382).  Here only the chain body is generated: a fixed,
+// hand-written kernel skeleton (128-bit streaming loads of every input up front, values in
+// registers, 128-bit streaming stores) is specialised with the cluster's straight-line program,
+// compiled for sm_100a with NVRTC (no headers, ~0.1 s), loaded through the driver API and cached
+// per device.  Arithmetic is the same as everywhere else: fp32 ops rounded one by one, no fma
+// contraction, each result rounded to the op's dtype.  If NVRTC or the driver entry points are
+// not available the caller falls back to the register-file interpreter kernel.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "cdr_common.cuh"
+
+namespace cdr {
+namespace {
+
+// ---------------------------------------------------------------- NVRTC / driver bindings
+struct Api {
+  bool ok = false;
+  nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*, const char* const*);
+  nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*);
+  nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetCUBIN)(nvrtcProgram, char*);
+  nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetProgramLog)(nvrtcProgram, char*);
+  nvrtcResult (*DestroyProgram)(nvrtcProgram*);
+  CUresult (*ModuleLoadData)(CUmodule*, const void*);
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*);
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                           void**, void**);
+};
+
+void* driver_entry(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  return p;
+}
+
+const Api& api() {
+  static Api a;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (getenv("CDR_DISABLE_JIT")) return;
+    void* h = dlopen("libnvrtc.so.12", RTLD_NOW | RTLD_LOCAL);
+    if (!h) h = dlopen("libnvrtc.so", RTLD_NOW | RTLD_LOCAL);
+    if (!h) return;
+#define CDR_SYM(field, name) \
+  a.field = reinterpret_cast<decltype(a.field)>(dlsym(h, name)); \
+  if (!a.field) return;
+    CDR_SYM(CreateProgram, "nvrtcCreateProgram")
+    CDR_SYM(CompileProgram, "nvrtcCompileProgram")
+    CDR_SYM(GetCUBINSize, "nvrtcGetCUBINSize")
+    CDR_SYM(GetCUBIN, "nvrtcGetCUBIN")
+    CDR_SYM(GetProgramLogSize, "nvrtcGetProgramLogSize")
+    CDR_SYM(GetProgramLog, "nvrtcGetProgramLog")
+    CDR_SYM(DestroyProgram, "nvrtcDestroyProgram")
+#undef CDR_SYM
+    a.ModuleLoadData = reinterpret_cast<decltype(a.ModuleLoadData)>(driver_entry("cuModuleLoadData"));
+    a.ModuleGetFunction = reinterpret_cast<decltype(a.ModuleGetFunction)>(driver_entry("cuModuleGetFunction"));
+    a.LaunchKernel = reinterpret_cast<decltype(a.LaunchKernel)>(driver_entry("cuLaunchKernel"));
+    a.ok = a.ModuleLoadData && a.ModuleGetFunction && a.LaunchKernel;
+  });
+  return a;
+}
+
+// ---------------------------------------------------------------- source generation
+const char* kPrelude = R"SRC(
+typedef unsigned int u32; typedef unsigned short u16; typedef long long i64;
+struct __align__(16) U4 { u32 x, y, z, w; };
+struct Args { const void* in[8]; void* out[4]; i64 n_units; i64 cols; };
+__device__ __forceinline__ U4 ld_cs(const void* p) { U4 v; asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v; }
+__device__ __forceinline__ U4 ld_nc(const void* p) { U4 v; asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v; }
+__device__ __forceinline__ void st_cs(void* p, U4 v) { asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
+__device__ __forceinline__ float bf2f(u32 h) { return __uint_as_float(h << 16); }
+__device__ __forceinline__ u32 f2bf(float x) { u16 h; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(x)); return h; }
+__device__ __forceinline__ float h2f(u32 h) { float f; u16 s = (u16)h; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(s)); return f; }
+__device__ __forceinline__ u32 f2h(float x) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(x)); return h; }
+__device__ __forceinline__ float rnd1(float x) { return bf2f(f2bf(x)); }   // round to bf16
+__device__ __forceinline__ float rnd2(float x) { return h2f(f2h(x)); }     // round to f16
+__device__ __forceinline__ float rnd0(float x) { return x; }
+__device__ __forceinline__ float relu_f(float x) { return x > 0.0f ? x : (x != x ? x : 0.0f); }
+__device__ __forceinline__ float max_f(float a, float b) { return (a != a || b != b) ? (a + b) : fmaxf(a, b); }
+__device__ __forceinline__ float min_f(float a, float b) { return (a != a || b != b) ? (a + b) : fminf(a, b); }
+__device__ __forceinline__ void un_f32(U4 q, float* f) { f[0] = __uint_as_float(q.x); f[1] = __uint_as_float(q.y); f[2] = __uint_as_float(q.z); f[3] = __uint_as_float(q.w); }
+__device__ __forceinline__ void un_bf16(U4 q, float* f) { u32 w[4] = {q.x, q.y, q.z, q.w}; for (int i = 0; i < 4; ++i) { f[2*i] = __uint_as_float(w[i] << 16); f[2*i+1] = __uint_as_float(w[i] & 0xffff0000u); } }
+__device__ __forceinline__ void un_f16(U4 q, float* f) { u32 w[4] = {q.x, q.y, q.z, q.w}; for (int i = 0; i < 4; ++i) { f[2*i] = h2f(w[i] & 0xffffu); f[2*i+1] = h2f(w[i] >> 16); } }
+__device__ __forceinline__ U4 pk_f32(const float* f) { U4 q; q.x = __float_as_uint(f[0]); q.y = __float_as_uint(f[1]); q.z = __float_as_uint(f[2]); q.w = __float_as_uint(f[3]); return q; }
+__device__ __forceinline__ U4 pk_bf16(const float* f) { u32 w[4]; for (int i = 0; i < 4; ++i) w[i] = f2bf(f[2*i]) | (f2bf(f[2*i+1]) << 16); U4 q; q.x = w[0]; q.y = w[1]; q.z = w[2]; q.w = w[3]; return q; }
+__device__ __forceinline__ U4 pk_f16(const float* f) { u32 w[4]; for (int i = 0; i < 4; ++i) w[i] = f2h(f[2*i]) | (f2h(f[2*i+1]) << 16); U4 q; q.x = w[0]; q.y = w[1]; q.z = w[2]; q.w = w[3]; return q; }
+)SRC";
+
+const char* dt_c(int dt) { return dt == CDR_F32 ? "float" : "u16"; }
+const char* dt_un(int dt) { return dt == CDR_F32 ? "un_f32" : dt == CDR_BF16 ? "un_bf16" : "un_f16"; }
+const char* dt_pk(int dt) { return dt == CDR_F32 ? "pk_f32" : dt == CDR_BF16 ? "pk_bf16" : "pk_f16"; }
+const char* dt_scalar(int dt) { return dt == CDR_F32 ? "" : dt == CDR_BF16 ? "bf2f" : "h2f"; }
+int dt_vec(int dt) { return dt == CDR_F32 ? 4 : 8; }
+
+std::string fimm(float v) {
+  char buf[64];
+  unsigned bits;
+  memcpy(&bits, &v, 4);
+  snprintf(buf, sizeof(buf), "__uint_as_float(0x%08xu)", bits);   // exact, also for inf / nan
+  return buf;
+}
+
+std::string expr(const cdr_ew_instr& i) {
+  auto R = [](int r) { return "r" + std::to_string(r); };
+  const std::string a = R(i.a), b = R(i.b), c = R(i.c), k = fimm(i.imm);
+  switch (i.op) {
+    case CDR_OP_ADD: return "__fadd_rn(" + a + ", " + b + ")";
+    case CDR_OP_SUB: return "__fsub_rn(" + a + ", " + b + ")";
+    case CDR_OP_MUL: return "__fmul_rn(" + a + ", " + b + ")";
+    case CDR_OP_DIV: return "__fdiv_rn(" + a + ", " + b + ")";
+    case CDR_OP_RELU: return "relu_f(" + a + ")";
+    case CDR_OP_NEG: return "(-" + a + ")";
+    case CDR_OP_ABS: return "fabsf(" + a + ")";
+    case CDR_OP_EXP: return "expf(" + a + ")";
+    case CDR_OP_LOG: return "logf(" + a + ")";
+    case CDR_OP_SQRT: return "__fsqrt_rn(" + a + ")";
+    case CDR_OP_SIGMOID: return "__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-" + a + ")))";
+    case CDR_OP_TANH: return "tanhf(" + a + ")";
+    case CDR_OP_SIN: return "sinf(" + a + ")";
+    case CDR_OP_COS: return "cosf(" + a + ")";
+    case CDR_OP_MAX: return "max_f(" + a + ", " + b + ")";
+    case CDR_OP_MIN: return "min_f(" + a + ", " + b + ")";
+    case CDR_OP_ADDCDIV: return "__fadd_rn(" + a + ", __fdiv_rn(__fmul_rn(" + k + ", " + b + "), " + c + "))";
+    case CDR_OP_ADDCMUL: return "__fadd_rn(" + a + ", __fmul_rn(__fmul_rn(" + k + ", " + b + "), " + c + "))";
+    case CDR_OP_CONST: return k;
+    case CDR_OP_COPY: return a;
+    case CDR_OP_ADD_IMM: return "__fadd_rn(" + a + ", " + k + ")";
+    case CDR_OP_MUL_IMM: return "__fmul_rn(" + a + ", " + k + ")";
+    case CDR_OP_RSUB_IMM: return "__fsub_rn(" + k + ", " + a + ")";
+    case CDR_OP_RDIV_IMM: return "__fdiv_rn(" + k + ", " + a + ")";
+    default: return "0.0f";
+  }
+}
+
+// One thread handles UN units of E consecutive elements; all loads first, then math and stores.
+std::string generate(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E, int UN) {
+  std::string s = kPrelude;
+  const int nin = p.n_inputs;
+  // the chain on one element
+  s += "__device__ __forceinline__ void chain(const float* in, float* out) {\n";
+  for (int i = 0; i < nin; ++i) s += "  const float r" + std::to_string(i) + " = in[" + std::to_string(i) + "];\n";
+  for (int k = 0; k < p.n_instr; ++k) {
+    const int rt = p.instr[k].round_to == CDR_BF16 ? 1 : p.instr[k].round_to == CDR_F16 ? 2 : 0;
+    s += "  const float r" + std::to_string(nin + k) + " = rnd" + std::to_string(rt) + "(" + expr(p.instr[k]) + ");\n";
+  }
+  for (int o = 0; o < p.n_outputs; ++o) s += "  out[" + std::to_string(o) + "] = r" + std::to_string(p.out_reg[o]) + ";\n";
+  s += "}\n";
+  const std::string Es = std::to_string(E), UNs = std::to_string(UN);
+  s += "extern \"C\" __global__ void __launch_bounds__(256) cdr_jit_k(const __grid_constant__ Args a) {\n";
+  s += "  const i64 unit0 = (i64)blockIdx.x * (256 * " + UNs + ") + threadIdx.x;\n";
+  s += "  float v[" + UNs + "][" + std::to_string(nin > 0 ? nin : 1) + "][" + Es + "];\n";
+  s += "#pragma unroll\n  for (int u = 0; u < " + UNs + "; ++u) {\n    const i64 unit = unit0 + (i64)u * 256;\n    if (unit < a.n_units) {\n      const i64 e0 = unit * " + Es + ";\n";
+  for (int i = 0; i < nin; ++i) {
+    const int dt = in_dt[i], V = dt_vec(dt), m = p.input_mode[i];
+    const std::string I = std::to_string(i), T = dt_c(dt);
+    if (m == CDR_IN_FULL || m == CDR_IN_ROW) {
+      const std::string base = m == CDR_IN_FULL ? "e0" : "(e0 % a.cols)";
+      const std::string ld = m == CDR_IN_FULL ? "ld_cs" : "ld_nc";
+      for (int k = 0; k < E / V; ++k)
+        s += "      " + std::string(dt_un(dt)) + "(" + ld + "((const " + T + "*)a.in[" + I + "] + " + base + " + " +
+             std::to_string(k * V) + "), v[u][" + I + "] + " + std::to_string(k * V) + ");\n";
+    } else {
+      const std::string idx = m == CDR_IN_COL ? "(e0 / a.cols)" : "0";
+      s += "      { const float t = " + std::string(dt_scalar(dt)) + "(((const " + T + "*)a.in[" + I + "])[" + idx +
+           "]);\n#pragma unroll\n        for (int e = 0; e < " + Es + "; ++e) v[u][" + I + "][e] = t; }\n";
+    }
+  }
+  s += "    }\n  }\n";
+  s += "#pragma unroll\n  for (int u = 0; u < " + UNs + "; ++u) {\n    const i64 unit = unit0 + (i64)u * 256;\n    if (unit < a.n_units) {\n      const i64 e0 = unit * " + Es + ";\n";
+  s += "      float o[" + std::to_string(p.n_outputs) + "][" + Es + "];\n";
+  s += "#pragma unroll\n      for (int e = 0; e < " + Es + "; ++e) {\n        float in[" + std::to_string(nin > 0 ? nin : 1) + "], out[" +
+       std::to_string(p.n_outputs) + "];\n";
+  for (int i = 0; i < nin; ++i) s += "        in[" + std::to_string(i) + "] = v[u][" + std::to_string(i) + "][e];\n";
+  s += "        chain(in, out);\n";
+  for (int o = 0; o < p.n_outputs; ++o) s += "        o[" + std::to_string(o) + "][e] = out[" + std::to_string(o) + "];\n";
+  s += "      }\n";
+  for (int o = 0; o < p.n_outputs; ++o) {
+    const int dt = out_dt[o], V = dt_vec(dt);
+    for (int k = 0; k < E / V; ++k)
+      s += "      st_cs((" + std::string(dt_c(dt)) + "*)a.out[" + std::to_string(o) + "] + e0 + " + std::to_string(k * V) + ", " +
+           dt_pk(dt) + "(o[" + std::to_string(o) + "] + " + std::to_string(k * V) + "));\n";
+  }
+  s += "    }\n  }\n}\n";
+  return s;
+}
+
+struct JitKernel {
+  CUfunction fn = nullptr;
+  bool failed = false;
+};
+std::mutex g_mu;
+std::unordered_map<std::string, JitKernel> g_cache;   // key: device + source
+
+struct JitArgs {
+  const void* in[8];
+  void* out[4];
+  long long n_units;
+  long long cols;
+};
+
+}  // namespace
+
+// Source text of the kernel that would be instantiated (for inspection and tests; needs no GPU).
+std::string jit_elementwise_source(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E) {
+  return generate(p, in_dt, out_dt, E, E == 4 ? 4 : 2);
+}
+
+// Compile `src` to a cubin image for sm_100a; empty on failure (message in `log`).
+std::vector<char> jit_compile(const std::string& src, std::string* log) {
+  const Api& A = api();
+  std::vector<char> cubin;
+  if (!A.CreateProgram) { if (log) *log = "NVRTC is not available"; return cubin; }
+  nvrtcProgram prog;
+  if (A.CreateProgram(&prog, src.c_str(), "cdr_jit.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS) return cubin;
+  const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17"};
+  const nvrtcResult rc = A.CompileProgram(prog, 3, opts);
+  if (rc != NVRTC_SUCCESS) {
+    size_t n = 0;
+    if (log && A.GetProgramLogSize(prog, &n) == NVRTC_SUCCESS && n > 1) {
+      log->resize(n);
+      A.GetProgramLog(prog, &(*log)[0]);
+    }
+    A.DestroyProgram(&prog);
+    return cubin;
+  }
+  size_t n = 0;
+  if (A.GetCUBINSize(prog, &n) == NVRTC_SUCCESS && n > 0) {
+    cubin.resize(n);
+    if (A.GetCUBIN(prog, cubin.data()) != NVRTC_SUCCESS) cubin.clear();
+  }
+  A.DestroyProgram(&prog);
+  return cubin;
+}
+
+// Launch the JIT instance for this program on the vector path.  CDR_ERR_UNSUPPORTED means "no JIT
+// here, use the interpreter"; other non-zero codes are real failures.
+int launch_elementwise_jit(const void* const* in, void* const* out, const int* in_dt, const int* out_dt,
+                           const cdr_ew_params& p, int64_t n_units, int64_t cols, int E, cudaStream_t stream) {
+  const Api& A = api();
+  if (!A.ok) return CDR_ERR_UNSUPPORTED;
+  const int UN = E == 4 ? 4 : 2;
+  int dev = 0;
+  CDR_CUDA_TRY(cudaGetDevice(&dev));
+  const std::string src = generate(p, in_dt, out_dt, E, UN);
+  const std::string key = std::to_string(dev) + "#" + src;
+  CUfunction fn = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    JitKernel& k = g_cache[key];
+    if (k.failed) return CDR_ERR_UNSUPPORTED;
+    if (!k.fn) {
+      std::string log;
+      const std::vector<char> cubin = jit_compile(src, &log);
+      CUmodule mod = nullptr;
+      if (cubin.empty() || A.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS ||
+          A.ModuleGetFunction(&k.fn, mod, "cdr_jit_k") != CUDA_SUCCESS) {
+        k.failed = true;
+        k.fn = nullptr;
+        if (getenv("CDR_JIT_VERBOSE")) fprintf(stderr, "conductor_b200: JIT failed, using the interpreter\n%s\n", log.c_str());
+        return CDR_ERR_UNSUPPORTED;
+      }
+    }
+    fn = k.fn;
+  }
+  JitArgs args{};
+  for (int i = 0; i < p.n_inputs; ++i) args.in[i] = in[i];
+  for (int o = 0; o < p.n_outputs; ++o) args.out[o] = out[o];
+  args.n_units = n_units;
+  args.cols = cols;
+  const int64_t per_cta = 256LL * UN;
+  const int64_t grid = (n_units + per_cta - 1) / per_cta;
+  if (grid > 0x7fffffff) return CDR_ERR_UNSUPPORTED;
+  void* params[] = {&args};
+  const CUresult r = A.LaunchKernel(fn, static_cast<unsigned>(grid), 1, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(stream),
+                                    params, nullptr);
+  if (r != CUDA_SUCCESS) { set_error("elementwise JIT launch failed with %d", static_cast<int>(r)); return CDR_ERR_CUDA; }
+  return CDR_OK;
+}
+
+}  // namespace cdr

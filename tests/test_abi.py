@@ -54,6 +54,47 @@ def test_argument_errors_need_no_gpu(built_library):
     assert lib.cdr_workspace_bytes(1, None, 0, None, 0, None, 0, None) == -1
 
 
+def test_generated_elementwise_source_compiles_without_a_gpu(built_library):
+    """The run-time instance of an elementwise program: generated source is specialised with the
+    program and the dtypes, and NVRTC accepts it for sm_100a (no device needed to compile)."""
+    import torch
+
+    import abi_util as abi
+    from conductor_b200.codegen.operator_registry import EwOp
+    from conductor_b200.compiler.executor import make_descriptors
+
+    lib = loader.load_library()
+    x, w, col = torch.zeros(8, 16), torch.zeros(16, dtype=torch.bfloat16), torch.zeros(8, 1, dtype=torch.float16)
+    out = torch.zeros(8, 16, dtype=torch.bfloat16)
+    prog = abi.ew_program(3, [
+        (EwOp.MUL, 0, 1, 0, 0, torch.float32), (EwOp.TANH, 3, 0, 0, 0, torch.float32),
+        (EwOp.ADDCMUL, 4, 2, 0, 0.5, torch.float32), (EwOp.RSUB_IMM, 5, 0, 0, 2.0, torch.bfloat16)],
+        [6], [abi.FULL, abi.ROW, abi.COL])
+    pp, ps = ctypes.cast(ctypes.byref(prog), ctypes.c_void_p), ctypes.sizeof(prog)
+    buf = ctypes.create_string_buffer(1 << 16)
+    ind, outd = make_descriptors([x, w, col]), make_descriptors([out])
+    rc = lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, buf, len(buf), 0)
+    assert rc == 0, lib.cdr_last_error()
+    src = buf.value.decode()
+    assert "cdr_jit_k" in src and "tanhf" in src and "un_bf16" in src and "% a.cols" in src
+    # compile when NVRTC is installed; the library reports its absence as "unsupported"
+    rc = lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, buf, len(buf), 1)
+    if rc != 0:
+        assert rc == -2 and b"NVRTC" in lib.cdr_last_error()
+        if b"not available" not in lib.cdr_last_error():
+            pytest.fail(lib.cdr_last_error().decode())
+    # truncation keeps the terminator; integer programs have no run-time instance
+    small = ctypes.create_string_buffer(32)
+    assert lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, small, len(small), 0) == 0
+    assert len(small.value) == 31
+    xi = torch.zeros(8, 16, dtype=torch.int32)
+    iprog = abi.ew_program(1, [(EwOp.ADD, 0, 0, 0, 0, torch.int32)], [1])
+    assert lib.cdr_elementwise_source(make_descriptors([xi]), 1, make_descriptors([xi]), 1,
+                                      ctypes.cast(ctypes.byref(iprog), ctypes.c_void_p), ctypes.sizeof(iprog),
+                                      buf, len(buf), 0) == -2
+    assert lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, None, 0, 0) == -1
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from conductor_b200.utils.exceptions import DeviceError
 

@@ -125,6 +125,42 @@ def test_interpreted_program_with_broadcasts(executor):
     assert_close(out2, want2, F32_TOL, "interpreted chain, scalar path")
 
 
+def test_runtime_instance_mixed_dtypes_and_tail(executor):
+    """A program with no ahead-of-time instance, on shapes the vector skeleton takes (aligned rows)
+    plus a tail that is not a whole vector: mixed fp32 / bf16 / fp16 inputs, per-op rounding."""
+    gen = torch.Generator().manual_seed(17)
+    rows, cols = 257, 1032
+    x = torch.randn(rows, cols, generator=gen)
+    w = torch.randn(cols, generator=gen).bfloat16()
+    col = torch.randn(rows, 1, generator=gen).half()
+    s = torch.tensor(0.75)
+    # eager semantics: every op rounds to its own result type
+    t1 = x * w.float()                                   # fp32
+    t2 = torch.tanh(t1)                                  # fp32
+    t3 = (t2 + 0.5 * col.float() * s).bfloat16()         # addcmul, rounded to bf16
+    want_a = (2.0 - t3.float()).bfloat16()               # bf16 output
+    want_b = torch.maximum(t2, x)                        # fp32 output
+    prog = abi.ew_program(4, [
+        (EwOp.MUL, 0, 1, 0, 0, torch.float32), (EwOp.TANH, 4, 0, 0, 0, torch.float32),
+        (EwOp.ADDCMUL, 5, 2, 3, 0.5, torch.bfloat16), (EwOp.RSUB_IMM, 6, 0, 0, 2.0, torch.bfloat16),
+        (EwOp.MAX, 5, 0, 0, 0, torch.float32)], [7, 8], [FULL, ROW, COL, SCALAR])
+    dx, dw, dcol, ds = cuda(x, w, col, s)
+    oa = torch.empty(rows, cols, dtype=torch.bfloat16, device=DEV)
+    ob = torch.empty(rows, cols, dtype=torch.float32, device=DEV)
+    abi.launch(Template.ELEMENTWISE, [dx, dw, dcol, ds], [oa, ob], prog)
+    assert_close(oa.float(), want_a.float(), BF16_TOL, "run-time instance, bf16 output")
+    assert_close(ob, want_b, F32_TOL, "run-time instance, fp32 output")
+    # +,-,*,/ only: bit-exact against eager, on a flat length that leaves a scalar tail
+    n = 8 * 4096 + 5
+    a, b = torch.randn(n, generator=gen), torch.randn(n, generator=gen) + 3.0
+    prog2 = abi.ew_program(2, [(EwOp.SUB, 0, 1, 0, 0, torch.float32), (EwOp.DIV, 2, 1, 0, 0, torch.float32),
+                               (EwOp.MUL_IMM, 3, 0, 0, 1.25, torch.float32)], [4])
+    da, db = cuda(a, b)
+    out = torch.empty_like(da)
+    abi.launch(Template.ELEMENTWISE, [da, db], [out], prog2)
+    assert bits_equal(out, ((a - b) / b) * 1.25)
+
+
 def test_two_outputs(executor):
     gen = torch.Generator().manual_seed(16)
     a, b = torch.randn(50, 40, generator=gen), torch.randn(50, 40, generator=gen)
