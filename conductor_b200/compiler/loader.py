@@ -29,8 +29,8 @@ SYMBOLS = {
     "cdr_last_error": (_c.c_char_p, []),
     "cdr_device_count": (_c.c_int, []),
     "cdr_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
-    "cdr_elementwise_source": (_c.c_int, [_TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_char_p,
-                                          _c.c_size_t, _c.c_int]),
+    "cdr_template_source": (_c.c_int, [_c.c_int, _TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,
+                                       _c.c_char_p, _c.c_size_t, _c.c_int]),
     "cdr_workspace_bytes": (_c.c_int, [_c.c_int, _TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,
                                        _c.POINTER(_c.c_size_t)]),
     "cdr_launch": (_c.c_int, [_c.c_int, _TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,

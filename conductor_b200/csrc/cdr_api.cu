@@ -18,6 +18,7 @@
 namespace cdr {
 
 std::string jit_elementwise_source(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E);
+std::string jit_row_reduce_source(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E, int64_t cols);
 std::vector<char> jit_compile(const std::string& src, std::string* log);
 int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out);
 
@@ -169,25 +170,38 @@ int cdr_device_status(int* status_out, int clear) {
   return *status_out ? CDR_ERR_TIMEOUT : CDR_OK;
 }
 
-int cdr_elementwise_source(const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs, int n_outputs,
-                           const void* params, size_t params_bytes, char* buffer, size_t buffer_bytes, int compile) {
+int cdr_template_source(int template_id, const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs, int n_outputs,
+                        const void* params, size_t params_bytes, char* buffer, size_t buffer_bytes, int compile) {
   g_error[0] = 0;
+  if (template_id != CDR_T_ELEMENTWISE && template_id != CDR_T_ROW_REDUCE) {
+    set_error("template %d has no run-time instances", template_id);
+    return CDR_ERR_UNSUPPORTED;
+  }
   if (int rc = check_lists(inputs, n_inputs, outputs, n_outputs)) return rc;
-  if (int rc = check_params(CDR_T_ELEMENTWISE, params, params_bytes)) return rc;
-  const cdr_ew_params* p = static_cast<const cdr_ew_params*>(params);
+  if (int rc = check_params(template_id, params, params_bytes)) return rc;
+  const bool reduce = template_id == CDR_T_ROW_REDUCE;
+  const cdr_ew_params* p = reduce ? &static_cast<const cdr_reduce_params*>(params)->chain : static_cast<const cdr_ew_params*>(params);
   if (int rc = validate_ew_program(p, n_inputs, n_outputs)) return rc;
+  if (reduce && (n_outputs != 1 || n_inputs < 1)) { set_error("row_reduce: needs >=1 input and exactly one output"); return CDR_ERR_BAD_ARG; }
   if (!buffer || buffer_bytes == 0) { set_error("buffer is null or empty"); return CDR_ERR_BAD_ARG; }
   int in_dt[CDR_EW_MAX_INPUTS] = {0}, out_dt[CDR_EW_MAX_OUTPUTS] = {0};
   bool any16 = false;
   for (int i = 0; i < n_inputs; ++i) { in_dt[i] = inputs[i].dtype; any16 |= dtype_size(in_dt[i]) == 2; }
-  for (int o = 0; o < n_outputs; ++o) { out_dt[o] = outputs[o].dtype; any16 |= dtype_size(out_dt[o]) == 2; }
+  for (int o = 0; o < n_outputs; ++o) { out_dt[o] = outputs[o].dtype; if (!reduce) any16 |= dtype_size(out_dt[o]) == 2; }
   for (int i = 0; i < n_inputs + n_outputs; ++i) {
     const int dt = i < n_inputs ? in_dt[i] : out_dt[i - n_inputs];
-    if (dt != CDR_F32 && dt != CDR_BF16 && dt != CDR_F16) { set_error("only floating-point chains are instantiated at run time"); return CDR_ERR_UNSUPPORTED; }
+    if (dt != CDR_F32 && dt != CDR_BF16 && dt != CDR_F16) { set_error("only floating-point programs are instantiated at run time"); return CDR_ERR_UNSUPPORTED; }
   }
   std::string src;
   try {
-    src = jit_elementwise_source(*p, in_dt, out_dt, any16 ? 8 : 4);
+    if (reduce) {
+      int64_t cols = 0;
+      for (int i = 0; i < n_inputs; ++i)
+        if (p->input_mode[i] == CDR_IN_FULL && inputs[i].rank >= 1) { cols = inputs[i].shape[inputs[i].rank - 1]; break; }
+      src = jit_row_reduce_source(*p, in_dt, out_dt[0], static_cast<const cdr_reduce_params*>(params)->reduce_op, any16 ? 8 : 4, cols);
+    } else {
+      src = jit_elementwise_source(*p, in_dt, out_dt, any16 ? 8 : 4);
+    }
     const size_t n = src.size() < buffer_bytes - 1 ? src.size() : buffer_bytes - 1;
     memcpy(buffer, src.data(), n);
     buffer[n] = 0;

@@ -148,12 +148,10 @@ std::string expr(const cdr_ew_instr& i) {
   }
 }
 
-// One thread handles UN units of E consecutive elements; all loads first, then math and stores.
-std::string generate(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E, int UN) {
-  std::string s = kPrelude;
+// The program on one element: registers become local constants, every op rounds to its result type.
+std::string chain_source(const cdr_ew_params& p) {
   const int nin = p.n_inputs;
-  // the chain on one element
-  s += "__device__ __forceinline__ void chain(const float* in, float* out) {\n";
+  std::string s = "__device__ __forceinline__ void chain(const float* in, float* out) {\n";
   for (int i = 0; i < nin; ++i) s += "  const float r" + std::to_string(i) + " = in[" + std::to_string(i) + "];\n";
   for (int k = 0; k < p.n_instr; ++k) {
     const int rt = p.instr[k].round_to == CDR_BF16 ? 1 : p.instr[k].round_to == CDR_F16 ? 2 : 0;
@@ -161,20 +159,38 @@ std::string generate(const cdr_ew_params& p, const int* in_dt, const int* out_dt
   }
   for (int o = 0; o < p.n_outputs; ++o) s += "  out[" + std::to_string(o) + "] = r" + std::to_string(p.out_reg[o]) + ";\n";
   s += "}\n";
+  return s;
+}
+
+// Vector loads of input `i` for one unit of E elements into `dst` (FULL and ROW inputs only).
+std::string vector_loads(int i, int dt, int mode, int E, const std::string& full_base, const std::string& row_base,
+                         const std::string& dst, const std::string& indent) {
+  const int V = dt_vec(dt);
+  const std::string I = std::to_string(i), T = dt_c(dt);
+  const std::string base = mode == CDR_IN_FULL ? full_base : row_base;
+  const std::string ld = mode == CDR_IN_FULL ? "ld_cs" : "ld_nc";
+  std::string s;
+  for (int k = 0; k < E / V; ++k)
+    s += indent + dt_un(dt) + "(" + ld + "((const " + T + "*)a.in[" + I + "] + " + base + " + " + std::to_string(k * V) + "), " +
+         dst + " + " + std::to_string(k * V) + ");\n";
+  return s;
+}
+
+// One thread handles UN units of E consecutive elements; all loads first, then math and stores.
+std::string generate(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E, int UN) {
+  std::string s = kPrelude;
+  const int nin = p.n_inputs;
+  s += chain_source(p);
   const std::string Es = std::to_string(E), UNs = std::to_string(UN);
   s += "extern \"C\" __global__ void __launch_bounds__(256) cdr_jit_k(const __grid_constant__ Args a) {\n";
   s += "  const i64 unit0 = (i64)blockIdx.x * (256 * " + UNs + ") + threadIdx.x;\n";
   s += "  float v[" + UNs + "][" + std::to_string(nin > 0 ? nin : 1) + "][" + Es + "];\n";
   s += "#pragma unroll\n  for (int u = 0; u < " + UNs + "; ++u) {\n    const i64 unit = unit0 + (i64)u * 256;\n    if (unit < a.n_units) {\n      const i64 e0 = unit * " + Es + ";\n";
   for (int i = 0; i < nin; ++i) {
-    const int dt = in_dt[i], V = dt_vec(dt), m = p.input_mode[i];
+    const int dt = in_dt[i], m = p.input_mode[i];
     const std::string I = std::to_string(i), T = dt_c(dt);
     if (m == CDR_IN_FULL || m == CDR_IN_ROW) {
-      const std::string base = m == CDR_IN_FULL ? "e0" : "(e0 % a.cols)";
-      const std::string ld = m == CDR_IN_FULL ? "ld_cs" : "ld_nc";
-      for (int k = 0; k < E / V; ++k)
-        s += "      " + std::string(dt_un(dt)) + "(" + ld + "((const " + T + "*)a.in[" + I + "] + " + base + " + " +
-             std::to_string(k * V) + "), v[u][" + I + "] + " + std::to_string(k * V) + ");\n";
+      s += vector_loads(i, dt, m, E, "e0", "(e0 % a.cols)", "v[u][" + I + "]", "      ");
     } else {
       const std::string idx = m == CDR_IN_COL ? "(e0 / a.cols)" : "0";
       s += "      { const float t = " + std::string(dt_scalar(dt)) + "(((const " + T + "*)a.in[" + I + "])[" + idx +
@@ -200,6 +216,63 @@ std::string generate(const cdr_ew_params& p, const int* in_dt, const int* out_dt
   return s;
 }
 
+// Chain + reduction over the last dimension.  G threads (one warp, or the whole 256-thread CTA)
+// share a row; a thread walks its row in chunks of U units of E elements, loads first, then math.
+// Args: n_units = rows, out[0] = one value per row.
+std::string generate_row_reduce(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E, int U, int G) {
+  std::string s = kPrelude;
+  const int nin = p.n_inputs;
+  s += chain_source(p);
+  const char* ident = reduce_op == CDR_RED_MAX ? "__uint_as_float(0xff800000u)" : reduce_op == CDR_RED_MIN ? "__uint_as_float(0x7f800000u)" : "0.0f";
+  const char* comb = reduce_op == CDR_RED_MAX ? "max_f" : reduce_op == CDR_RED_MIN ? "min_f" : "__fadd_rn";
+  s += std::string("__device__ __forceinline__ float comb(float x, float y) { return ") + comb + "(x, y); }\n";
+  const std::string Es = std::to_string(E), Us = std::to_string(U), Gs = std::to_string(G);
+  s += "extern \"C\" __global__ void __launch_bounds__(256) cdr_jit_k(const __grid_constant__ Args a) {\n";
+  s += "  constexpr int G = " + Gs + ", RPB = 256 / G, U = " + Us + ", E = " + Es + ";\n";
+  s += "  const int tg = threadIdx.x % G;\n";
+  s += "  const i64 row = (i64)blockIdx.x * RPB + threadIdx.x / G;\n";
+  s += "  const bool live = row < a.n_units;\n";
+  s += "  const i64 upr = a.cols / E;\n";
+  s += std::string("  float acc = ") + ident + ";\n";
+  s += "  if (live) {\n";
+  for (int i = 0; i < nin; ++i) {
+    const int m = p.input_mode[i];
+    if (m == CDR_IN_COL || m == CDR_IN_SCALAR)
+      s += "    const float s" + std::to_string(i) + " = " + dt_scalar(in_dt[i]) + "(((const " + dt_c(in_dt[i]) + "*)a.in[" +
+           std::to_string(i) + "])[" + (m == CDR_IN_COL ? "row" : "0") + "]);\n";
+  }
+  s += "    for (i64 u0 = tg; u0 < upr; u0 += (i64)G * U) {\n";
+  s += "      float v[U][" + std::to_string(nin) + "][E];\n";
+  s += "#pragma unroll\n      for (int u = 0; u < U; ++u) {\n        const i64 unit = u0 + (i64)u * G;\n        if (unit < upr) {\n";
+  s += "          const i64 c0 = unit * E;\n          const i64 e0 = row * a.cols + c0;\n";
+  for (int i = 0; i < nin; ++i) {
+    const int m = p.input_mode[i];
+    if (m == CDR_IN_FULL || m == CDR_IN_ROW)
+      s += vector_loads(i, in_dt[i], m, E, "e0", "c0", "v[u][" + std::to_string(i) + "]", "          ");
+  }
+  s += "        }\n      }\n";
+  s += "#pragma unroll\n      for (int u = 0; u < U; ++u) {\n        if (u0 + (i64)u * G < upr) {\n";
+  s += "#pragma unroll\n          for (int e = 0; e < E; ++e) {\n            float in[" + std::to_string(nin) + "], out[1];\n";
+  for (int i = 0; i < nin; ++i) {
+    const int m = p.input_mode[i];
+    const std::string I = std::to_string(i);
+    s += "            in[" + I + "] = " + ((m == CDR_IN_FULL || m == CDR_IN_ROW) ? "v[u][" + I + "][e]" : "s" + I) + ";\n";
+  }
+  s += "            chain(in, out);\n            acc = comb(acc, out[0]);\n          }\n        }\n      }\n    }\n  }\n";
+  s += "#pragma unroll\n  for (int o = 16; o > 0; o >>= 1) acc = comb(acc, __shfl_xor_sync(0xffffffffu, acc, o));\n";
+  if (G == 256) {
+    s += "  __shared__ float part[8];\n";
+    s += "  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;\n  __syncthreads();\n";
+    s += "  if (threadIdx.x == 0) {\n    acc = part[0];\n#pragma unroll\n    for (int w = 1; w < 8; ++w) acc = comb(acc, part[w]);\n  }\n";
+  }
+  s += "  if (live && tg == 0) {\n";
+  if (reduce_op == CDR_RED_MEAN) s += "    acc = __fdiv_rn(acc, (float)a.cols);\n";
+  if (out_dt == CDR_F32) s += "    ((float*)a.out[0])[row] = acc;\n";
+  else s += std::string("    ((u16*)a.out[0])[row] = (u16)") + (out_dt == CDR_BF16 ? "f2bf" : "f2h") + "(acc);\n";
+  s += "  }\n}\n";
+  return s;
+}
+
 struct JitKernel {
   CUfunction fn = nullptr;
   bool failed = false;
@@ -219,6 +292,14 @@ struct JitArgs {
 // Source text of the kernel that would be instantiated (for inspection and tests; needs no GPU).
 std::string jit_elementwise_source(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E) {
   return generate(p, in_dt, out_dt, E, E == 4 ? 4 : 2);
+}
+
+namespace {
+int row_group(int64_t cols, int E) { return cols / E >= 256 ? 256 : 32; }
+}  // namespace
+
+std::string jit_row_reduce_source(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E, int64_t cols) {
+  return generate_row_reduce(p, in_dt, out_dt, reduce_op, E, E == 4 ? 4 : 2, row_group(cols, E));
 }
 
 // Compile `src` to a cubin image for sm_100a; empty on failure (message in `log`).
@@ -248,49 +329,74 @@ std::vector<char> jit_compile(const std::string& src, std::string* log) {
   return cubin;
 }
 
-// Launch the JIT instance for this program on the vector path.  CDR_ERR_UNSUPPORTED means "no JIT
-// here, use the interpreter"; other non-zero codes are real failures.
+namespace {
+// Compiled instance of `src` on the current device; CDR_ERR_UNSUPPORTED when there is none.
+int get_kernel(const Api& A, const std::string& src, CUfunction* fn) {
+  int dev = 0;
+  CDR_CUDA_TRY(cudaGetDevice(&dev));
+  const std::string key = std::to_string(dev) + "#" + src;
+  std::lock_guard<std::mutex> lock(g_mu);
+  JitKernel& k = g_cache[key];
+  if (k.failed) return CDR_ERR_UNSUPPORTED;
+  if (!k.fn) {
+    std::string log;
+    const std::vector<char> cubin = jit_compile(src, &log);
+    CUmodule mod = nullptr;
+    if (cubin.empty() || A.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS ||
+        A.ModuleGetFunction(&k.fn, mod, "cdr_jit_k") != CUDA_SUCCESS) {
+      k.failed = true;
+      k.fn = nullptr;
+      if (getenv("CDR_JIT_VERBOSE")) fprintf(stderr, "conductor_b200: JIT failed, using the interpreter\n%s\n", log.c_str());
+      return CDR_ERR_UNSUPPORTED;
+    }
+  }
+  *fn = k.fn;
+  return CDR_OK;
+}
+
+int launch_jit(const Api& A, CUfunction fn, JitArgs& args, int64_t grid, cudaStream_t stream, const char* who) {
+  if (grid > 0x7fffffff) return CDR_ERR_UNSUPPORTED;
+  void* params[] = {&args};
+  const CUresult r = A.LaunchKernel(fn, static_cast<unsigned>(grid), 1, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(stream),
+                                    params, nullptr);
+  if (r != CUDA_SUCCESS) { set_error("%s: run-time instance launch failed with %d", who, static_cast<int>(r)); return CDR_ERR_CUDA; }
+  return CDR_OK;
+}
+}  // namespace
+
+// Launch the run-time instance for this program on the vector path.  CDR_ERR_UNSUPPORTED means
+// "no instance here, use the interpreter"; other non-zero codes are real failures.
 int launch_elementwise_jit(const void* const* in, void* const* out, const int* in_dt, const int* out_dt,
                            const cdr_ew_params& p, int64_t n_units, int64_t cols, int E, cudaStream_t stream) {
   const Api& A = api();
   if (!A.ok) return CDR_ERR_UNSUPPORTED;
   const int UN = E == 4 ? 4 : 2;
-  int dev = 0;
-  CDR_CUDA_TRY(cudaGetDevice(&dev));
-  const std::string src = generate(p, in_dt, out_dt, E, UN);
-  const std::string key = std::to_string(dev) + "#" + src;
   CUfunction fn = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_mu);
-    JitKernel& k = g_cache[key];
-    if (k.failed) return CDR_ERR_UNSUPPORTED;
-    if (!k.fn) {
-      std::string log;
-      const std::vector<char> cubin = jit_compile(src, &log);
-      CUmodule mod = nullptr;
-      if (cubin.empty() || A.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS ||
-          A.ModuleGetFunction(&k.fn, mod, "cdr_jit_k") != CUDA_SUCCESS) {
-        k.failed = true;
-        k.fn = nullptr;
-        if (getenv("CDR_JIT_VERBOSE")) fprintf(stderr, "conductor_b200: JIT failed, using the interpreter\n%s\n", log.c_str());
-        return CDR_ERR_UNSUPPORTED;
-      }
-    }
-    fn = k.fn;
-  }
+  if (int rc = get_kernel(A, generate(p, in_dt, out_dt, E, UN), &fn)) return rc;
   JitArgs args{};
   for (int i = 0; i < p.n_inputs; ++i) args.in[i] = in[i];
   for (int o = 0; o < p.n_outputs; ++o) args.out[o] = out[o];
   args.n_units = n_units;
   args.cols = cols;
   const int64_t per_cta = 256LL * UN;
-  const int64_t grid = (n_units + per_cta - 1) / per_cta;
-  if (grid > 0x7fffffff) return CDR_ERR_UNSUPPORTED;
-  void* params[] = {&args};
-  const CUresult r = A.LaunchKernel(fn, static_cast<unsigned>(grid), 1, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(stream),
-                                    params, nullptr);
-  if (r != CUDA_SUCCESS) { set_error("elementwise JIT launch failed with %d", static_cast<int>(r)); return CDR_ERR_CUDA; }
-  return CDR_OK;
+  return launch_jit(A, fn, args, (n_units + per_cta - 1) / per_cta, stream, "elementwise");
+}
+
+// Chain + last-dimension reduction; every FULL/ROW input 16-byte aligned and cols % E == 0.
+int launch_row_reduce_jit(const void* const* in, void* out, const int* in_dt, int out_dt, const cdr_ew_params& p,
+                          int reduce_op, int64_t rows, int64_t cols, int E, cudaStream_t stream) {
+  const Api& A = api();
+  if (!A.ok) return CDR_ERR_UNSUPPORTED;
+  const int G = row_group(cols, E);
+  CUfunction fn = nullptr;
+  if (int rc = get_kernel(A, generate_row_reduce(p, in_dt, out_dt, reduce_op, E, E == 4 ? 4 : 2, G), &fn)) return rc;
+  JitArgs args{};
+  for (int i = 0; i < p.n_inputs; ++i) args.in[i] = in[i];
+  args.out[0] = out;
+  args.n_units = rows;
+  args.cols = cols;
+  const int64_t rpb = 256 / G;
+  return launch_jit(A, fn, args, (rows + rpb - 1) / rpb, stream, "row_reduce");
 }
 
 }  // namespace cdr

@@ -22,6 +22,8 @@
 namespace cdr {
 
 int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out);
+int launch_row_reduce_jit(const void* const* in, void* out, const int* in_dt, int out_dt, const cdr_ew_params& p,
+                          int reduce_op, int64_t rows, int64_t cols, int E, cudaStream_t stream);
 int64_t expected_input_numel(int mode, int64_t n, int64_t cols);
 
 namespace {
@@ -484,6 +486,22 @@ int launch_row_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, i
 
   GenArgs g{};
   fill_gen_args(g, ins, n_in, out, p, rows, cols);
+
+  // no ahead-of-time instance: instantiate the vector skeleton for this program at run time
+  {
+    bool any16 = false, ok = true;
+    for (int i = 0; i < n_in; ++i) any16 |= dtype_size(ins[i].dtype) == 2;
+    const int E = any16 ? 8 : 4;
+    for (int i = 0; i < n_in; ++i) {
+      const int m = p->chain.input_mode[i];
+      if (m == CDR_IN_FULL || m == CDR_IN_ROW) ok &= aligned16(ins[i].data);
+    }
+    if (ok && cols % E == 0) {
+      const int rc = launch_row_reduce_jit(g.in, g.out, g.in_dtype, g.out_dtype, p->chain, p->reduce_op, rows, cols, E, stream);
+      if (rc != CDR_ERR_UNSUPPORTED) return rc;
+    }
+  }
+
   int64_t grid = rows;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   if (grid > cap) grid = cap;

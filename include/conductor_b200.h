@@ -202,16 +202,17 @@ CDR_API int cdr_device_count(void);
  * `future` misuse detection of the reference runtime header (choreo-headers/choreo.h:1013-1112). */
 CDR_API int cdr_device_status(int* status_out, int clear);
 
-/* CUDA source of the kernel instance an elementwise program would run when it has no
+/* CUDA source of the kernel instance an elementwise or row-reduce program runs when it has no
  * ahead-of-time instance (the hand-written streaming skeleton specialised with the program),
  * written NUL-terminated into `buffer` (truncated to buffer_bytes).  With `compile` != 0 the source
  * is also compiled for sm_100a with NVRTC -- no GPU needed -- and CDR_ERR_UNSUPPORTED is returned
- * with the compiler log in cdr_last_error() if that fails.  Only dtypes and the program are read
- * from the descriptors.  Replaces the generated-DSL dump of the reference
+ * with the compiler log in cdr_last_error() if that fails.  Only dtypes, the last dimension and the
+ * program are read from the descriptors.  template_id is CDR_T_ELEMENTWISE or CDR_T_ROW_REDUCE.
+ * Replaces the generated-DSL dump of the reference
  * (conductor/codegen/dslgen.py:154-177 generate_dsl_file, conductor/utils/artifacts.py:18-237). */
-CDR_API int cdr_elementwise_source(const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,
-                                   int n_outputs, const void* params, size_t params_bytes, char* buffer,
-                                   size_t buffer_bytes, int compile);
+CDR_API int cdr_template_source(int template_id, const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,
+                                int n_outputs, const void* params, size_t params_bytes, char* buffer,
+                                size_t buffer_bytes, int compile);
 
 /* Bytes of device workspace cdr_launch() needs for this call (0 for most
  * templates).  Replaces the fixed `memory_pool_size_mb` of the reference runtime

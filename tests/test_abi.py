@@ -73,26 +73,39 @@ def test_generated_elementwise_source_compiles_without_a_gpu(built_library):
     pp, ps = ctypes.cast(ctypes.byref(prog), ctypes.c_void_p), ctypes.sizeof(prog)
     buf = ctypes.create_string_buffer(1 << 16)
     ind, outd = make_descriptors([x, w, col]), make_descriptors([out])
-    rc = lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, buf, len(buf), 0)
+    rc = lib.cdr_template_source(1, ind, 3, outd, 1, pp, ps, buf, len(buf), 0)
     assert rc == 0, lib.cdr_last_error()
     src = buf.value.decode()
     assert "cdr_jit_k" in src and "tanhf" in src and "un_bf16" in src and "% a.cols" in src
     # compile when NVRTC is installed; the library reports its absence as "unsupported"
-    rc = lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, buf, len(buf), 1)
+    rc = lib.cdr_template_source(1, ind, 3, outd, 1, pp, ps, buf, len(buf), 1)
     if rc != 0:
         assert rc == -2 and b"NVRTC" in lib.cdr_last_error()
         if b"not available" not in lib.cdr_last_error():
             pytest.fail(lib.cdr_last_error().decode())
     # truncation keeps the terminator; integer programs have no run-time instance
     small = ctypes.create_string_buffer(32)
-    assert lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, small, len(small), 0) == 0
+    assert lib.cdr_template_source(1, ind, 3, outd, 1, pp, ps, small, len(small), 0) == 0
     assert len(small.value) == 31
     xi = torch.zeros(8, 16, dtype=torch.int32)
     iprog = abi.ew_program(1, [(EwOp.ADD, 0, 0, 0, 0, torch.int32)], [1])
-    assert lib.cdr_elementwise_source(make_descriptors([xi]), 1, make_descriptors([xi]), 1,
+    assert lib.cdr_template_source(1, make_descriptors([xi]), 1, make_descriptors([xi]), 1,
                                       ctypes.cast(ctypes.byref(iprog), ctypes.c_void_p), ctypes.sizeof(iprog),
                                       buf, len(buf), 0) == -2
-    assert lib.cdr_elementwise_source(ind, 3, outd, 1, pp, ps, None, 0, 0) == -1
+    assert lib.cdr_template_source(1, ind, 3, outd, 1, pp, ps, None, 0, 0) == -1
+    assert lib.cdr_template_source(5, ind, 3, outd, 1, pp, ps, buf, len(buf), 0) == -2
+    # chain + reduction over the last dimension: warp-per-row and CTA-per-row skeletons, every reduce op
+    for cols in (64, 4096):
+        for op in (1, 2, 3, 4):
+            xr, wr = torch.zeros(4, cols, dtype=torch.bfloat16), torch.zeros(cols)
+            rp = kt.CdrReduceParams()
+            rp.chain = abi.ew_program(2, [(EwOp.MUL, 0, 1, 0, 0, torch.float32), (EwOp.EXP, 2, 0, 0, 0, torch.float32)],
+                                      [3], [abi.FULL, abi.ROW])
+            rp.reduce_op = op
+            rc = lib.cdr_template_source(2, make_descriptors([xr, wr]), 2, make_descriptors([torch.zeros(4)]), 1,
+                                         ctypes.cast(ctypes.byref(rp), ctypes.c_void_p), ctypes.sizeof(rp), buf, len(buf), 1)
+            assert rc == 0 or b"not available" in lib.cdr_last_error(), lib.cdr_last_error()
+            assert ("G = 256" if cols == 4096 else "G = 32") in buf.value.decode()
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

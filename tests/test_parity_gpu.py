@@ -244,6 +244,35 @@ def test_row_sum_max_fp32(executor):
         assert_close(out, want, F32_TOL, f"row reduce op {op}")
 
 
+@pytest.mark.parametrize("rows,cols", [(37, 64), (9, 1024), (5, 4104), (3, 70000)])
+def test_row_reduce_runtime_instance(executor, rows, cols):
+    """Chains with no ahead-of-time reduce instance on vector-shaped rows (warp-per-row and
+    CTA-per-row skeletons): mixed dtypes, every reduce op, NaN propagation through max."""
+    gen = torch.Generator().manual_seed(24)
+    x = torch.randn(rows, cols, generator=gen).bfloat16()
+    w = torch.randn(cols, generator=gen)
+    col = torch.randn(rows, 1, generator=gen)
+    val = torch.sigmoid(x.float() * w) - col                       # fp32 chain over a bf16 input
+    chain = abi.ew_program(3, [(EwOp.MUL, 0, 1, 0, 0, torch.float32), (EwOp.SIGMOID, 3, 0, 0, 0, torch.float32),
+                               (EwOp.SUB, 4, 2, 0, 0, torch.float32)], [5], [FULL, ROW, COL])
+    dx, dw, dcol = cuda(x, w, col)
+    for op, want in ((ReduceOp.SUM, val.double().sum(-1).float()), (ReduceOp.MEAN, val.double().mean(-1).float()),
+                     (ReduceOp.MAX, val.amax(-1)), (ReduceOp.MIN, val.amin(-1))):
+        out = torch.empty(rows, device=DEV)
+        abi.launch(Template.ROW_REDUCE, [dx, dw, dcol], [out], reduce_params(chain, op))
+        tol = F32_TOL * max(1.0, float(want.abs().max())) if op == ReduceOp.SUM else F32_TOL
+        assert_close(out, want, tol, f"row reduce run-time instance op {op} {rows}x{cols}")
+    # NaN in one row poisons that row's max only; bf16 output rounds once at the end
+    xn = x.clone()
+    xn[rows // 2, cols - 3] = float("nan")
+    out = torch.empty(rows, dtype=torch.bfloat16, device=DEV)
+    abi.launch(Template.ROW_REDUCE, [xn.to(DEV), dw, dcol], [out], reduce_params(chain, ReduceOp.MAX))
+    got = out.cpu().float()
+    assert torch.isnan(got[rows // 2]) and int(torch.isnan(got).sum()) == 1
+    keep = torch.arange(rows) != rows // 2
+    assert_close(got[keep], val.amax(-1).bfloat16().float()[keep], BF16_TOL, "bf16 row max")
+
+
 def test_full_reduce_with_workspace(executor):
     gen = torch.Generator().manual_seed(23)
     x = torch.randn(300, 517, generator=gen)
