@@ -141,64 +141,87 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this code convergently and one elected lane issues the tcgen05
+    // instructions: with warp-uniform control flow the operand descriptors live in uniform
+    // registers, where tcgen05.mma reads them, instead of being moved there before every
+    // instruction (measured: ~95 cycles per MMA issued from a single-lane branch, more than the
+    // 64 cycles a 128x128x16 MMA executes in).
+    {
+      const bool leader = sm100::elect_one();
       constexpr uint32_t idesc_s = sm100::umma_idesc_f16(BH_ROWS, BKV, BF16, false, false);
       constexpr uint32_t idesc_o = sm100::umma_idesc_f16(BH_ROWS, HD, BF16, false, true);  // V is MN-major
-      bool ok = sm100::mbar_wait(&bars[B_QFULL], 0);
-      if (!ok) sm100::report_timeout(a.status, 22);
+      // every lane waits; the vote makes the outcome provably uniform
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+        const bool done = __all_sync(0xffffffffu, sm100::mbar_wait(bar, parity));
+        if (!done && leader) sm100::report_timeout(a.status, site);
+        return done;
+      };
+      bool ok = wait_all(&bars[B_QFULL], 0, 22);
 
       // S_h(j) = Q_h K_j^T; the caller has already waited for K_j
       auto issue_s = [&](int h, int j) {
         const uint32_t q_addr = sm100::smem_u32(smem + L::Q_OFF + h * L::TILE_BYTES);
         const uint32_t k_addr = sm100::smem_u32(smem + L::KV_OFF + ((2 * j) % KV_STAGES) * L::TILE_BYTES);
         const uint32_t d = tmem_base + TMEM_S + h * 128;
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * (128 * 128) + (kk % 4) * 32;
-          sm100::umma_f16_ss(d, sm100::umma_desc_k_sw128(q_addr + off), sm100::umma_desc_k_sw128(k_addr + off), idesc_s,
-                             kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * (128 * 128) + (kk % 4) * 32;
+            sm100::umma_f16_ss(d, sm100::umma_desc_k_sw128(q_addr + off), sm100::umma_desc_k_sw128(k_addr + off), idesc_s,
+                               kk > 0 ? 1u : 0u);
+          }
+          sm100::umma_commit(&bars[B_SFULL + h]);
         }
-        sm100::umma_commit(&bars[B_SFULL + h]);
+        __syncwarp();
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) sm100::umma_commit(bar);
+        __syncwarp();
       };
 
-      auto wait_tile = [&](int i, int site) -> bool {
-        if (sm100::mbar_wait(&bars[B_FULL + i % KV_STAGES], (i / KV_STAGES) & 1)) return true;
-        sm100::report_timeout(a.status, site);
-        return false;
-      };
-      if (ok && n_iter > 0) ok = wait_tile(0, 23);
+      if (ok && n_iter > 0) ok = wait_all(&bars[B_FULL + 0], 0, 23);
       if (ok && n_iter > 0) {
         sm100::tc_fence_after();
         for (int h = 0; h < 2; ++h)
           if (nblk[h] > 0) issue_s(h, 0);
-        sm100::umma_commit(&bars[B_EMPTY + 0]);          // K_0 free once both S(0) are done
+        commit(&bars[B_EMPTY + 0]);          // K_0 free once both S(0) are done
       }
       for (int j = 0; j < n_iter && ok; ++j) {
         const bool next = j + 1 < n_iter;
         const int vt = 2 * j + 1, kt = 2 * j + 2;       // ring tiles of V_j and K_(j+1)
-        if (!wait_tile(vt, 25)) break;
+        ok = wait_all(&bars[B_FULL + vt % KV_STAGES], (vt / KV_STAGES) & 1, 25);
+        if (!ok) break;
         bool k_ready = false;
         const uint32_t v_addr = sm100::smem_u32(smem + L::KV_OFF + (vt % KV_STAGES) * L::TILE_BYTES);
         for (int h = 0; h < 2 && ok; ++h) {
           if (j < nblk[h]) {
-            if (!sm100::mbar_wait(&bars[B_PFULL + h], j & 1)) { sm100::report_timeout(a.status, 26); ok = false; break; }
+            ok = wait_all(&bars[B_PFULL + h], j & 1, 26);
+            if (!ok) break;
             sm100::tc_fence_after();
             const uint32_t p_tmem = tmem_base + TMEM_S + h * 128;   // packed bf16 pairs: 8 columns per 16 keys
+            if (leader) {
 #pragma unroll
-            for (int kk = 0; kk < BKV / 16; ++kk) {
-              const uint64_t vdesc = sm100::umma_desc_mn_sw128(v_addr + kk * (16 * 128), 128 * 128);
-              sm100::umma_f16_ts(tmem_base + TMEM_O + h * 128, p_tmem + kk * 8, vdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+              for (int kk = 0; kk < BKV / 16; ++kk) {
+                const uint64_t vdesc = sm100::umma_desc_mn_sw128(v_addr + kk * (16 * 128), 128 * 128);
+                sm100::umma_f16_ts(tmem_base + TMEM_O + h * 128, p_tmem + kk * 8, vdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+              }
+              sm100::umma_commit(&bars[B_PVDONE + h]);
             }
-            sm100::umma_commit(&bars[B_PVDONE + h]);
+            __syncwarp();
           }
           if (next && j + 1 < nblk[h]) {
-            if (!k_ready) { ok = wait_tile(kt, 24); if (!ok) break; k_ready = true; sm100::tc_fence_after(); }
+            if (!k_ready) {
+              ok = wait_all(&bars[B_FULL + kt % KV_STAGES], (kt / KV_STAGES) & 1, 24);
+              if (!ok) break;
+              k_ready = true;
+              sm100::tc_fence_after();
+            }
             issue_s(h, j + 1);
           }
         }
         if (!ok) break;
-        sm100::umma_commit(&bars[B_EMPTY + vt % KV_STAGES]);
-        if (next) sm100::umma_commit(&bars[B_EMPTY + kt % KV_STAGES]);
+        commit(&bars[B_EMPTY + vt % KV_STAGES]);
+        if (next) commit(&bars[B_EMPTY + kt % KV_STAGES]);
       }
     }
   } else {

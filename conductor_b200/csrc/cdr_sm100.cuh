@@ -66,9 +66,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
+// Non-blocking test of a phase (mbarrier.test_wait never suspends the thread).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 // Bounded wait.  try_wait itself blocks for a hardware-defined slice, so kMaxPolls polls are
 // far beyond any legitimate wait (seconds) yet still finite.
-constexpr uint32_t kMaxPolls = 1u << 24;
+#ifndef CDR_MAX_POLLS
+#define CDR_MAX_POLLS (1u << 24)
+#endif
+constexpr uint32_t kMaxPolls = CDR_MAX_POLLS;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kMaxPolls; ++i)
     if (mbar_try_wait(bar, parity)) return true;
