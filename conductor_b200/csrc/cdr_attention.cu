@@ -8,17 +8,28 @@
 // Tensor-core bound.  One CTA per (batch*head, 256-query tile), handled as two 128-row halves
 // A and B that share every K/V block (halving operand traffic per flop) and ping-pong on the
 // tensor core: while the softmax warps of one half work, the MMAs of the other half run.
-//   warp 0      TMA producer: both Q halves once, then K_j and V_j into two-stage rings
+//   warp 0      TMA producer: both Q halves once, then K_j and V_j through one 5-stage ring
 //   warp 1      MMA issuer:  S_h = Q_h K_j^T (fp32 in TMEM) and O_h += P_h V_j, where P_h is
-//               read straight from TMEM (it overwrites the S_h columns as packed bf16)
-//   warps 2-5   softmax of half A, warps 6-9 of half B: one query row per thread; tcgen05.ld
-//               the S row, running max / sum in the log2 domain, P = exp2(..) stored back to
-//               TMEM with tcgen05.st; the O accumulator stays in TMEM and is rescaled only when
-//               the running max grew by more than 2^8 (exact after the final division)
+//               read straight from TMEM (it overwrites the S_h columns as packed bf16).  The whole
+//               warp runs the loop convergently and an elected lane issues, which keeps the
+//               operand descriptors in uniform registers (a single-lane branch cost ~95 cycles
+//               per MMA, more than the 64 cycles a 128x128x16 MMA executes in)
+//   warps 2-3   idle: they complete the control warp group so that setmaxnreg can hand its
+//               registers (80 per thread kept) to the softmax groups (208 per thread, no spills)
+//   warps 4-7   softmax of half A, warps 8-11 of half B: one query row per thread; tcgen05.ld
+//               the S row, running max (3-input max) / sum in the log2 domain, P = exp2(..) with
+//               two-lane fp32 instructions and one pair in eight on the FMA pipes (cubic) to take
+//               load off the special-function unit, stored back to TMEM with tcgen05.st; the O
+//               accumulator stays in TMEM and is rescaled only when the
+//               running max grew by more than 2^8 (exact after the final division)
 // TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511.  MMAs of one CTA execute in
 // issue order, so reusing the S_h columns for S_h(j+1) after P_h(j) needs no extra barrier.
 // Causal work is triangular, so CTAs are numbered heaviest tile first.  No load is multicast;
 // every wait is bounded and reports through the device status word.
+// Measured alternatives that lost: persistent CTAs with a polling issuer (-8 %), 64-key blocks
+// with P double-buffered beside S (-50 %: the tensor core accepts about one MMA per 90 cycles
+// whatever its N, so halving N halves the rate), 16 softmax warps sharing rows (-13 %), P handed
+// over in two parts of 64 keys so that half of P.V starts early (-1.5 %).
 #include <cuda.h>
 #include <math.h>
 
@@ -33,7 +44,19 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t 
 namespace {
 
 constexpr int BQ = 256, BH_ROWS = 128, BKV = 128;   // query tile, rows per half, keys per block
+#ifndef CDR_ATT_WG
+#define CDR_ATT_WG 1
+#endif
+#if CDR_ATT_WG
+// Roles aligned to warp groups so that setmaxnreg can move registers from the control warps to the
+// softmax warps: group 0 = TMA warp, MMA warp and two idle warps; groups 1, 2 = softmax of half A, B.
+constexpr int ATT_THREADS = 384;
+constexpr int SOFTMAX_WARP0 = 4;
+constexpr int REGS_CONTROL = 80, REGS_SOFTMAX = 208;   // 128*80 + 256*208 <= 384*168, the CTA's allocation at launch
+#else
 constexpr int ATT_THREADS = 320;
+constexpr int SOFTMAX_WARP0 = 2;
+#endif
 constexpr int TMEM_S = 0, TMEM_O = 256, ATT_TMEM_COLS = 512;   // + 128 * half
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -67,11 +90,74 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+#ifndef CDR_ATT_EMU
+#define CDR_ATT_EMU 1   // pairs of every 8 whose exp2 runs on the FMA pipes
+#endif
+
+// ---- two fp32 lanes per instruction (fma/add/sub .f32x2) and the three-input max of sm_100
+__device__ __forceinline__ uint64_t pack2(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) { uint64_t d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+
+// 2^x for a pair on the FMA pipes instead of the special-function unit: x = n + f with n the
+// nearest integer (magic-number rounding) and f in [-0.5, 0.5]; 2^f by a cubic (max relative error
+// 7.5e-5, far inside the 2^-9 of the 16-bit P it feeds); n goes straight into the exponent field.
+// Inputs are clamped to -125 so the exponent cannot wrap.
+__device__ __forceinline__ void poly_exp2_pair(uint64_t x, float& p0, float& p1) {
+  float x0, x1;
+  unpack2(x, x0, x1);
+  x = pack2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+  const uint64_t magic = pack2(12582912.0f, 12582912.0f);
+  const uint64_t t = add2(x, magic);
+  const uint64_t f = sub2(x, sub2(t, magic));
+  uint64_t r = fma2(pack2(0.055171459913253784f, 0.055171459913253784f), f, pack2(0.2426108568906784f, 0.2426108568906784f));
+  r = fma2(r, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+  r = fma2(r, f, pack2(0.9999281167984009f, 0.9999281167984009f));
+  float t0, t1, r0, r1;
+  unpack2(t, t0, t1);
+  unpack2(r, r0, r1);
+  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
   if (BF16) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
   __half2 t = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// P = exp2(s*c - m) for one row's 128 scores, packed to 16-bit pairs and stored over the S columns the
+// row just read (`p_taddr`); row sums accumulate in two fp32 lanes.  EMU of every 8 pairs take the polynomial path,
+// the rest the special-function unit.
+template <bool BF16, int EMU>
+__device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2, float neg_m, float& l0, float& l1, uint32_t p_taddr) {
+  const uint64_t scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
+  uint64_t lsum = pack2(l0, l1);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t pw[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float p0, p1;
+      const uint64_t x = fma2(pack2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2);
+      if ((i & 7) < EMU) {
+        poly_exp2_pair(x, p0, p1);
+      } else {
+        float x0, x1;
+        unpack2(x, x0, x1);
+        p0 = fast_exp2(x0);
+        p1 = fast_exp2(x1);
+      }
+      lsum = add2(lsum, pack2(p0, p1));
+      pw[i] = pack_pair<BF16>(p0, p1);
+    }
+    sm100::tmem_st16(p_taddr + c * 16, pw);
+  }
+  unpack2(lsum, l0, l1);
 }
 
 template <int HD, bool BF16>
@@ -116,6 +202,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   sm100::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+#if CDR_ATT_WG
+  // one setmaxnreg per warp group, executed by all four of its warps
+  if (warp < SOFTMAX_WARP0) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CONTROL));
+#endif
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -224,9 +314,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         if (next) commit(&bars[B_EMPTY + kt % KV_STAGES]);
       }
     }
-  } else {
+  } else if (warp >= SOFTMAX_WARP0) {
+#if CDR_ATT_WG
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
+#endif
     // ------------------------------------------------------------ softmax / correction / epilogue
-    const int g = (warp - 2) >> 2;       // half this warp group serves
+    const int g = (warp - SOFTMAX_WARP0) >> 2;       // half this warp group serves
     const int q = warp & 3;              // TMEM lane quadrant
     const int n_my = nblk[g];
     const int row_in_half = q * 32 + lane;
@@ -260,11 +353,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
             bmax = fmaxf(bmax, v);
           }
       } else {
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains of 3-input max
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sr[c][i]));
+          for (int i = 0; i < 16; ++i)
+            mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
         bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       }
       bmax *= a.scale_log2;  // scale > 0: max commutes with the scaling
@@ -289,21 +383,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         }
       }
 
-      // P = exp2(s*c - m) as packed 16-bit pairs, stored over the S columns this row just read
+      // masked blocks keep the special-function path: exp2(-inf) must be exactly 0
       const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pw[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i]), a.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i + 1]), a.scale_log2, neg_m));
-          l0 += p0;
-          l1 += p1;
-          pw[i] = pack_pair<BF16>(p0, p1);
-        }
-        sm100::tmem_st16(s_taddr + c * 16, pw);
-      }
+      if (need_mask) store_p<BF16, 0>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
+      else store_p<BF16, CDR_ATT_EMU>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
       sm100::tmem_st_wait();
       sm100::tc_fence_before();
       __syncwarp();

@@ -201,30 +201,44 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop convergently and one elected lane issues the tcgen05
+    // instructions, so the operand descriptors stay in uniform registers.
+    {
+      const bool leader = sm100::elect_one();
       constexpr uint32_t idesc = sm100::umma_idesc_f16(BM, BN, BF16, false, false);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
         const uint32_t as = tile_iter % ACC_STAGES, aph = (tile_iter / ACC_STAGES) & 1;
-        if (!sm100::mbar_wait(&acc_empty[as], aph ^ 1)) { sm100::report_timeout(a.status, 11); break; }
+        if (!__all_sync(0xffffffffu, sm100::mbar_wait(&acc_empty[as], aph ^ 1))) {
+          if (leader) sm100::report_timeout(a.status, 11);
+          break;
+        }
         sm100::tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-          if (!sm100::mbar_wait(&full[s], ph)) { sm100::report_timeout(a.status, 12); ok = false; break; }
+          if (!__all_sync(0xffffffffu, sm100::mbar_wait(&full[s], ph))) {
+            if (leader) sm100::report_timeout(a.status, 12);
+            ok = false;
+            break;
+          }
           sm100::tc_fence_after();
           const uint32_t a_addr = sm100::smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
-            const uint64_t bdesc = sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
-            sm100::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
+              const uint64_t bdesc = sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
+              sm100::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            sm100::umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
           }
-          sm100::umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+          __syncwarp();
         }
-        if (ok) sm100::umma_commit(&acc_full[as]);
+        if (ok && leader) sm100::umma_commit(&acc_full[as]);
+        __syncwarp();
       }
     }
   } else {
