@@ -94,6 +94,17 @@ def test_generated_elementwise_source_compiles_without_a_gpu(built_library):
                                       buf, len(buf), 0) == -2
     assert lib.cdr_template_source(1, ind, 3, outd, 1, pp, ps, None, 0, 0) == -1
     assert lib.cdr_template_source(5, ind, 3, outd, 1, pp, ps, buf, len(buf), 0) == -2
+    # an all-bf16 chain of exactly-rounding ops is emitted on bf16x2 instructions
+    xb, wb = torch.zeros(8, 16, dtype=torch.bfloat16), torch.zeros(16, dtype=torch.bfloat16)
+    pprog = abi.ew_program(2, [(EwOp.MUL, 0, 1, 0, 0, torch.bfloat16), (EwOp.RELU, 2, 0, 0, 0, torch.bfloat16),
+                               (EwOp.ADD_IMM, 3, 0, 0, 1.5, torch.bfloat16)], [4], [abi.FULL, abi.ROW])
+    args = (make_descriptors([xb, wb]), 2, make_descriptors([xb]), 1, ctypes.cast(ctypes.byref(pprog), ctypes.c_void_p),
+            ctypes.sizeof(pprog), buf, len(buf))
+    rc = lib.cdr_template_source(1, *args, 1)
+    assert rc == 0 or b"not available" in lib.cdr_last_error(), lib.cdr_last_error()
+    assert "= bmul(r0, r1)" in buf.value.decode() and "0x3fc03fc0u" in buf.value.decode()
+    pprog.instr[2].imm = 0.1     # not a bf16 value: eager adds the fp32 constant, so no packed form
+    assert lib.cdr_template_source(1, *args, 0) == 0 and "= bmul(r0, r1)" not in buf.value.decode()
     # chain + reduction over the last dimension: warp-per-row and CTA-per-row skeletons, every reduce op
     for cols in (64, 4096):
         for op in (1, 2, 3, 4):

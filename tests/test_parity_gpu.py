@@ -161,6 +161,47 @@ def test_runtime_instance_mixed_dtypes_and_tail(executor):
     assert bits_equal(out, ((a - b) / b) * 1.25)
 
 
+def test_packed_bf16_chain_bit_exact(executor):
+    """All-bf16 chains of +,-,*,relu,neg,abs,max,min run on bf16x2 instructions in their run-time
+    instance; every op must round exactly like eager (fp32 op, then round to bf16), NaN included."""
+    gen = torch.Generator().manual_seed(18)
+    rows, cols = 129, 520
+    x = (torch.randn(rows, cols, generator=gen) * 3).bfloat16()
+    w = torch.randn(cols, generator=gen).bfloat16()
+    b = torch.randn(cols, generator=gen).bfloat16()
+    col = torch.randn(rows, 1, generator=gen).bfloat16()
+    x[3, 7] = float("nan")
+    x[5, 9] = float("inf")
+    x[6, 11] = 1e-39        # bf16 subnormal
+    t = torch.relu(x * w - b) + 1.5                      # eager bf16: each op rounds
+    want1 = torch.minimum(torch.maximum(-t, col), torch.abs(x))
+    want2 = 2.0 - t * 0.5
+    bf = torch.bfloat16
+    prog = abi.ew_program(4, [
+        (EwOp.MUL, 0, 1, 0, 0, bf), (EwOp.SUB, 4, 2, 0, 0, bf), (EwOp.RELU, 5, 0, 0, 0, bf), (EwOp.ADD_IMM, 6, 0, 0, 1.5, bf),
+        (EwOp.NEG, 7, 0, 0, 0, bf), (EwOp.MAX, 8, 3, 0, 0, bf), (EwOp.ABS, 0, 0, 0, 0, bf), (EwOp.MIN, 9, 10, 0, 0, bf),
+        (EwOp.MUL_IMM, 7, 0, 0, 0.5, bf), (EwOp.RSUB_IMM, 12, 0, 0, 2.0, bf)], [11, 13], [FULL, ROW, ROW, COL])
+    dx, dw, db, dcol = cuda(x, w, b, col)
+    o1, o2 = torch.empty_like(dx), torch.empty_like(dx)
+    abi.launch(Template.ELEMENTWISE, [dx, dw, db, dcol], [o1, o2], prog)
+    for got, want, name in ((o1, want1, "min/max/abs"), (o2, want2, "imm ops")):
+        g, e = got.cpu(), want
+        same = (g.view(torch.int16) == e.view(torch.int16)) | (torch.isnan(g) & torch.isnan(e))
+        assert bool(same.all()), f"{name}: {int((~same).sum())} elements differ from eager"
+    # the same chain reduced over the last dimension: fp32 accumulation of the bf16 chain values
+    chain = abi.ew_program(3, [(EwOp.MUL, 0, 1, 0, 0, bf), (EwOp.SUB, 3, 2, 0, 0, bf), (EwOp.RELU, 4, 0, 0, 0, bf)], [5],
+                           [FULL, ROW, ROW])
+    xc = x.clone()
+    xc[3, 7] = 0.25
+    xc[5, 9] = -2.0
+    val = torch.relu(xc * w - b).float()
+    for op, want in ((ReduceOp.SUM, val.double().sum(-1).float()), (ReduceOp.MEAN, val.double().mean(-1).float()),
+                     (ReduceOp.MAX, val.amax(-1)), (ReduceOp.MIN, val.amin(-1))):
+        out = torch.empty(rows, device=DEV)
+        abi.launch(Template.ROW_REDUCE, [xc.to(DEV), dw, db], [out], reduce_params(chain, op))
+        assert_close(out, want, F32_TOL, f"packed chain reduce op {op}")
+
+
 def test_two_outputs(executor):
     gen = torch.Generator().manual_seed(16)
     a, b = torch.randn(50, 40, generator=gen), torch.randn(50, 40, generator=gen)
