@@ -5,10 +5,13 @@
 // choreo-op/flashattention-gcu-only-test.co:75-122 (d_i = d_prev*e^(m_prev-m) + e^(s-m)); the
 // executed path is eager torch.nn.functional.scaled_dot_product_attention in bf16.
 //
-// Tensor-core bound.  One CTA per (batch*head, 256-query tile), handled as two 128-row halves
-// A and B that share every K/V block (halving operand traffic per flop) and ping-pong on the
-// tensor core: while the softmax warps of one half work, the MMAs of the other half run.
-//   warp 0      TMA producer: both Q halves once, then K_j and V_j through one 5-stage ring
+// Tensor-core bound.  Persistent CTAs, one per SM, each walking a fixed, balanced sequence of
+// (batch*head, 256-query) tiles, so that the loads and first scores of a tile overlap the output
+// phase of the previous one.  A tile is handled as two 128-row halves A and B that share every
+// K/V block (halving operand traffic per flop) and ping-pong on the tensor core: while the softmax
+// warps of one half work, the MMAs of the other half run.
+//   warp 0      TMA producer: both Q halves per tile, K_j and V_j through one 5-stage ring that
+//               never resets across tiles
 //   warp 1      MMA issuer:  S_h = Q_h K_j^T (fp32 in TMEM) and O_h += P_h V_j, where P_h is
 //               read straight from TMEM (it overwrites the S_h columns as packed bf16).  The whole
 //               warp runs the loop convergently and an elected lane issues, which keeps the
@@ -24,9 +27,9 @@
 //               running max grew by more than 2^8 (exact after the final division)
 // TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511.  MMAs of one CTA execute in
 // issue order, so reusing the S_h columns for S_h(j+1) after P_h(j) needs no extra barrier.
-// Causal work is triangular, so CTAs are numbered heaviest tile first.  No load is multicast;
-// every wait is bounded and reports through the device status word.
-// Measured alternatives that lost: persistent CTAs with a polling issuer (-8 %), 64-key blocks
+// Causal work is triangular: tiles are numbered heaviest first and dealt to the CTAs in a snake
+// order.  No load is multicast; every wait is bounded and reports through the device status word.
+// Measured alternatives that lost: a polling issuer that lets a half run into the next tile (-8 %), 64-key blocks
 // with P double-buffered beside S (-50 %: the tensor core accepts about one MMA per 90 cycles
 // whatever its N, so halving N halves the rate), 16 softmax warps sharing rows (-13 %), P handed
 // over in two parts of 64 keys so that half of P.V starts early (-1.5 %).
@@ -81,8 +84,8 @@ struct AttnSmem {
 };
 
 // barrier indices; ring barriers are indexed by stage, the others by half
-enum { B_QFULL = 0, B_FULL = 1, B_EMPTY = B_FULL + KV_STAGES, B_SFULL = B_EMPTY + KV_STAGES, B_PFULL = B_SFULL + 2,
-       B_PVDONE = B_PFULL + 2, B_COUNT = B_PVDONE + 2 };
+enum { B_QFULL = 0, B_QEMPTY = 1, B_FULL = 2, B_EMPTY = B_FULL + KV_STAGES, B_SFULL = B_EMPTY + KV_STAGES, B_PFULL = B_SFULL + 2,
+       B_PVDONE = B_PFULL + 2, B_OFREE = B_PVDONE + 2, B_COUNT = B_OFREE + 2 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -160,6 +163,38 @@ __device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2,
   unpack2(lsum, l0, l1);
 }
 
+// One (batch*head, 256-query) tile of this CTA's sequence.
+struct Tile {
+  int bh, q0;
+  int nblk[2];   // key blocks each 128-row half attends to
+  int n_iter;    // key blocks the tile loads (max of the two)
+};
+
+// k-th tile of this CTA.  Tiles are numbered heaviest (last query tile) first; round k hands tiles
+// k*G .. k*G+G-1 to the CTAs in ascending order for even k and descending for odd k, which evens out
+// the triangular causal work (C5: 64 block steps on the busiest SM against a mean of 62.3).
+__device__ __forceinline__ bool tile_at(const AttnArgs& a, int k, Tile& t) {
+  const int G = static_cast<int>(gridDim.x), b = static_cast<int>(blockIdx.x);
+  const int total = a.BH * a.n_qtiles;
+  const int idx = k * G + ((k & 1) ? (G - 1 - b) : b);
+  if (k * G >= total || idx >= total) return false;
+  t.q0 = (a.n_qtiles - 1 - idx / a.BH) * BQ;
+  t.bh = idx % a.BH;
+  const int kv_total = (a.S + BKV - 1) / BKV;
+  t.n_iter = 0;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row0 = t.q0 + h * BH_ROWS;
+    int n;
+    if (row0 >= a.S) n = 0;
+    else if (a.causal) { const int lim = row0 / BKV + 1; n = lim < kv_total ? lim : kv_total; }
+    else n = kv_total;
+    t.nblk[h] = n;
+    t.n_iter = n > t.n_iter ? n : t.n_iter;
+  }
+  return true;
+}
+
 template <int HD, bool BF16>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
   using L = AttnSmem<HD>;
@@ -169,28 +204,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heaviest (last) query tiles first
-  const int q_tile = a.n_qtiles - 1 - static_cast<int>(blockIdx.x) / a.BH;
-  const int bh = static_cast<int>(blockIdx.x) % a.BH;
-  const int q0 = q_tile * BQ;
-  const int kv_total = (a.S + BKV - 1) / BKV;
-  // key blocks each half attends to
-  int nblk[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int row0 = q0 + h * BH_ROWS;
-    if (row0 >= a.S) nblk[h] = 0;
-    else if (a.causal) { const int lim = row0 / BKV + 1; nblk[h] = lim < kv_total ? lim : kv_total; }
-    else nblk[h] = kv_total;
-  }
-  const int n_iter = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
 
   if (warp == 0 && lane == 0) {
     sm100::prefetch_tensormap(&a.tmap_q);
     sm100::prefetch_tensormap(&a.tmap_k);
     sm100::prefetch_tensormap(&a.tmap_v);
-    for (int i = 0; i < B_COUNT; ++i)
-      sm100::mbar_init(&bars[i], (i == B_PFULL || i == B_PFULL + 1) ? 4 : 1);  // P: one arrival per softmax warp
+    for (int i = 0; i < B_COUNT; ++i) {
+      const bool per_warp = (i >= B_PFULL && i < B_PFULL + 2) || (i >= B_OFREE && i < B_OFREE + 2);
+      sm100::mbar_init(&bars[i], per_warp ? 4 : 1);   // P and O-free: one arrival per softmax warp of the half
+    }
     sm100::fence_barrier_init();
   }
   if (warp == 1) {
@@ -208,25 +230,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
 #endif
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // Runs ahead of the consumers across tile boundaries: the ring index never resets, and the Q
+    // halves of the next tile are fetched as soon as the last S MMA of the current one is done.
     if (lane == 0) {
-      const int active = (nblk[0] > 0) + (nblk[1] > 0);
-      sm100::mbar_arrive_expect_tx(&bars[B_QFULL], active * L::TILE_BYTES);
-      for (int h = 0; h < 2; ++h)
-        if (nblk[h] > 0)
+      int ring = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        Tile t;
+        if (!tile_at(a, k, t)) break;
+        if (k > 0 && !sm100::mbar_wait(&bars[B_QEMPTY], (k - 1) & 1)) { sm100::report_timeout(a.status, 21); break; }
+        const int active = (t.nblk[0] > 0) + (t.nblk[1] > 0);
+        sm100::mbar_arrive_expect_tx(&bars[B_QFULL], active * L::TILE_BYTES);
+        for (int h = 0; h < 2; ++h)
+          if (t.nblk[h] > 0)
+#pragma unroll
+            for (int d = 0; d < HD / 64; ++d)
+              sm100::tma_load_3d(smem + L::Q_OFF + h * L::TILE_BYTES + d * (128 * 128), &a.tmap_q, d * 64,
+                                 t.q0 + h * BH_ROWS, t.bh, &bars[B_QFULL]);
+        // ring tile i of the tile: K_j for i = 2j, V_j for i = 2j + 1
+        for (int i = 0; i < 2 * t.n_iter; ++i) {
+          const int r = ring + i, st = r % KV_STAGES, use = r / KV_STAGES;
+          if (use > 0 && !sm100::mbar_wait(&bars[B_EMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 20); ok = false; break; }
+          sm100::mbar_arrive_expect_tx(&bars[B_FULL + st], L::TILE_BYTES);
+          const void* tmap = (i & 1) ? static_cast<const void*>(&a.tmap_v) : static_cast<const void*>(&a.tmap_k);
 #pragma unroll
           for (int d = 0; d < HD / 64; ++d)
-            sm100::tma_load_3d(smem + L::Q_OFF + h * L::TILE_BYTES + d * (128 * 128), &a.tmap_q, d * 64,
-                               q0 + h * BH_ROWS, bh, &bars[B_QFULL]);
-      // ring tile i: K_j for i = 2j, V_j for i = 2j + 1
-      for (int i = 0; i < 2 * n_iter; ++i) {
-        const int st = i % KV_STAGES, use = i / KV_STAGES;
-        if (use > 0 && !sm100::mbar_wait(&bars[B_EMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 20); break; }
-        sm100::mbar_arrive_expect_tx(&bars[B_FULL + st], L::TILE_BYTES);
-        const void* tmap = (i & 1) ? static_cast<const void*>(&a.tmap_v) : static_cast<const void*>(&a.tmap_k);
-#pragma unroll
-        for (int d = 0; d < HD / 64; ++d)
-          sm100::tma_load_3d(smem + L::KV_OFF + st * L::TILE_BYTES + d * (128 * 128), tmap, d * 64, (i >> 1) * BKV, bh,
-                             &bars[B_FULL + st]);
+            sm100::tma_load_3d(smem + L::KV_OFF + st * L::TILE_BYTES + d * (128 * 128), tmap, d * 64, (i >> 1) * BKV, t.bh,
+                               &bars[B_FULL + st]);
+        }
+        ring += 2 * t.n_iter;
       }
     }
   } else if (warp == 1) {
@@ -235,7 +267,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     // instructions: with warp-uniform control flow the operand descriptors live in uniform
     // registers, where tcgen05.mma reads them, instead of being moved there before every
     // instruction (measured: ~95 cycles per MMA issued from a single-lane branch, more than the
-    // 64 cycles a 128x128x16 MMA executes in).
+    // 64 cycles a 128x128x16 MMA executes in).  Tiles follow one another without a gap: the first
+    // scores of the next tile are issued right behind the last product of the current one, while
+    // the softmax warps still write the current tile's output.
     {
       const bool leader = sm100::elect_one();
       constexpr uint32_t idesc_s = sm100::umma_idesc_f16(BH_ROWS, BKV, BF16, false, false);
@@ -246,72 +280,95 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         if (!done && leader) sm100::report_timeout(a.status, site);
         return done;
       };
-      bool ok = wait_all(&bars[B_QFULL], 0, 22);
-
-      // S_h(j) = Q_h K_j^T; the caller has already waited for K_j
-      auto issue_s = [&](int h, int j) {
-        const uint32_t q_addr = sm100::smem_u32(smem + L::Q_OFF + h * L::TILE_BYTES);
-        const uint32_t k_addr = sm100::smem_u32(smem + L::KV_OFF + ((2 * j) % KV_STAGES) * L::TILE_BYTES);
-        const uint32_t d = tmem_base + TMEM_S + h * 128;
-        if (leader) {
-#pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk) {
-            const uint32_t off = (kk / 4) * (128 * 128) + (kk % 4) * 32;
-            sm100::umma_f16_ss(d, sm100::umma_desc_k_sw128(q_addr + off), sm100::umma_desc_k_sw128(k_addr + off), idesc_s,
-                               kk > 0 ? 1u : 0u);
-          }
-          sm100::umma_commit(&bars[B_SFULL + h]);
-        }
-        __syncwarp();
-      };
       auto commit = [&](uint64_t* bar) {
         if (leader) sm100::umma_commit(bar);
         __syncwarp();
       };
+      int ring = 0;                 // ring index of the current tile's K_0
+      int blocks[2] = {0, 0};       // key blocks issued so far per half (phases of its S / P / PV barriers)
+      int tiles_done[2] = {0, 0};   // tiles whose products are all issued, per half (gates the reuse of O_h)
+      bool ok = true;
 
-      if (ok && n_iter > 0) ok = wait_all(&bars[B_FULL + 0], 0, 23);
-      if (ok && n_iter > 0) {
-        sm100::tc_fence_after();
-        for (int h = 0; h < 2; ++h)
-          if (nblk[h] > 0) issue_s(h, 0);
-        commit(&bars[B_EMPTY + 0]);          // K_0 free once both S(0) are done
-      }
-      for (int j = 0; j < n_iter && ok; ++j) {
-        const bool next = j + 1 < n_iter;
-        const int vt = 2 * j + 1, kt = 2 * j + 2;       // ring tiles of V_j and K_(j+1)
-        ok = wait_all(&bars[B_FULL + vt % KV_STAGES], (vt / KV_STAGES) & 1, 25);
+      for (int k = 0; ok; ++k) {
+        Tile t;
+        if (!tile_at(a, k, t)) break;
+        const int n_iter = t.n_iter;
+        ok = wait_all(&bars[B_QFULL], k & 1, 22);
         if (!ok) break;
-        bool k_ready = false;
-        const uint32_t v_addr = sm100::smem_u32(smem + L::KV_OFF + (vt % KV_STAGES) * L::TILE_BYTES);
-        for (int h = 0; h < 2 && ok; ++h) {
-          if (j < nblk[h]) {
-            ok = wait_all(&bars[B_PFULL + h], j & 1, 26);
-            if (!ok) break;
-            sm100::tc_fence_after();
-            const uint32_t p_tmem = tmem_base + TMEM_S + h * 128;   // packed bf16 pairs: 8 columns per 16 keys
-            if (leader) {
+        auto ring_wait = [&](int i, int site) { const int r = ring + i; return wait_all(&bars[B_FULL + r % KV_STAGES], (r / KV_STAGES) & 1, site); };
+        auto ring_free = [&](int i) { commit(&bars[B_EMPTY + (ring + i) % KV_STAGES]); };
+        // S_h(j) = Q_h K_j^T; the caller has already waited for K_j
+        auto issue_s = [&](int h, int j) {
+          const uint32_t q_addr = sm100::smem_u32(smem + L::Q_OFF + h * L::TILE_BYTES);
+          const uint32_t k_addr = sm100::smem_u32(smem + L::KV_OFF + ((ring + 2 * j) % KV_STAGES) * L::TILE_BYTES);
+          const uint32_t d = tmem_base + TMEM_S + h * 128;
+          if (leader) {
 #pragma unroll
-              for (int kk = 0; kk < BKV / 16; ++kk) {
-                const uint64_t vdesc = sm100::umma_desc_mn_sw128(v_addr + kk * (16 * 128), 128 * 128);
-                sm100::umma_f16_ts(tmem_base + TMEM_O + h * 128, p_tmem + kk * 8, vdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-              }
-              sm100::umma_commit(&bars[B_PVDONE + h]);
+            for (int kk = 0; kk < HD / 16; ++kk) {
+              const uint32_t off = (kk / 4) * (128 * 128) + (kk % 4) * 32;
+              sm100::umma_f16_ss(d, sm100::umma_desc_k_sw128(q_addr + off), sm100::umma_desc_k_sw128(k_addr + off), idesc_s,
+                                 kk > 0 ? 1u : 0u);
             }
-            __syncwarp();
+            sm100::umma_commit(&bars[B_SFULL + h]);
           }
-          if (next && j + 1 < nblk[h]) {
-            if (!k_ready) {
-              ok = wait_all(&bars[B_FULL + kt % KV_STAGES], (kt / KV_STAGES) & 1, 24);
-              if (!ok) break;
-              k_ready = true;
-              sm100::tc_fence_after();
-            }
-            issue_s(h, j + 1);
-          }
+          __syncwarp();
+        };
+
+        if (n_iter > 0) {
+          ok = ring_wait(0, 23);
+          if (!ok) break;
+          sm100::tc_fence_after();
+          for (int h = 0; h < 2; ++h)
+            if (t.nblk[h] > 0) issue_s(h, 0);
+          ring_free(0);                       // K_0 free once both S(0) are done
+          if (n_iter == 1) commit(&bars[B_QEMPTY]);
         }
-        if (!ok) break;
-        commit(&bars[B_EMPTY + vt % KV_STAGES]);
-        if (next) commit(&bars[B_EMPTY + kt % KV_STAGES]);
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const bool next = j + 1 < n_iter;
+          const int vt = 2 * j + 1, kt = 2 * j + 2;       // ring tiles of V_j and K_(j+1)
+          ok = ring_wait(vt, 25);
+          if (!ok) break;
+          bool k_ready = false;
+          const uint32_t v_addr = sm100::smem_u32(smem + L::KV_OFF + ((ring + vt) % KV_STAGES) * L::TILE_BYTES);
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (j < t.nblk[h]) {
+              // the first product of a tile overwrites O_h: the previous tile's epilogue must have read it
+              if (j == 0 && tiles_done[h] > 0) {
+                ok = wait_all(&bars[B_OFREE + h], (tiles_done[h] - 1) & 1, 28);
+                if (!ok) break;
+              }
+              ok = wait_all(&bars[B_PFULL + h], blocks[h] & 1, 26);
+              if (!ok) break;
+              ++blocks[h];
+              sm100::tc_fence_after();
+              const uint32_t p_tmem = tmem_base + TMEM_S + h * 128;   // packed bf16 pairs: 8 columns per 16 keys
+              if (leader) {
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk) {
+                  const uint64_t vdesc = sm100::umma_desc_mn_sw128(v_addr + kk * (16 * 128), 128 * 128);
+                  sm100::umma_f16_ts(tmem_base + TMEM_O + h * 128, p_tmem + kk * 8, vdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                sm100::umma_commit(&bars[B_PVDONE + h]);
+              }
+              __syncwarp();
+              if (j == t.nblk[h] - 1) ++tiles_done[h];
+            }
+            if (next && j + 1 < t.nblk[h]) {
+              if (!k_ready) {
+                ok = ring_wait(kt, 24);
+                if (!ok) break;
+                k_ready = true;
+                sm100::tc_fence_after();
+              }
+              issue_s(h, j + 1);
+            }
+          }
+          if (!ok) break;
+          ring_free(vt);
+          if (next) ring_free(kt);
+          if (j + 2 == n_iter) commit(&bars[B_QEMPTY]);   // every S of this tile is issued: Q may be replaced
+        }
+        ring += 2 * n_iter;
       }
     }
   } else if (warp >= SOFTMAX_WARP0) {
@@ -321,98 +378,108 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     // ------------------------------------------------------------ softmax / correction / epilogue
     const int g = (warp - SOFTMAX_WARP0) >> 2;       // half this warp group serves
     const int q = warp & 3;              // TMEM lane quadrant
-    const int n_my = nblk[g];
     const int row_in_half = q * 32 + lane;
-    const int row = q0 + g * BH_ROWS + row_in_half;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t s_taddr = tmem_base + TMEM_S + g * 128 + lane_sel;
     const uint32_t o_taddr = tmem_base + TMEM_O + g * 128 + lane_sel;
-    float m_ref = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    int n = 0;                           // key blocks consumed so far over all tiles (barrier phases)
     bool ok = true;
 
-    for (int j = 0; j < n_my; ++j) {
-      if (!sm100::mbar_wait(&bars[B_SFULL + g], j & 1)) { sm100::report_timeout(a.status, 27); ok = false; break; }
-      sm100::tc_fence_after();
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) sm100::tmem_ld32(s_taddr + c * 32, sr[c]);
-      sm100::tmem_ld_wait();
+    for (int k = 0; ok; ++k) {
+      Tile t;
+      if (!tile_at(a, k, t)) break;
+      const int n_my = t.nblk[g];
+      if (n_my == 0) continue;
+      const int row0 = t.q0 + g * BH_ROWS;
+      const int row = row0 + row_in_half;
+      float m_ref = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
-      const int key0 = j * BKV;
-      const bool need_mask = (a.causal && key0 + BKV - 1 > q0 + g * BH_ROWS) || (key0 + BKV > a.S);
-      float bmax = -INFINITY;
-      if (need_mask) {
+      for (int j = 0; j < n_my; ++j, ++n) {
+        if (!sm100::mbar_wait(&bars[B_SFULL + g], n & 1)) { sm100::report_timeout(a.status, 27); ok = false; break; }
+        sm100::tc_fence_after();
+        uint32_t sr[4][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            float v = __uint_as_float(sr[c][i]);
-            if (key >= a.S || (a.causal && key > row)) v = -INFINITY;
-            sr[c][i] = __float_as_uint(v);
-            bmax = fmaxf(bmax, v);
-          }
-      } else {
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains of 3-input max
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
-        bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      }
-      bmax *= a.scale_log2;  // scale > 0: max commutes with the scaling
+        for (int c = 0; c < 4; ++c) sm100::tmem_ld32(s_taddr + c * 32, sr[c]);
+        sm100::tmem_ld_wait();
 
-      // S_h(j) was issued after P_h(j-1) V_(j-1), and MMAs complete in order: O_h is stable here
-      if (j == 0) {
-        m_ref = bmax;
-      } else if (__any_sync(0xffffffffu, bmax > m_ref + kRescaleThreshold)) {
-        const float m_new = fmaxf(m_ref, bmax);
-        const float alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
-        l0 *= alpha;
-        l1 *= alpha;
-        m_ref = m_new;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          sm100::tmem_ld32(o_taddr + c * 32, o);
-          sm100::tmem_ld_wait();
+        const int key0 = j * BKV;
+        const bool need_mask = (a.causal && key0 + BKV - 1 > row0) || (key0 + BKV > a.S);
+        float bmax = -INFINITY;
+        if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          sm100::tmem_st32(o_taddr + c * 32, o);
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c * 32 + i;
+              float v = __uint_as_float(sr[c][i]);
+              if (key >= a.S || (a.causal && key > row)) v = -INFINITY;
+              sr[c][i] = __float_as_uint(v);
+              bmax = fmaxf(bmax, v);
+            }
+        } else {
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains of 3-input max
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
+          bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         }
+        bmax *= a.scale_log2;  // scale > 0: max commutes with the scaling
+
+        // S_h(j) was issued after P_h(j-1) V_(j-1), and MMAs complete in order: O_h is stable here
+        if (j == 0) {
+          m_ref = bmax;
+        } else if (__any_sync(0xffffffffu, bmax > m_ref + kRescaleThreshold)) {
+          const float m_new = fmaxf(m_ref, bmax);
+          const float alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
+          l0 *= alpha;
+          l1 *= alpha;
+          m_ref = m_new;
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            sm100::tmem_ld32(o_taddr + c * 32, o);
+            sm100::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            sm100::tmem_st32(o_taddr + c * 32, o);
+          }
+        }
+
+        // masked blocks keep the special-function path: exp2(-inf) must be exactly 0
+        const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+        if (need_mask) store_p<BF16, 0>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
+        else store_p<BF16, CDR_ATT_EMU>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
+        sm100::tmem_st_wait();
+        sm100::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&bars[B_PFULL + g]);
       }
+      if (!ok) break;
 
-      // masked blocks keep the special-function path: exp2(-inf) must be exactly 0
-      const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-      if (need_mask) store_p<BF16, 0>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
-      else store_p<BF16, CDR_ATT_EMU>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
-      sm100::tmem_st_wait();
-      sm100::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&bars[B_PFULL + g]);
-    }
-
-    // ---- epilogue: O / l, rounded to the output type
-    if (ok && n_my > 0) {
-      if (!sm100::mbar_wait(&bars[B_PVDONE + g], (n_my - 1) & 1)) { sm100::report_timeout(a.status, 29); ok = false; }
-    }
-    if (ok && n_my > 0) {
+      // ---- epilogue: O / l, rounded to the output type; O_h is handed back after the last read
+      if (!sm100::mbar_wait(&bars[B_PVDONE + g], (n - 1) & 1)) { sm100::report_timeout(a.status, 29); ok = false; break; }
       sm100::tc_fence_after();
       const float inv = 1.0f / (l0 + l1);
-      unsigned char* orow = static_cast<unsigned char*>(a.out) + (static_cast<size_t>(bh) * a.S + row) * (HD * 2);
+      unsigned char* orow = static_cast<unsigned char*>(a.out) + (static_cast<size_t>(t.bh) * a.S + row) * (HD * 2);
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
         sm100::tmem_ld32(o_taddr + c * 32, o);
         sm100::tmem_ld_wait();
+        if (c == HD / 32 - 1) {
+          sm100::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) sm100::mbar_arrive(&bars[B_OFREE + g]);
+        }
         if (row < a.S) {
 #pragma unroll
           for (int gq = 0; gq < 4; ++gq) {
             uint32_t w[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
-              w[t] = pack_pair<BF16>(__uint_as_float(o[gq * 8 + t * 2]) * inv, __uint_as_float(o[gq * 8 + t * 2 + 1]) * inv);
+            for (int tt = 0; tt < 4; ++tt)
+              w[tt] = pack_pair<BF16>(__uint_as_float(o[gq * 8 + tt * 2]) * inv, __uint_as_float(o[gq * 8 + tt * 2 + 1]) * inv);
             *reinterpret_cast<uint4*>(orow + c * 64 + gq * 16) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
@@ -447,8 +514,10 @@ int launch_attention_cfg(const AttnArgs& a, cudaStream_t stream) {
     CDR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     configured_dev[dev & 63] = true;
   }
-  const int64_t grid = static_cast<int64_t>(a.BH) * a.n_qtiles;
-  if (grid > 0x7fffffff) { set_error("attention: too many tiles"); return CDR_ERR_UNSUPPORTED; }
+  const int64_t tiles = static_cast<int64_t>(a.BH) * a.n_qtiles;
+  if (tiles > 0x3fffffff) { set_error("attention: too many tiles"); return CDR_ERR_UNSUPPORTED; }
+  const int64_t sms = sm_count();
+  const int64_t grid = tiles < sms ? tiles : sms;   // persistent: one CTA per SM walks its share of the tiles
   kern<<<static_cast<unsigned>(grid), ATT_THREADS, smem, stream>>>(a);
   CDR_CUDA_TRY(cudaGetLastError());
   return CDR_OK;
