@@ -17,6 +17,8 @@
 // the instruction count low enough to stay memory-bound.
 #include <type_traits>
 
+#include <stdlib.h>
+
 #include "cdr_common.cuh"
 
 namespace cdr {
@@ -104,6 +106,12 @@ __global__ void __launch_bounds__(NT, (768 / NT > 0 ? 768 / NT : 1)) row_reduce_
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const idx_t cols = static_cast<idx_t>(a.cols), rows = static_cast<idx_t>(a.rows);
   const idx_t vec_per_row = cols / V;
+
+  // Programmatic dependent launch: let the next kernel of the stream be scheduled while this one
+  // runs, and wait for the previous one to finish (and flush) before the first global access.
+  // Both are no-ops when the launch does not carry the attribute.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // row-broadcast operands: loaded once, register resident for the whole kernel
   uint4 rowv[NROW > 0 ? NROW : 1][VPT];
@@ -353,6 +361,11 @@ RowChain match_row_chain(const cdr_ew_params& p, int dt, int* full_idx, int* row
   return kRNone;
 }
 
+inline bool pdl_enabled() {
+  static const bool on = getenv("CDR_DISABLE_PDL") == nullptr;
+  return on;
+}
+
 template <class Chain, int NT, int VPT, int RB, bool EXACT>
 int launch_named_variant(const RowArgs& a, cudaStream_t s) {
   auto kern = row_reduce_named_kernel<Chain, NT, VPT, RB, EXACT>;
@@ -373,8 +386,19 @@ int launch_named_variant(const RowArgs& a, cudaStream_t s) {
   // latency-bound and cost as much as a full one
   const int64_t rounds = (n_blocks + grid - 1) / grid;
   grid = (n_blocks + rounds - 1) / rounds;
-  kern<<<static_cast<unsigned>(grid), NT, 0, s>>>(a);
-  CDR_CUDA_TRY(cudaGetLastError());
+  // launched with programmatic stream serialization: the kernel begins with griddepcontrol.wait,
+  // so it may be scheduled before its predecessor in the stream has drained
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(NT);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a));
   return CDR_OK;
 }
 
