@@ -554,6 +554,20 @@ def test_attention_shapes_against_oracle(executor, B, H, S, D, causal):
     assert_close(out.float(), want, BF16_TOL, f"attention {B}x{H}x{S}x{D} causal={causal}")
 
 
+@pytest.mark.parametrize("B,H,S,D,causal", [(3, 20, 600, 64, True), (2, 40, 520, 128, False), (1, 150, 300, 128, True)])
+def test_attention_more_tiles_than_sms(executor, B, H, S, D, causal):
+    """More (batch*head, query tile) pairs than the GPU has SMs: every persistent CTA walks several
+    tiles, with ragged sequence lengths (partial key blocks, a last query tile with an empty half)."""
+    q, k, v = rp.inputs_attention(B, H, S, D, seed=3 * S + D)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=causal)
+    out = attention(*cuda(q, k, v), causal=causal)
+    assert_close(out.float(), ref, BF16_TOL, f"attention {B}x{H}x{S}x{D} causal={causal}")
+    # one head against the C oracle as well
+    want = bf16_bits_to_tensor(scalar.attention_bf16(*(tensor_to_bf16_bits(t[:1, :1]) for t in (q, k, v)), scale=D ** -0.5,
+                                                     causal=causal)).float()
+    assert_close(out[:1, :1].float(), want, BF16_TOL, "first head vs oracle")
+
+
 def test_attention_fp16_custom_scale_and_large_logits(executor):
     gen = torch.Generator().manual_seed(55)
     q = (4 * torch.randn(1, 2, 320, 64, generator=gen)).half()      # large logits: the running max keeps growing
