@@ -10,7 +10,7 @@
 // phase of the previous one.  A tile is handled as two 128-row halves A and B that share every
 // K/V block (halving operand traffic per flop) and ping-pong on the tensor core: while the softmax
 // warps of one half work, the MMAs of the other half run.
-//   warp 0      TMA producer: both Q halves per tile, K_j and V_j through one 5-stage ring that
+//   warp 0      TMA producer: both Q halves per tile, K_j and V_j through one 4-stage ring that
 //               never resets across tiles
 //   warp 1      MMA issuer:  S_h = Q_h K_j^T (fp32 in TMEM) and O_h += P_h V_j, where P_h is
 //               read straight from TMEM (it overwrites the S_h columns as packed bf16).  The whole
@@ -72,7 +72,7 @@ struct AttnArgs {
   int* status;
 };
 
-constexpr int KV_STAGES = 5;   // one ring for K and V tiles: K_0 V_0 K_1 V_1 ... (2.5 key blocks in flight)
+constexpr int KV_STAGES = 4;   // one ring for K and V tiles: K_0 V_0 K_1 V_1 ... (4 measured as fast as 5)
 
 template <int HD>
 struct AttnSmem {
