@@ -11,6 +11,7 @@ There is no eager fallback: everything in the plan is a hand-written kernel temp
 """
 from __future__ import annotations
 
+import time
 from typing import Optional
 
 import torch
@@ -18,6 +19,7 @@ import torch
 from ..codegen.kernel_templates import KernelLaunch
 from ..utils.exceptions import DeviceError, ExecutionError
 from ..utils.logging import get_logger
+from ..utils.tracer import get_tracer
 from .executor import get_executor
 from .jit_compiler import CompiledArtifact
 
@@ -96,6 +98,8 @@ class Callable:
 
     # ------------------------------------------------------------------ call
     def __call__(self, *args):
+        tracer = get_tracer()
+        t_start = time.perf_counter() if tracer.should_trace_execution() else None
         tensors = [a for a in args if isinstance(a, torch.Tensor)]
         dag = self.dag
         if len(tensors) != len(dag.inputs):
@@ -146,6 +150,8 @@ class Callable:
         self.calls += 1
         if self.record_inputs:
             self.last_inputs = tuple(env[b] for b in dag.inputs)
+        if t_start is not None:
+            tracer.trace_execution(self.artifact.entry_point, tensors, list(outputs), (time.perf_counter() - t_start) * 1e3)
         return tuple(outputs)
 
     def _is_shard(self, t: torch.Tensor, buf) -> bool:

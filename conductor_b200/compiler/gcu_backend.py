@@ -48,7 +48,7 @@ class GCUBackend:
         text = str(graph_module.graph)
         for t in example_inputs or []:
             if isinstance(t, torch.Tensor):
-                text += f"|{tuple(t.shape)}:{t.dtype}:{t.device.type}"
+                text += f"|{tuple(t.shape)}:{t.dtype}:{t.stride()}:{t.device.type}"
         return hashlib.md5(text.encode()).hexdigest()
 
     def clear_cache(self) -> None:

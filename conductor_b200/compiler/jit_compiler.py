@@ -21,7 +21,9 @@ from ..optimization.graph_analyzer import ComputationDAG, GraphAnalyzer
 from ..utils.cache import CompilationCache
 from ..utils.config import get_config
 from ..utils.exceptions import CompilationError, ConductorError
+from ..utils.artifacts import get_debug_manager
 from ..utils.logging import get_logger
+from ..utils.tracer import get_tracer
 from .loader import library_path
 
 logger = get_logger(__name__)
@@ -77,6 +79,8 @@ class ChoreoJITCompiler:
         graph_hash = self._generate_graph_hash(graph_module, example_inputs)
         self.cache.enabled = cfg.cache.enabled
         cached = self.cache.get(graph_hash)
+        tracer = get_tracer()
+        tracer.trace_cache_operation("lookup", graph_hash, cached is not None)
         if cached is not None:
             self.stats["cache_hits"] += 1
             return cached
@@ -111,20 +115,17 @@ class ChoreoJITCompiler:
         self.stats["seconds"] += time.perf_counter() - t0
         logger.info("compiled %s: %d nodes -> %d kernels", name, len(dag.nodes),
                     sum(1 for l in launches if l.template))
-        if cfg.debug.enabled:
-            logger.debug("\n%s\n%s", self.graph_analyzer.describe(dag), plan_text)
-            if cfg.debug.dump_dir:
-                self._dump(cfg.debug.dump_dir, name, graph_module, dag, plan_text)
+        tracer.trace_graph_hash(graph_hash, {"kernel": name, "nodes": len(dag.nodes), "clusters": len(clusters)})
+        tracer.trace_dag(dag)
+        tracer.trace_dsl(plan_text)
+        tracer.trace_compilation(
+            ["parse_fx_graph", "identify_fusion_opportunities", "schedule_clusters", "select_templates"],
+            {"kernel": name, "kernels": sum(1 for l in launches if l.template), "aliases": sum(1 for l in launches if not l.template),
+             "seconds": round(time.perf_counter() - t0, 6), "library": str(library_path())})
+        manager = get_debug_manager()
+        if manager.enabled():
+            manager.save_compilation(name, graph_module, self.graph_analyzer.describe(dag), plan_text, launches)
         return artifact
-
-    def _dump(self, dump_dir: str, name: str, gm, dag, plan_text: str) -> None:
-        """Opt-in artifact dump (reference: ``conductor/utils/artifacts.py:18-237`` always writes
-        ``debug_dir`` next to the package; here nothing is written unless a directory is set)."""
-        import os
-
-        os.makedirs(dump_dir, exist_ok=True)
-        with open(os.path.join(dump_dir, f"{name}.plan.txt"), "w") as f:
-            f.write(str(gm.graph) + "\n\n" + self.graph_analyzer.describe(dag) + "\n\n" + plan_text + "\n")
 
     def clear_cache(self) -> None:
         self.cache.clear()

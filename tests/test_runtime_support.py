@@ -66,19 +66,40 @@ def test_compile_cache_hits_and_key_covers_dtype():
 
 
 def test_debug_dump_is_opt_in(tmp_path):
+    """Artifacts and trace (reference: utils/artifacts.py, utils/tracer.py): nothing is written or
+    traced by default; with a directory set, one compile leaves the FX graph, the DAG table, the
+    cluster list with template parameters and the plan."""
+    import json
+
+    from conductor_b200.utils.artifacts import get_debug_manager
+    from conductor_b200.utils.tracer import get_tracer, reset_tracer
+
+    assert not get_debug_manager().enabled() and not get_tracer().is_enabled()
     cfg = ConductorConfig.load()
     cfg.debug.enabled = True
     cfg.debug.dump_dir = str(tmp_path / "dump")
     set_config(cfg)
+    reset_tracer()
     try:
         art = ChoreoJITCompiler().compile_graph(traced(), [torch.randn(4, 4)] * 3)
-        files = list((tmp_path / "dump").glob("*.plan.txt"))
-        assert len(files) == 1
-        text = files[0].read_text()
-        assert "elementwise<elementwise[mul,add]>" in text and "buffers:" in text and art.entry_point in files[0].name
+        mgr = get_debug_manager()
+        names = {p.name for p in mgr.list_artifacts(art.entry_point)}
+        for kind in ("fx.txt", "dag.txt", "clusters.json", "plan.txt"):
+            assert f"{art.entry_point}.{kind}" in names, names
+        assert "elementwise<elementwise[mul,add]>" in mgr.get_plan_path(art.entry_point).read_text()
+        assert "buffers:" in mgr.get_dag_path(art.entry_point).read_text()
+        clusters = json.loads(mgr.get_clusters_path(art.entry_point).read_text())
+        assert clusters[0]["template"] == "elementwise" and clusters[0]["nodes"] == ["mul", "add"]
+        assert [i["op"] for i in clusters[0]["params"]["instr"]] == [3, 1]           # MUL then ADD
+        assert len(clusters[0]["params"]["input_mode"]) == 3
+        kinds = [r["kind"] for r in get_tracer().records]
+        assert {"cache", "hash", "dag", "plan", "compilation"} <= set(kinds)
+        assert mgr.get_artifact_summary(art.entry_point)["total_bytes"] > 0
+        assert mgr.clean_artifacts(art.entry_point) == len(names) and not mgr.list_artifacts()
     finally:
         reset_config()
-    assert not get_config().debug.enabled
+        reset_tracer()
+    assert not get_config().debug.enabled and not get_debug_manager().enabled()
 
 
 def test_artifact_metadata():
