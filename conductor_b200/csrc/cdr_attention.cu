@@ -21,8 +21,8 @@
 //               registers (80 per thread kept) to the softmax groups (208 per thread, no spills)
 //   warps 4-7   softmax of half A, warps 8-11 of half B: one query row per thread; tcgen05.ld
 //               the S row, running max (3-input max) / sum in the log2 domain, P = exp2(..) with
-//               two-lane fp32 instructions and one pair in eight on the FMA pipes (cubic) to take
-//               load off the special-function unit, stored back to TMEM with tcgen05.st; the O
+//               two-lane fp32 instructions (a cubic on the FMA pipes can take pairs off the
+//               special-function unit, CDR_ATT_EMU, but no share of it paid off), stored back to TMEM with tcgen05.st; the O
 //               accumulator stays in TMEM and is rescaled only when the
 //               running max grew by more than 2^8 (exact after the final division)
 // TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511.  MMAs of one CTA execute in
@@ -94,7 +94,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 #ifndef CDR_ATT_EMU
-#define CDR_ATT_EMU 1   // pairs of every 8 whose exp2 runs on the FMA pipes
+#define CDR_ATT_EMU 0   // pairs of every 8 whose exp2 runs on the FMA pipes (0: measured best on this kernel)
 #endif
 
 // ---- two fp32 lanes per instruction (fma/add/sub .f32x2) and the three-input max of sm_100
