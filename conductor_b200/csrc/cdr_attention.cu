@@ -139,7 +139,7 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
 template <bool BF16, int EMU>
 __device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2, float neg_m, float& l0, float& l1, uint32_t p_taddr) {
   const uint64_t scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
-  uint64_t lsum = pack2(l0, l1);
+  uint64_t lsum4[4] = {pack2(l0, l1), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};   // independent chains
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t pw[16];
@@ -155,12 +155,12 @@ __device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2,
         p0 = fast_exp2(x0);
         p1 = fast_exp2(x1);
       }
-      lsum = add2(lsum, pack2(p0, p1));
+      lsum4[i & 3] = add2(lsum4[i & 3], pack2(p0, p1));
       pw[i] = pack_pair<BF16>(p0, p1);
     }
     sm100::tmem_st16(p_taddr + c * 16, pw);
   }
-  unpack2(lsum, l0, l1);
+  unpack2(add2(add2(lsum4[0], lsum4[1]), add2(lsum4[2], lsum4[3])), l0, l1);
 }
 
 // One (batch*head, 256-query) tile of this CTA's sequence.
