@@ -167,6 +167,42 @@ class _ProgramBuilder:
                                           and _FLOAT_RANK[odt] > _FLOAT_RANK[src_dt])
             self.reg_of[out] = src if widening else self._emit(EwOp.COPY, src, dtype=odt)
             return
+        canon = info.canonical_name
+        if canon == "clamp":                                  # clamp / clip / hardtanh / relu6
+            lo, hi = {"relu6": (0.0, 6.0), "hardtanh": (-1.0, 1.0)}.get(node.op_name, (None, None))
+            nums = [s[1] if is_num(s) else None for s in spec[1:3]] + [None, None]
+            lo = kw.get("min", kw.get("min_val", nums[0] if nums[0] is not None else lo))
+            hi = kw.get("max", kw.get("max_val", nums[1] if nums[1] is not None else hi))
+            if any(is_buf(s) for s in spec[1:]) or any(k[0] == "buf" for k in kws.values()):
+                raise UnsupportedOperationError(node.op_name, "tensor bounds")
+            r = self._operand(node, spec[0], odt)
+            if lo is not None:
+                r = self._emit(EwOp.MAX, r, self._emit(EwOp.CONST, imm=lo, dtype=odt), dtype=odt)
+            if hi is not None:
+                r = self._emit(EwOp.MIN, r, self._emit(EwOp.CONST, imm=hi, dtype=odt), dtype=odt)
+            self.reg_of[out] = r
+            return
+        if canon == "pow":                                    # pow / square / reciprocal
+            x = self._operand(node, spec[0], odt)
+            e = {"square": 2, "reciprocal": -1}.get(node.op_name)
+            if e is None:
+                if len(spec) < 2 or not is_num(spec[1]):
+                    raise UnsupportedOperationError(node.op_name, "only constant exponents 2, 3, 0.5, -1, 1")
+                e = spec[1][1]
+            if e == 2:
+                r = self._emit(EwOp.MUL, x, x, dtype=odt)
+            elif e == 3:                                      # eager: (x*x)*x
+                r = self._emit(EwOp.MUL, self._emit(EwOp.MUL, x, x, dtype=odt), x, dtype=odt)
+            elif e == 0.5:
+                r = self._emit(EwOp.SQRT, x, dtype=odt)
+            elif e == -1:
+                r = self._emit(EwOp.RDIV_IMM, x, imm=1.0, dtype=odt)
+            elif e == 1:
+                r = x
+            else:
+                raise UnsupportedOperationError(node.op_name, f"exponent {e!r}")
+            self.reg_of[out] = r
+            return
         if op in (EwOp.ADD, EwOp.SUB, EwOp.MUL, EwOp.DIV, EwOp.MAX, EwOp.MIN):
             if len(spec) < 2:
                 raise UnsupportedOperationError(node.op_name, "needs two operands")
@@ -202,6 +238,21 @@ class _ProgramBuilder:
                 r = self._emit(op, self._operand(node, a, odt), self._operand(node, b, odt), dtype=odt)
             self.reg_of[out] = r
             return
+        if op in (EwOp.GT, EwOp.GE, EwOp.LT, EwOp.LE, EwOp.EQ, EwOp.NE):
+            if len(spec) < 2:
+                raise UnsupportedOperationError(node.op_name, "needs two operands")
+            cdt = torch.float32                               # the 1.0 / 0.0 result is never rounded
+            regs = [self._operand(node, s, cdt) for s in spec[:2]]
+            self.reg_of[out] = self._emit(op, regs[0], regs[1], dtype=cdt)
+            return
+        if op == EwOp.WHERE:
+            if len(spec) < 3:
+                raise UnsupportedOperationError(node.op_name, "needs condition and two values")
+            regs = [self._operand(node, s, odt) for s in spec[:3]]
+            self.reg_of[out] = self._emit(op, regs[0], regs[1], regs[2], dtype=odt)
+            return
+        if op == EwOp.GELU and kw.get("approximate", "none") != "none":
+            raise UnsupportedOperationError(node.op_name, "only the erf form of gelu")
         if op in (EwOp.ADDCDIV, EwOp.ADDCMUL):
             value = kw.get("value", 1)
             if len(spec) > 3 and spec[3][0] == "const":

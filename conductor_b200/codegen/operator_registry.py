@@ -40,6 +40,7 @@ class OpType(Enum):
 class EwOp:
     ADD, SUB, MUL, DIV, RELU, NEG, ABS, EXP, LOG, SQRT, SIGMOID, TANH, SIN, COS = range(1, 15)
     MAX, MIN, ADDCDIV, ADDCMUL, CONST, COPY, ADD_IMM, MUL_IMM, RSUB_IMM, RDIV_IMM = range(15, 25)
+    GT, GE, LT, LE, EQ, NE, WHERE, RSQRT, SILU, GELU, ERF = range(25, 36)
 
 
 class ReduceOp:
@@ -116,6 +117,21 @@ class OperatorRegistry:
         r(_ew("minimum", EwOp.MIN, 2))
         r(_ew("addcdiv", EwOp.ADDCDIV, 3))
         r(_ew("addcmul", EwOp.ADDCMUL, 3))
+        # comparisons produce 1.0 / 0.0 inside a fused chain; `where` selects on != 0
+        r(_ew("gt", EwOp.GT, 2), "greater", "__gt__")
+        r(_ew("ge", EwOp.GE, 2), "greater_equal", "__ge__")
+        r(_ew("lt", EwOp.LT, 2), "less", "__lt__")
+        r(_ew("le", EwOp.LE, 2), "less_equal", "__le__")
+        r(_ew("eq", EwOp.EQ, 2), "__eq__")
+        r(_ew("ne", EwOp.NE, 2), "not_equal", "__ne__")
+        r(_ew("where", EwOp.WHERE, 3))
+        r(_ew("rsqrt", EwOp.RSQRT, 1))
+        r(_ew("silu", EwOp.SILU, 1), "silu_")
+        r(_ew("gelu", EwOp.GELU, 1))
+        r(_ew("erf", EwOp.ERF, 1))
+        # lowered to existing instructions: clamp -> max/min with constants, pow -> mul / sqrt / reciprocal
+        r(_ew("clamp", EwOp.MAX, 1), "clip", "clamp_", "hardtanh", "relu6")
+        r(_ew("pow", EwOp.MUL, 2), "square", "reciprocal")
         # dtype casts are a rounding-only instruction
         r(_ew("to_dtype", EwOp.COPY, 1), "float", "bfloat16", "half", "to", "type")
         r(_red("sum", ReduceOp.SUM))

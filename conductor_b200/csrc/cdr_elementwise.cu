@@ -68,6 +68,17 @@ __device__ __forceinline__ float apply_op_f(int op, float a, float b, float c, f
     case CDR_OP_MUL_IMM: return __fmul_rn(a, imm);
     case CDR_OP_RSUB_IMM: return __fsub_rn(imm, a);
     case CDR_OP_RDIV_IMM: return __fdiv_rn(imm, a);
+    case CDR_OP_GT: return a > b ? 1.0f : 0.0f;
+    case CDR_OP_GE: return a >= b ? 1.0f : 0.0f;
+    case CDR_OP_LT: return a < b ? 1.0f : 0.0f;
+    case CDR_OP_LE: return a <= b ? 1.0f : 0.0f;
+    case CDR_OP_EQ: return a == b ? 1.0f : 0.0f;
+    case CDR_OP_NE: return a != b ? 1.0f : 0.0f;
+    case CDR_OP_WHERE: return a != 0.0f ? b : c;
+    case CDR_OP_RSQRT: return __fdiv_rn(1.0f, __fsqrt_rn(a));
+    case CDR_OP_SILU: return __fdiv_rn(a, __fadd_rn(1.0f, expf(-a)));
+    case CDR_OP_GELU: return __fmul_rn(__fmul_rn(a, 0.5f), __fadd_rn(1.0f, erff(__fmul_rn(a, 0.70710678118654752440f))));
+    case CDR_OP_ERF: return erff(a);
     default: return 0.0f;
   }
 }
@@ -93,6 +104,13 @@ __device__ __forceinline__ int64_t apply_op_i(int op, int64_t a, int64_t b, int6
     case CDR_OP_ADD_IMM: return static_cast<int64_t>(static_cast<uint64_t>(a) + static_cast<uint64_t>(k));
     case CDR_OP_MUL_IMM: return static_cast<int64_t>(static_cast<uint64_t>(a) * static_cast<uint64_t>(k));
     case CDR_OP_RSUB_IMM: return static_cast<int64_t>(static_cast<uint64_t>(k) - static_cast<uint64_t>(a));
+    case CDR_OP_GT: return a > b;
+    case CDR_OP_GE: return a >= b;
+    case CDR_OP_LT: return a < b;
+    case CDR_OP_LE: return a <= b;
+    case CDR_OP_EQ: return a == b;
+    case CDR_OP_NE: return a != b;
+    case CDR_OP_WHERE: return a != 0 ? b : c;
     default: return 0;
   }
 }
@@ -400,7 +418,7 @@ int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out) {
   for (int k = 0; k < p->n_instr; ++k) {
     const cdr_ew_instr& i = p->instr[k];
     const int limit = n_in + k;  // only earlier registers may be read
-    if (i.op < CDR_OP_ADD || i.op > CDR_OP_RDIV_IMM) {
+    if (i.op < CDR_OP_ADD || i.op > CDR_OP_LAST) {
       set_error("elementwise: instruction %d has unknown op %d", k, i.op);
       return CDR_ERR_UNSUPPORTED;
     }

@@ -233,6 +233,17 @@ __device__ __forceinline__ float gen_op(int op, float a, float b, float c, float
     case CDR_OP_MUL_IMM: return __fmul_rn(a, imm);
     case CDR_OP_RSUB_IMM: return __fsub_rn(imm, a);
     case CDR_OP_RDIV_IMM: return __fdiv_rn(imm, a);
+    case CDR_OP_GT: return a > b ? 1.0f : 0.0f;
+    case CDR_OP_GE: return a >= b ? 1.0f : 0.0f;
+    case CDR_OP_LT: return a < b ? 1.0f : 0.0f;
+    case CDR_OP_LE: return a <= b ? 1.0f : 0.0f;
+    case CDR_OP_EQ: return a == b ? 1.0f : 0.0f;
+    case CDR_OP_NE: return a != b ? 1.0f : 0.0f;
+    case CDR_OP_WHERE: return a != 0.0f ? b : c;
+    case CDR_OP_RSQRT: return __fdiv_rn(1.0f, __fsqrt_rn(a));
+    case CDR_OP_SILU: return __fdiv_rn(a, __fadd_rn(1.0f, expf(-a)));
+    case CDR_OP_GELU: return __fmul_rn(__fmul_rn(a, 0.5f), __fadd_rn(1.0f, erff(__fmul_rn(a, 0.70710678118654752440f))));
+    case CDR_OP_ERF: return erff(a);
     default: return 0.0f;
   }
 }

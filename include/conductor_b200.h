@@ -126,8 +126,20 @@ enum cdr_ew_op {
   CDR_OP_ADD_IMM = 21, /* r[a] + imm                    */
   CDR_OP_MUL_IMM = 22, /* r[a] * imm                    */
   CDR_OP_RSUB_IMM = 23,/* imm - r[a]                    */
-  CDR_OP_RDIV_IMM = 24 /* imm / r[a]                    */
+  CDR_OP_RDIV_IMM = 24,/* imm / r[a]                    */
+  CDR_OP_GT = 25,      /* r[a] >  r[b] ? 1 : 0 (comparisons yield 1.0 / 0.0; NaN compares false, NE true) */
+  CDR_OP_GE = 26,
+  CDR_OP_LT = 27,
+  CDR_OP_LE = 28,
+  CDR_OP_EQ = 29,
+  CDR_OP_NE = 30,
+  CDR_OP_WHERE = 31,   /* r[a] != 0 ? r[b] : r[c]       */
+  CDR_OP_RSQRT = 32,   /* 1 / sqrt(r[a])                */
+  CDR_OP_SILU = 33,    /* r[a] / (1 + exp(-r[a]))       */
+  CDR_OP_GELU = 34,    /* 0.5 r[a] (1 + erf(r[a] / sqrt 2)) */
+  CDR_OP_ERF = 35
 };
+#define CDR_OP_LAST CDR_OP_ERF
 
 /* how an external input is indexed against the [rows, cols] view of the output */
 enum cdr_ew_mode {

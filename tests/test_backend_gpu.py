@@ -159,6 +159,46 @@ def test_wider_elementwise_and_reduction_coverage():
         assert_close(got, want, 2e-5 if name in ("reduce_then_scale",) else 1e-5, name)
 
 
+def test_comparison_select_and_activation_coverage():
+    """Comparisons and `where` inside a fused chain (1.0 / 0.0 registers), clamp family, constant
+    powers, rsqrt, silu, erf-gelu: selects and clamps exactly, transcendental ones within 1e-5."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(50)
+    x = torch.randn(72, 160, generator=gen)
+    y = torch.randn(72, 160, generator=gen)
+    x[0, 0], x[1, 1], y[2, 2] = float("nan"), 0.0, float("nan")
+    exact = {
+        "where_gt": lambda a, b: torch.where(a > 0, a, b * 0.5),
+        "relu_backward_mask": lambda a, b: b * (a > 0),
+        "compare_chain": lambda a, b: torch.where(a >= b, a - b, b - a) + (a == b) + (a != b) * 2.0 + (a < b) + (a <= b),
+        "clamp_family": lambda a, b: torch.clamp(a, -1.0, 2.0) + b.clamp(min=0.5) + torch.clamp(a, max=0.25)
+        + F.relu6(b) + F.hardtanh(a),
+        "const_powers": lambda a, b: a ** 2 + b.pow(3) + torch.square(a),
+    }
+    close = {
+        "rsqrt_recip": lambda a, b: torch.rsqrt(a * a + 1.0) + (b * b + 1.0).reciprocal() + (a * a + 0.5) ** 0.5,
+        "silu_gelu_erf": lambda a, b: F.silu(a) + F.gelu(b) + torch.erf(a * b),
+        "rms_norm": lambda a, b: a * torch.rsqrt((a * a).mean(-1, keepdim=True) + 1e-6) * b,
+    }
+    for name, fn in {**exact, **close}.items():
+        want = rp.run_reference(fn, [x, y])
+        got = compiled(fn)(x.to(DEV), y.to(DEV)).cpu()
+        if name in exact:
+            same = (got == want) | (torch.isnan(got) & torch.isnan(want))
+            assert bool(same.all()), f"{name}: {int((~same).sum())} elements differ"
+        else:
+            assert_close(got, want, 1e-5, name)
+    # bf16: the select runs in the chain's registers, results round per op like eager
+    xb, yb = x.bfloat16(), y.bfloat16()
+    fn = exact["where_gt"]
+    got = compiled(fn)(xb.to(DEV), yb.to(DEV)).cpu()
+    want = rp.run_reference(fn, [xb, yb])
+    same = (got == want) | (torch.isnan(got) & torch.isnan(want))
+    assert got.dtype == torch.bfloat16 and bool(same.all())
+    with pytest.raises(Exception):
+        compiled(lambda a: F.gelu(a, approximate="tanh"))(x.to(DEV))
+
+
 def test_integer_graph_is_bit_exact():
     a = torch.randint(-1000, 1000, (33, 65), dtype=torch.int32)
     b = torch.randint(-2**31, 2**31 - 1, (33, 65), dtype=torch.int32)
