@@ -47,19 +47,11 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t 
 namespace {
 
 constexpr int BQ = 256, BH_ROWS = 128, BKV = 128;   // query tile, rows per half, keys per block
-#ifndef CDR_ATT_WG
-#define CDR_ATT_WG 1
-#endif
-#if CDR_ATT_WG
 // Roles aligned to warp groups so that setmaxnreg can move registers from the control warps to the
 // softmax warps: group 0 = TMA warp, MMA warp and two idle warps; groups 1, 2 = softmax of half A, B.
 constexpr int ATT_THREADS = 384;
 constexpr int SOFTMAX_WARP0 = 4;
 constexpr int REGS_CONTROL = 80, REGS_SOFTMAX = 208;   // 128*80 + 256*208 <= 384*168, the CTA's allocation at launch
-#else
-constexpr int ATT_THREADS = 320;
-constexpr int SOFTMAX_WARP0 = 2;
-#endif
 constexpr int TMEM_S = 0, TMEM_O = 256, ATT_TMEM_COLS = 512;   // + 128 * half
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -224,10 +216,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   sm100::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-#if CDR_ATT_WG
   // one setmaxnreg per warp group, executed by all four of its warps
   if (warp < SOFTMAX_WARP0) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CONTROL));
-#endif
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     // Runs ahead of the consumers across tile boundaries: the ring index never resets, and the Q
@@ -372,9 +362,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       }
     }
   } else if (warp >= SOFTMAX_WARP0) {
-#if CDR_ATT_WG
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
-#endif
     // ------------------------------------------------------------ softmax / correction / epilogue
     const int g = (warp - SOFTMAX_WARP0) >> 2;       // half this warp group serves
     const int q = warp & 3;              // TMEM lane quadrant
@@ -511,6 +499,16 @@ int launch_attention_cfg(const AttnArgs& a, cudaStream_t stream) {
   int dev = 0;
   CDR_CUDA_TRY(cudaGetDevice(&dev));
   if (!configured_dev[dev & 63]) {
+    // setmaxnreg.inc waits until the CTA's register pool (threads x registers per thread at launch)
+    // can cover the request; if the compiled kernel ever got fewer registers than the split below
+    // assumes, that wait would never end -- refuse to launch instead
+    cudaFuncAttributes fa;
+    CDR_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
+    if (fa.numRegs * ATT_THREADS < 128 * REGS_CONTROL + (ATT_THREADS - 128) * REGS_SOFTMAX) {
+      set_error("attention: kernel was built with %d registers per thread, the register split needs %d", fa.numRegs,
+                (128 * REGS_CONTROL + (ATT_THREADS - 128) * REGS_SOFTMAX + ATT_THREADS - 1) / ATT_THREADS);
+      return CDR_ERR_UNSUPPORTED;
+    }
     CDR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     configured_dev[dev & 63] = true;
   }
