@@ -57,7 +57,8 @@ class CdrReduceParams(ctypes.Structure):
 
 
 class CdrGemmParams(ctypes.Structure):
-    _fields_ = [("activation", ctypes.c_int32), ("has_bias", ctypes.c_int32)]
+    _fields_ = [("activation", ctypes.c_int32), ("has_bias", ctypes.c_int32), ("weight_layout", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
 
 
 class CdrAttnParams(ctypes.Structure):
@@ -377,29 +378,44 @@ def _lower_softmax(cluster: FusionCluster) -> KernelLaunch:
     raise UnsupportedOperationError(node.op_name, "not a softmax operation")
 
 
+W_NK, W_KN = 0, 1   # cdr_weight_layout
+
+
 def _lower_gemm(cluster: FusionCluster) -> KernelLaunch:
+    """linear(x, W[N,K][, b]) -> out = x @ W^T (+ b); matmul / mm(x, W[K,N]) -> out = x @ W with the
+    weight read in place as an MN-major operand.  A following relu joins as the epilogue."""
     _require_shapes(cluster)
     node = cluster.nodes[0]
-    if node.op_name != "linear":
-        raise UnsupportedOperationError(node.op_name, "only linear(x, W, b) lowers to the GEMM template")
     spec = node.metadata.get("arg_spec", [])
     kws = node.metadata.get("kwarg_spec", {})
     ops = [s for s in spec if s[0] == "buf"]
-    if "bias" in kws and kws["bias"][0] == "buf":
-        ops.append(kws["bias"])
-    bufs = [node.inputs[s[1]] for s in ops]
-    if len(bufs) not in (2, 3):
-        raise UnsupportedOperationError("linear", "expected (x, weight[, bias])")
-    x, w = bufs[0], bufs[1]
-    if len(w.shape) != 2 or x.shape[-1] != w.shape[1]:
-        raise UnsupportedOperationError("linear", f"shapes {x.shape} x {w.shape}")
+    if node.op_name == "linear":
+        if "bias" in kws and kws["bias"][0] == "buf":
+            ops.append(kws["bias"])
+        bufs = [node.inputs[s[1]] for s in ops]
+        if len(bufs) not in (2, 3):
+            raise UnsupportedOperationError("linear", "expected (x, weight[, bias])")
+        x, w = bufs[0], bufs[1]
+        if len(w.shape) != 2 or x.shape[-1] != w.shape[1]:
+            raise UnsupportedOperationError("linear", f"shapes {x.shape} x {w.shape}")
+        layout = W_NK
+    elif get_op_desc(node.op_name).canonical_name == "matmul":
+        bufs = [node.inputs[s[1]] for s in ops]
+        if len(bufs) != 2:
+            raise UnsupportedOperationError(node.op_name, "expected two tensor operands")
+        x, w = bufs
+        if len(w.shape) != 2 or len(x.shape) < 2 or x.shape[-1] != w.shape[0]:
+            raise UnsupportedOperationError(node.op_name, f"shapes {x.shape} x {w.shape}: the right operand must be 2-D")
+        layout = W_KN
+    else:
+        raise UnsupportedOperationError(node.op_name, "no GEMM lowering")
     act = 0
     if len(cluster.nodes) == 2:
         if cluster.nodes[1].op_name != "relu":
             raise UnsupportedOperationError(cluster.signature(), "unsupported epilogue")
         act = 1
     out = cluster.external_outputs[0]
-    p = CdrGemmParams(act, 1 if len(bufs) == 3 else 0)
+    p = CdrGemmParams(act, 1 if len(bufs) == 3 else 0, layout, 0)
     return KernelLaunch(Template.GEMM_EPILOGUE, cluster.signature(), bufs, [out], p, [out.shape], [out.dtype],
                         cluster=cluster)
 

@@ -36,12 +36,13 @@ constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /
 
 struct GemmArgs {
   CUtensorMap tmap_a;  // x  [M, K], box 64 x 128
-  CUtensorMap tmap_b;  // W  [N, K], box 64 x 256
+  CUtensorMap tmap_b;  // W  [N, K], box 64 x 256 -- or, with w_kn, W [K, N], box 64 (N) x 64 (K)
   const void* bias;    // [N] or nullptr
   void* out;           // [M, N]
   int M, N, K;
   int relu;
   int is_bf16;
+  int w_kn;            // W is stored [K, N] (N contiguous): the B operand is MN-major
   int tiles_m, tiles_n;
   int* status;
 };
@@ -195,7 +196,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
           sm100::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
           unsigned char* st = smem + s * STAGE_BYTES;
           sm100::tma_load_2d(st, &a.tmap_a, kb * BK, m0, &full[s]);
-          sm100::tma_load_2d(st + A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
+          if (!a.w_kn) {
+            sm100::tma_load_2d(st + A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
+          } else {   // [K, N]: one box of 64 k-rows per 64 columns of N
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              sm100::tma_load_2d(st + A_BYTES + c * (BK * 128), &a.tmap_b, n0 + c * 64, kb * BK, &full[s]);
+          }
         }
       }
     }
@@ -206,6 +213,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     {
       const bool leader = sm100::elect_one();
       constexpr uint32_t idesc = sm100::umma_idesc_f16(BM, BN, BF16, false, false);
+      constexpr uint32_t idesc_kn = sm100::umma_idesc_f16(BM, BN, BF16, false, true);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
@@ -230,8 +238,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
-              const uint64_t bdesc = sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
-              sm100::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              // [N, K] weights are K-major like x; [K, N] weights are MN-major: 16 k-rows of 128
+              // bytes per step, 64-column atoms BK*128 bytes apart
+              const uint64_t bdesc = a.w_kn ? sm100::umma_desc_mn_sw128(b_addr + k * (UMMA_K * 128), BK * 128)
+                                            : sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
+              sm100::umma_f16_ss(d_tmem, adesc, bdesc, a.w_kn ? idesc_kn : idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             sm100::umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
           }
@@ -335,7 +346,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
           if (rank == 0) sm100::mbar_arrive_expect_tx(&full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
           unsigned char* st = smem + s * P_STAGE_BYTES;
           sm100::tma_load_2d_pair(st, &a.tmap_a, kb * BK, m0, &full[s]);
-          sm100::tma_load_2d_pair(st + P_A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
+          if (!a.w_kn) {
+            sm100::tma_load_2d_pair(st + P_A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
+          } else {   // [K, N]: this CTA's 128 columns of N as two boxes of 64 k-rows
+            sm100::tma_load_2d_pair(st + P_A_BYTES, &a.tmap_b, n0, kb * BK, &full[s]);
+            sm100::tma_load_2d_pair(st + P_A_BYTES + BK * 128, &a.tmap_b, n0 + 64, kb * BK, &full[s]);
+          }
         }
       }
     }
@@ -346,6 +362,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
     if (rank == 0) {
       const bool leader = sm100::elect_one();
       constexpr uint32_t idesc = sm100::umma_idesc_f16(P_BM, P_BN, BF16, false, false);
+      constexpr uint32_t idesc_kn = sm100::umma_idesc_f16(P_BM, P_BN, BF16, false, true);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++tile_iter) {
@@ -370,8 +387,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
-              const uint64_t bdesc = sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
-              sm100::umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              const uint64_t bdesc = a.w_kn ? sm100::umma_desc_mn_sw128(b_addr + k * (UMMA_K * 128), BK * 128)
+                                            : sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
+              sm100::umma_f16_ss_pair(d_tmem, adesc, bdesc, a.w_kn ? idesc_kn : idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             sm100::umma_commit_pair(&empty[s], 3);   // frees the stage in both CTAs
           }
@@ -477,8 +495,13 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   if (x.rank < 1 || w.rank != 2) { set_error("gemm_epilogue: x needs rank >= 1 and W rank 2"); return CDR_ERR_BAD_ARG; }
   const int64_t K = x.shape[x.rank - 1];
   const int64_t M = K ? numel(x) / K : 0;
-  const int64_t N = w.shape[0];
-  if (w.shape[1] != K) { set_error("gemm_epilogue: x has K=%lld, W has K=%lld", (long long)K, (long long)w.shape[1]); return CDR_ERR_BAD_ARG; }
+  const bool w_kn = p->weight_layout == CDR_W_KN;
+  if (p->weight_layout != CDR_W_NK && !w_kn) { set_error("gemm_epilogue: unknown weight layout %d", p->weight_layout); return CDR_ERR_BAD_ARG; }
+  const int64_t N = w.shape[w_kn ? 1 : 0];
+  if (w.shape[w_kn ? 0 : 1] != K) {
+    set_error("gemm_epilogue: x has K=%lld, W has K=%lld", (long long)K, (long long)w.shape[w_kn ? 0 : 1]);
+    return CDR_ERR_BAD_ARG;
+  }
   if (numel(out) != M * N) { set_error("gemm_epilogue: output must hold %lld elements", (long long)(M * N)); return CDR_ERR_BAD_ARG; }
   const int dt = x.dtype;
   if (dt != CDR_BF16 && dt != CDR_F16) { set_error("gemm_epilogue: dtype %d unsupported (bf16 and f16 only)", dt); return CDR_ERR_UNSUPPORTED; }
@@ -495,12 +518,16 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   if (K == 0) { set_error("gemm_epilogue: K == 0"); return CDR_ERR_UNSUPPORTED; }
   if (!x.data || !w.data || !out.data || (p->has_bias && !ins[2].data)) { set_error("gemm_epilogue: null pointer"); return CDR_ERR_BAD_ARG; }
   if (K % 8 != 0) { set_error("gemm_epilogue: K=%lld must be a multiple of 8 (16-byte row pitch for TMA)", (long long)K); return CDR_ERR_UNSUPPORTED; }
+  if (w_kn && N % 8 != 0) { set_error("gemm_epilogue: N=%lld must be a multiple of 8 for [K, N] weights", (long long)N); return CDR_ERR_UNSUPPORTED; }
   if (!aligned16(x.data) || !aligned16(w.data)) { set_error("gemm_epilogue: x and W must be 16-byte aligned"); return CDR_ERR_MISALIGNED; }
   if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) { set_error("gemm_epilogue: extent too large"); return CDR_ERR_UNSUPPORTED; }
 
   GemmArgs a;
   if (int rc = make_tensor_map_2d(&a.tmap_a, x.data, dt == CDR_BF16, M, K, BM, BK)) return rc;
-  if (int rc = make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, BN, BK)) return rc;
+  // [K, N] weights: rows are k, 64 columns of N (128 bytes) per box, BK rows
+  if (int rc = w_kn ? make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, K, N, BK, 64)
+                    : make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, BN, BK)) return rc;
+  a.w_kn = w_kn ? 1 : 0;
   a.bias = p->has_bias ? ins[2].data : nullptr;
   a.out = out.data;
   a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
@@ -526,7 +553,8 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   if (M >= P_BM && N >= P_BN) {
     // CTA-pair kernel: 256 x 256 tiles, clusters of two CTAs, at most one cluster per TPC.
     // Each CTA stages only 128 of the tile's 256 weight rows: the W box is 64 x 128 here.
-    if (int rc = make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, 128, BK)) return rc;
+    if (!w_kn)
+      if (int rc = make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, 128, BK)) return rc;
     a.tiles_m = static_cast<int>((M + P_BM - 1) / P_BM);
     a.tiles_n = static_cast<int>((N + P_BN - 1) / P_BN);
     const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;

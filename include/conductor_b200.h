@@ -88,7 +88,7 @@ enum cdr_template {
                              params = cdr_reduce_params                                  */
   CDR_T_SOFTMAX_FWD = 3,  /* row softmax over the last dim, no params                    */
   CDR_T_SOFTMAX_BWD = 4,  /* inputs (grad_out, y): dx = y * (g - sum(g*y)), no params    */
-  CDR_T_GEMM_EPILOGUE = 5,/* out = act(x @ W^T + bias), params = cdr_gemm_params         */
+  CDR_T_GEMM_EPILOGUE = 5,/* out = act(x @ W^T + bias) or act(x @ W + bias), params = cdr_gemm_params */
   CDR_T_ATTENTION = 6,    /* fused scaled-dot-product attention, params = cdr_attn_params*/
   CDR_T_FULL_REDUCE = 7   /* elementwise chain + reduction over every element,
                              params = cdr_reduce_params; needs workspace                 */
@@ -180,9 +180,16 @@ typedef struct cdr_reduce_params {
 
 enum cdr_activation { CDR_ACT_NONE = 0, CDR_ACT_RELU = 1 };
 
+enum cdr_weight_layout {
+  CDR_W_NK = 0, /* W is [N, K], K contiguous: out = x @ W^T  (torch.nn.functional.linear) */
+  CDR_W_KN = 1  /* W is [K, N], N contiguous: out = x @ W    (torch.matmul)               */
+};
+
 typedef struct cdr_gemm_params {
-  int32_t activation; /* enum cdr_activation                       */
-  int32_t has_bias;   /* 1: inputs are (x, W, bias); 0: (x, W)     */
+  int32_t activation;    /* enum cdr_activation                       */
+  int32_t has_bias;      /* 1: inputs are (x, W, bias); 0: (x, W)     */
+  int32_t weight_layout; /* enum cdr_weight_layout                    */
+  int32_t reserved;
 } cdr_gemm_params;
 
 typedef struct cdr_attn_params {

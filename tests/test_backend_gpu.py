@@ -199,6 +199,22 @@ def test_comparison_select_and_activation_coverage():
         compiled(lambda a: F.gelu(a, approximate="tanh"))(x.to(DEV))
 
 
+def test_matmul_operator_forms():
+    """`x @ w`, torch.mm and torch.matmul with a 2-D right operand lower to the GEMM template with the
+    weight read in place; a relu behind it runs as its own cluster."""
+    gen = torch.Generator().manual_seed(51)
+    x = torch.randn(3, 200, 256, generator=gen).bfloat16()
+    w = (torch.randn(256, 384, generator=gen) / 16).bfloat16()
+    for name, fn in {"matmul_relu": lambda a, b: torch.relu(a @ b), "matmul_scale": lambda a, b: torch.matmul(a, b) * 0.5}.items():
+        want = rp.run_reference(fn, [x, w])
+        got = compiled(fn)(x.to(DEV), w.to(DEV))
+        assert got.shape == want.shape
+        assert_close(got.float(), want.float(), 2e-2, name)
+    x2 = x[0].contiguous()
+    assert_close(compiled(lambda a, b: torch.mm(a, b))(x2.to(DEV), w.to(DEV)).float(),
+                 rp.run_reference(lambda a, b: torch.mm(a, b), [x2, w]).float(), 2e-2, "mm")
+
+
 def test_integer_graph_is_bit_exact():
     a = torch.randint(-1000, 1000, (33, 65), dtype=torch.int32)
     b = torch.randint(-2**31, 2**31 - 1, (33, 65), dtype=torch.int32)

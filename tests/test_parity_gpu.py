@@ -504,6 +504,29 @@ def test_gemm_without_bias_fp16_and_3d_input(executor):
     assert_close(out.float(), (x.float() @ w.float().T), BF16_TOL, "fp16 gemm")
 
 
+@pytest.mark.parametrize("M,N,K,relu", [(128, 256, 64, False), (300, 520, 200, True), (1024, 1024, 512, False),
+                                        (77, 72, 96, False), (2048, 256, 4096, True)])
+def test_gemm_with_k_by_n_weights(executor, M, N, K, relu):
+    """out = x @ W with W stored [K, N] (torch.matmul): the weight is read in place as an MN-major
+    operand; same numbers as the [N, K] form on the transposed weight, and as the oracle."""
+    gen = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=gen).bfloat16()
+    w_kn = (torch.randn(K, N, generator=gen) / K ** 0.5).bfloat16()
+    b = torch.randn(N, generator=gen).bfloat16()
+    dx, dw, db = cuda(x, w_kn, b)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    abi.launch(Template.GEMM_EPILOGUE, [dx, dw, db], [out], CdrGemmParams(1 if relu else 0, 1, 1, 0))
+    same = gemm(dx, dw.t().contiguous(), db, relu=relu)
+    assert bits_equal(out, same), "[K, N] and [N, K] forms differ"
+    want = bf16_bits_to_tensor(scalar.linear_bf16(tensor_to_bf16_bits(x), tensor_to_bf16_bits(w_kn.t().contiguous()),
+                                                  tensor_to_bf16_bits(b), relu=relu)).float()
+    assert_close(out.float(), want, BF16_TOL, f"x @ W[K,N] {M}x{N}x{K}")
+    # N not a multiple of 8 has no 16-byte row pitch in this layout
+    bad = torch.randn(64, 12, device=DEV).bfloat16()
+    assert abi.launch(Template.GEMM_EPILOGUE, [torch.randn(8, 64, device=DEV).bfloat16(), bad],
+                      [torch.empty(8, 12, device=DEV, dtype=torch.bfloat16)], CdrGemmParams(0, 0, 1, 0), check=False) == -2
+
+
 def test_gemm_rejects_what_it_cannot_run(executor):
     x = torch.randn(8, 12, device=DEV).bfloat16()         # K=12: row pitch not a multiple of 16 bytes
     w = torch.randn(8, 12, device=DEV).bfloat16()
