@@ -5,7 +5,9 @@ hands Dynamo's forward graph straight to the compiler), so a ``gcu``-compiled fu
 backward.  Here a plan whose single kernel is the row softmax becomes differentiable: when
 gradients are enabled and the input requires them, the forward launch goes through
 :class:`SoftmaxFunction`, whose backward launches the softmax-backward template
-(``dx = y * (g - sum(g * y))``) on the same C ABI.  Other plans stay forward-only and say so.
+(``dx = y * (g - sum(g * y))``) on the same C ABI, and a plan that is a chain of linear(+relu)
+kernels goes through :class:`LinearChainFunction`, whose backward is again GEMM-template launches.
+Other plans stay forward-only and say so.
 """
 from __future__ import annotations
 
@@ -40,11 +42,14 @@ class SoftmaxFunction(torch.autograd.Function):
         return dx, None, None
 
 
-def differentiable_kind(launches) -> str:
-    """'softmax' when the plan is exactly one softmax-forward kernel, else ''."""
+def differentiable_kind(launches, dag_inputs=None) -> str:
+    """'softmax' when the plan is exactly one softmax-forward kernel, 'linear_chain' when it is a
+    chain of linear(+relu) kernels whose weights are graph inputs, else ''."""
     kernels = [l for l in launches if l.template]
     if len(kernels) == 1 and kernels[0].template == Template.SOFTMAX_FWD and len(launches) == 1:
         return "softmax"
+    if dag_inputs is not None and len(kernels) == len(launches) and linear_chain_layers(launches, dag_inputs):
+        return "linear_chain"
     return ""
 
 
@@ -54,3 +59,104 @@ def require_differentiable(launches) -> None:
         raise UnsupportedOperationError(
             names or "graph", "backward is only available for a plan that is one row-softmax kernel; "
             "run other graphs under torch.no_grad() or detach their inputs")
+
+
+# ---------------------------------------------------------------------------------------------
+# Chains of linear layers (C4: Linear -> ReLU -> Linear).  Every gradient is again a launch of the
+# GEMM template: the operand-layout switches of `cdr_gemm_params` let it read dY, x and W in place
+# as the transposed operands the three products need, so no tensor is ever transposed in memory.
+#   dX = dY @ W              x = dY [M, N],            W [N, K] read as [K'=N, N'=K]   (weight_layout KN)
+#   dW = dY^T @ x            x = dY read as [K'=M, M'=N] (x_layout KM), W = x [M, K] read as [K'=M, N'=K]
+#   db = 1^T @ dY            x = ones [1, M],          W = dY read as [K'=M, N'=N]
+# and the ReLU mask dZ = dH * (H > 0) is one elementwise launch.
+def _gemm_launch(name, out_shape, dtype, weight_layout=0, x_layout=0) -> KernelLaunch:
+    from ..codegen.kernel_templates import CdrGemmParams
+
+    return KernelLaunch(Template.GEMM_EPILOGUE, name, [], [], CdrGemmParams(0, 0, weight_layout, x_layout),
+                        [tuple(out_shape)], [dtype])
+
+
+def _relu_mask_launch(shape, dtype) -> KernelLaunch:
+    from ..codegen.kernel_templates import CdrEwInstr, CdrEwParams
+    from ..codegen.operator_registry import EwOp
+    from ..utils.type_mapping import to_cdr_dtype
+
+    p = CdrEwParams()
+    p.n_inputs, p.n_instr, p.n_outputs = 2, 3, 1          # r0 = grad, r1 = activation output
+    p.instr[0] = CdrEwInstr(EwOp.CONST, 0, 0, 0, 0.0, to_cdr_dtype(torch.float32))
+    p.instr[1] = CdrEwInstr(EwOp.GT, 1, 2, 0, 0.0, to_cdr_dtype(torch.float32))
+    p.instr[2] = CdrEwInstr(EwOp.MUL, 0, 3, 0, 0.0, to_cdr_dtype(dtype))
+    p.out_reg[0] = 4
+    return KernelLaunch(Template.ELEMENTWISE, "relu_backward[autograd]", [], [], p, [tuple(shape)], [dtype])
+
+
+def linear_chain_layers(launches, dag_inputs):
+    """[(launch, has_bias)] when the plan is a chain of linear(+relu) kernels fed by graph inputs."""
+    if not launches:
+        return None
+    prev_out = None
+    layers = []
+    for i, l in enumerate(launches):
+        p = l.params
+        if l.template != Template.GEMM_EPILOGUE or p is None or p.weight_layout != 0 or p.x_layout != 0:
+            return None
+        if len(l.inputs) not in (2, 3) or len(l.outputs) != 1:
+            return None
+        if i == 0:
+            if l.inputs[0] not in dag_inputs:
+                return None
+        elif l.inputs[0] is not prev_out:
+            return None
+        if any(b not in dag_inputs for b in l.inputs[1:]):
+            return None
+        layers.append((l, len(l.inputs) == 3))
+        prev_out = l.outputs[0]
+    return layers
+
+
+class LinearChainFunction(torch.autograd.Function):
+    """Forward: the plan's GEMM launches.  Backward: GEMM launches with transposed-operand layouts."""
+
+    @staticmethod
+    def forward(ctx, executor, layers, x, *params):
+        ctx.executor, ctx.layers = executor, layers
+        acts = [x.detach()]
+        it = iter(params)
+        weights = []
+        for launch, has_bias in layers:
+            w = next(it).detach()
+            ins = [acts[-1], w] + ([next(it).detach()] if has_bias else [])
+            (h,) = executor.execute(launch, ins)
+            acts.append(h)
+            weights.append(w)
+        ctx.save_for_backward(*acts, *weights)
+        ctx.n_layers = len(layers)
+        return acts[-1]
+
+    @staticmethod
+    def backward(ctx, grad):
+        ex, layers, n = ctx.executor, ctx.layers, ctx.n_layers
+        saved = ctx.saved_tensors
+        acts, weights = saved[:n + 1], saved[n + 1:]
+        dt = acts[0].dtype
+        g = grad.contiguous().to(dt)
+        param_grads = []
+        for i in range(n - 1, -1, -1):
+            launch, has_bias = layers[i]
+            w, x, h = weights[i], acts[i], acts[i + 1]
+            N, K = w.shape
+            g2 = g.reshape(-1, N)
+            x2 = x.reshape(-1, K)
+            M = g2.shape[0]
+            if launch.params.activation == 1:
+                (g2,) = ex.execute(_relu_mask_launch(g2.shape, dt), [g2, h.reshape(-1, N)])
+            db = None
+            if has_bias:
+                ones = torch.ones(1, M, dtype=dt, device=g2.device)
+                (db,) = ex.execute(_gemm_launch("bias_grad[autograd]", (1, N), dt, weight_layout=1), [ones, g2])
+                db = db.reshape(N)
+            (dw,) = ex.execute(_gemm_launch("weight_grad[autograd]", (N, K), dt, weight_layout=1, x_layout=1), [g2, x2])
+            (dx,) = ex.execute(_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w])
+            param_grads = [dw] + ([db] if has_bias else []) + param_grads
+            g = dx.reshape(x.shape)
+        return (None, None, g, *param_grads)

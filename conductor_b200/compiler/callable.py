@@ -123,11 +123,18 @@ class Callable:
                         break
             outputs = None
             if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
-                from .autograd import SoftmaxFunction, differentiable_kind
+                from .autograd import LinearChainFunction, SoftmaxFunction, differentiable_kind, linear_chain_layers
 
-                if not host_mode and rows is None and differentiable_kind(self.launches) == "softmax":
+                kind = differentiable_kind(self.launches, dag.inputs) if not host_mode and rows is None else ""
+                if kind == "softmax":
                     # forward through an autograd.Function whose backward is the softmax-backward template
                     outputs = [SoftmaxFunction.apply(env[dag.inputs[0]], self._exec(), self.launches[0])]
+                elif kind == "linear_chain" and len(dag.output_spec) == 1 and dag.output_spec[0] is self.launches[-1].outputs[0]:
+                    layers = linear_chain_layers(self.launches, dag.inputs)
+                    operands = [env[self.launches[0].inputs[0]]]
+                    for l, _ in layers:
+                        operands += [env[b] for b in l.inputs[1:]]
+                    outputs = [LinearChainFunction.apply(self._exec(), layers, *operands)]
                 elif not self._warned_no_grad:
                     self._warned_no_grad = True
                     logger.warning("%s: inputs require grad but this plan has no backward; outputs are detached",

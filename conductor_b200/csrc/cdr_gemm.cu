@@ -35,7 +35,7 @@ constexpr int EPI_CHUNKS = BN / 32 / 2;   // 32-column chunks per epilogue warp
 constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct GemmArgs {
-  CUtensorMap tmap_a;  // x  [M, K], box 64 x 128
+  CUtensorMap tmap_a;  // x  [M, K], box 64 x 128 -- or, with x_km, x [K, M], box 64 (M) x 64 (K)
   CUtensorMap tmap_b;  // W  [N, K], box 64 x 256 -- or, with w_kn, W [K, N], box 64 (N) x 64 (K)
   const void* bias;    // [N] or nullptr
   void* out;           // [M, N]
@@ -43,6 +43,7 @@ struct GemmArgs {
   int relu;
   int is_bf16;
   int w_kn;            // W is stored [K, N] (N contiguous): the B operand is MN-major
+  int x_km;            // x is stored [K, M] (M contiguous): the A operand is MN-major
   int tiles_m, tiles_n;
   int* status;
 };
@@ -195,7 +196,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
           if (!sm100::mbar_wait(&empty[s], ph ^ 1)) { sm100::report_timeout(a.status, 10); ok = false; break; }
           sm100::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
           unsigned char* st = smem + s * STAGE_BYTES;
-          sm100::tma_load_2d(st, &a.tmap_a, kb * BK, m0, &full[s]);
+          if (!a.x_km) {
+            sm100::tma_load_2d(st, &a.tmap_a, kb * BK, m0, &full[s]);
+          } else {   // [K, M]: one box of 64 k-rows per 64 rows of the tile
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              sm100::tma_load_2d(st + c * (BK * 128), &a.tmap_a, m0 + c * 64, kb * BK, &full[s]);
+          }
           if (!a.w_kn) {
             sm100::tma_load_2d(st + A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
           } else {   // [K, N]: one box of 64 k-rows per 64 columns of N
@@ -212,8 +219,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     // instructions, so the operand descriptors stay in uniform registers.
     {
       const bool leader = sm100::elect_one();
-      constexpr uint32_t idesc = sm100::umma_idesc_f16(BM, BN, BF16, false, false);
-      constexpr uint32_t idesc_kn = sm100::umma_idesc_f16(BM, BN, BF16, false, true);
+      const uint32_t idesc = sm100::umma_idesc_f16(BM, BN, BF16, a.x_km != 0, a.w_kn != 0);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
@@ -237,12 +243,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
           if (leader) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
+              const uint64_t adesc = a.x_km ? sm100::umma_desc_mn_sw128(a_addr + k * (UMMA_K * 128), BK * 128)
+                                            : sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
               // [N, K] weights are K-major like x; [K, N] weights are MN-major: 16 k-rows of 128
               // bytes per step, 64-column atoms BK*128 bytes apart
               const uint64_t bdesc = a.w_kn ? sm100::umma_desc_mn_sw128(b_addr + k * (UMMA_K * 128), BK * 128)
                                             : sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
-              sm100::umma_f16_ss(d_tmem, adesc, bdesc, a.w_kn ? idesc_kn : idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              sm100::umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             sm100::umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
           }
@@ -345,7 +352,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
           if (!sm100::mbar_wait(&empty[s], ph ^ 1)) { sm100::report_timeout(a.status, 30); ok = false; break; }
           if (rank == 0) sm100::mbar_arrive_expect_tx(&full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
           unsigned char* st = smem + s * P_STAGE_BYTES;
-          sm100::tma_load_2d_pair(st, &a.tmap_a, kb * BK, m0, &full[s]);
+          if (!a.x_km) {
+            sm100::tma_load_2d_pair(st, &a.tmap_a, kb * BK, m0, &full[s]);
+          } else {   // [K, M]: this CTA's 128 rows of the tile as two boxes of 64 k-rows
+            sm100::tma_load_2d_pair(st, &a.tmap_a, m0, kb * BK, &full[s]);
+            sm100::tma_load_2d_pair(st + BK * 128, &a.tmap_a, m0 + 64, kb * BK, &full[s]);
+          }
           if (!a.w_kn) {
             sm100::tma_load_2d_pair(st + P_A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
           } else {   // [K, N]: this CTA's 128 columns of N as two boxes of 64 k-rows
@@ -361,8 +373,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
     // instructions, so the operand descriptors stay in uniform registers.
     if (rank == 0) {
       const bool leader = sm100::elect_one();
-      constexpr uint32_t idesc = sm100::umma_idesc_f16(P_BM, P_BN, BF16, false, false);
-      constexpr uint32_t idesc_kn = sm100::umma_idesc_f16(P_BM, P_BN, BF16, false, true);
+      const uint32_t idesc = sm100::umma_idesc_f16(P_BM, P_BN, BF16, a.x_km != 0, a.w_kn != 0);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++tile_iter) {
@@ -386,10 +397,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
           if (leader) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t adesc = sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
+              const uint64_t adesc = a.x_km ? sm100::umma_desc_mn_sw128(a_addr + k * (UMMA_K * 128), BK * 128)
+                                            : sm100::umma_desc_k_sw128(a_addr + k * (UMMA_K * 2));
               const uint64_t bdesc = a.w_kn ? sm100::umma_desc_mn_sw128(b_addr + k * (UMMA_K * 128), BK * 128)
                                             : sm100::umma_desc_k_sw128(b_addr + k * (UMMA_K * 2));
-              sm100::umma_f16_ss_pair(d_tmem, adesc, bdesc, a.w_kn ? idesc_kn : idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              sm100::umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             sm100::umma_commit_pair(&empty[s], 3);   // frees the stage in both CTAs
           }
@@ -493,8 +505,11 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   }
   const cdr_tensor &x = ins[0], &w = ins[1], &out = outs[0];
   if (x.rank < 1 || w.rank != 2) { set_error("gemm_epilogue: x needs rank >= 1 and W rank 2"); return CDR_ERR_BAD_ARG; }
-  const int64_t K = x.shape[x.rank - 1];
-  const int64_t M = K ? numel(x) / K : 0;
+  const bool x_km = p->x_layout == CDR_X_KM;
+  if (p->x_layout != CDR_X_MK && !x_km) { set_error("gemm_epilogue: unknown x layout %d", p->x_layout); return CDR_ERR_BAD_ARG; }
+  if (x_km && x.rank != 2) { set_error("gemm_epilogue: [K, M] x must have rank 2"); return CDR_ERR_BAD_ARG; }
+  const int64_t K = x_km ? x.shape[0] : x.shape[x.rank - 1];
+  const int64_t M = x_km ? x.shape[1] : (K ? numel(x) / K : 0);
   const bool w_kn = p->weight_layout == CDR_W_KN;
   if (p->weight_layout != CDR_W_NK && !w_kn) { set_error("gemm_epilogue: unknown weight layout %d", p->weight_layout); return CDR_ERR_BAD_ARG; }
   const int64_t N = w.shape[w_kn ? 1 : 0];
@@ -517,13 +532,16 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   if (M == 0 || N == 0) return CDR_OK;
   if (K == 0) { set_error("gemm_epilogue: K == 0"); return CDR_ERR_UNSUPPORTED; }
   if (!x.data || !w.data || !out.data || (p->has_bias && !ins[2].data)) { set_error("gemm_epilogue: null pointer"); return CDR_ERR_BAD_ARG; }
-  if (K % 8 != 0) { set_error("gemm_epilogue: K=%lld must be a multiple of 8 (16-byte row pitch for TMA)", (long long)K); return CDR_ERR_UNSUPPORTED; }
+  if (K % 8 != 0 && !(x_km && w_kn)) { set_error("gemm_epilogue: K=%lld must be a multiple of 8 (16-byte row pitch for TMA)", (long long)K); return CDR_ERR_UNSUPPORTED; }
+  if (x_km && M % 8 != 0) { set_error("gemm_epilogue: M=%lld must be a multiple of 8 for [K, M] x", (long long)M); return CDR_ERR_UNSUPPORTED; }
   if (w_kn && N % 8 != 0) { set_error("gemm_epilogue: N=%lld must be a multiple of 8 for [K, N] weights", (long long)N); return CDR_ERR_UNSUPPORTED; }
   if (!aligned16(x.data) || !aligned16(w.data)) { set_error("gemm_epilogue: x and W must be 16-byte aligned"); return CDR_ERR_MISALIGNED; }
   if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) { set_error("gemm_epilogue: extent too large"); return CDR_ERR_UNSUPPORTED; }
 
   GemmArgs a;
-  if (int rc = make_tensor_map_2d(&a.tmap_a, x.data, dt == CDR_BF16, M, K, BM, BK)) return rc;
+  if (int rc = x_km ? make_tensor_map_2d(&a.tmap_a, x.data, dt == CDR_BF16, K, M, BK, 64)
+                    : make_tensor_map_2d(&a.tmap_a, x.data, dt == CDR_BF16, M, K, BM, BK)) return rc;
+  a.x_km = x_km ? 1 : 0;
   // [K, N] weights: rows are k, 64 columns of N (128 bytes) per box, BK rows
   if (int rc = w_kn ? make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, K, N, BK, 64)
                     : make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, BN, BK)) return rc;

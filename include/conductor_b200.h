@@ -185,11 +185,16 @@ enum cdr_weight_layout {
   CDR_W_KN = 1  /* W is [K, N], N contiguous: out = x @ W    (torch.matmul)               */
 };
 
+enum cdr_x_layout {
+  CDR_X_MK = 0, /* x is [..., K], K contiguous                                            */
+  CDR_X_KM = 1  /* x is [K, M], M contiguous: out = x^T @ ...  (weight gradients)          */
+};
+
 typedef struct cdr_gemm_params {
   int32_t activation;    /* enum cdr_activation                       */
   int32_t has_bias;      /* 1: inputs are (x, W, bias); 0: (x, W)     */
   int32_t weight_layout; /* enum cdr_weight_layout                    */
-  int32_t reserved;
+  int32_t x_layout;      /* enum cdr_x_layout                         */
 } cdr_gemm_params;
 
 typedef struct cdr_attn_params {

@@ -199,6 +199,33 @@ def test_comparison_select_and_activation_coverage():
         compiled(lambda a: F.gelu(a, approximate="tanh"))(x.to(DEV))
 
 
+def test_mlp_is_differentiable_through_the_backend():
+    """loss.backward() through a gcu-compiled Linear -> ReLU -> Linear: every gradient is a launch of
+    the GEMM template with transposed-operand layouts (plus one elementwise launch for the ReLU mask)."""
+    torch.manual_seed(52)
+    ref = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 128)).bfloat16()
+    import copy
+
+    dev = copy.deepcopy(ref).to(DEV)
+    x = torch.randn(4, 96, 256).bfloat16()
+    xr = x.clone().requires_grad_(True)
+    out_ref = ref(xr)
+    gout = torch.randn(out_ref.shape).bfloat16()
+    out_ref.backward(gout)
+
+    xd = x.to(DEV).requires_grad_(True)
+    f = compiled(dev)
+    out = f(xd)
+    assert out.requires_grad and out.grad_fn is not None
+    assert_close(out.float(), out_ref.float(), 2e-2, "mlp forward")
+    out.backward(gout.to(DEV))
+    assert_close(xd.grad.float(), xr.grad.float(), 2e-2, "d/dx")
+    for (name, p_ref), p_dev in zip(ref.named_parameters(), dev.parameters()):
+        assert p_dev.grad is not None, name
+        scale = float(p_ref.grad.float().abs().max())
+        assert float((p_dev.grad.float().cpu() - p_ref.grad.float()).abs().max()) <= 2e-2 * max(scale, 1.0), name
+
+
 def test_matmul_operator_forms():
     """`x @ w`, torch.mm and torch.matmul with a 2-D right operand lower to the GEMM template with the
     weight read in place; a relu behind it runs as its own cluster."""

@@ -527,6 +527,26 @@ def test_gemm_with_k_by_n_weights(executor, M, N, K, relu):
                       [torch.empty(8, 12, device=DEV, dtype=torch.bfloat16)], CdrGemmParams(0, 0, 1, 0), check=False) == -2
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (296, 520, 200), (1024, 512, 2048), (72, 80, 100)])
+def test_gemm_with_transposed_x(executor, M, N, K):
+    """x stored [K, M] (MN-major A operand), alone and together with [K, N] weights -- the form a
+    weight gradient dW = dY^T @ x takes.  Bit-identical to the plain form on explicit transposes."""
+    gen = torch.Generator().manual_seed(2 * M + N + K)
+    x_km = torch.randn(K, M, generator=gen).bfloat16()
+    w_nk = (torch.randn(N, K, generator=gen) / K ** 0.5).bfloat16()
+    dx, dw = cuda(x_km, w_nk)
+    plain = gemm(dx.t().contiguous(), dw) if K % 8 == 0 else None    # the plain form needs a 16-byte K pitch
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    if K % 8 == 0:
+        abi.launch(Template.GEMM_EPILOGUE, [dx, dw], [out], CdrGemmParams(0, 0, 0, 1))
+        assert bits_equal(out, plain), "[K, M] x with [N, K] weights"
+    out2 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    abi.launch(Template.GEMM_EPILOGUE, [dx, dw.t().contiguous()], [out2], CdrGemmParams(0, 0, 1, 1))
+    if K % 8 == 0:
+        assert bits_equal(out2, plain), "[K, M] x with [K, N] weights"
+    assert_close(out2.float(), x_km.float().t() @ w_nk.float().t(), BF16_TOL, "x^T @ W")
+
+
 def test_gemm_rejects_what_it_cannot_run(executor):
     x = torch.randn(8, 12, device=DEV).bfloat16()         # K=12: row pitch not a multiple of 16 bytes
     w = torch.randn(8, 12, device=DEV).bfloat16()
