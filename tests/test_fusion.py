@@ -149,6 +149,47 @@ def test_scalars_lower_to_immediates():
     assert ops[:2] == [EwOp.MUL_IMM, EwOp.ADD_IMM] and EwOp.DIV in ops and ops[-1] == EwOp.SUB
 
 
+def test_comparison_where_clamp_and_pow_lowering():
+    F = torch.nn.functional
+    x, y = torch.randn(4, 16), torch.randn(4, 16)
+
+    def ops_of(fn, inputs):
+        (k,) = kernels(compile_with_dynamo(fn, inputs))
+        return [(k.params.instr[i].op, round(k.params.instr[i].imm, 3)) for i in range(k.params.n_instr)]
+
+    ops = ops_of(lambda a, b: torch.where(a > 0, a, b * 0.5), [x, y])
+    assert [o for o, _ in ops] == [EwOp.CONST, EwOp.GT, EwOp.MUL_IMM, EwOp.WHERE]
+    ops = ops_of(lambda a: torch.clamp(a, -1.0, 2.0), [x])
+    assert ops == [(EwOp.CONST, -1.0), (EwOp.MAX, 0.0), (EwOp.CONST, 2.0), (EwOp.MIN, 0.0)]
+    assert ops_of(lambda a: F.relu6(a), [x]) == [(EwOp.CONST, 0.0), (EwOp.MAX, 0.0), (EwOp.CONST, 6.0), (EwOp.MIN, 0.0)]
+    assert [o for o, _ in ops_of(lambda a: a ** 2 + a.pow(3), [x])] == [EwOp.MUL, EwOp.MUL, EwOp.MUL, EwOp.ADD]
+    got = [o for o, _ in ops_of(lambda a: F.silu(a) + F.gelu(a) + torch.rsqrt(a) + torch.erf(a), [x])]
+    assert sorted(got) == sorted([EwOp.SILU, EwOp.GELU, EwOp.RSQRT, EwOp.ERF, EwOp.ADD, EwOp.ADD, EwOp.ADD])
+    assert_unsupported(lambda a: F.gelu(a, approximate="tanh"), [x])
+    assert_unsupported(lambda a: a ** 2.5, [x])
+
+
+def test_matmul_lowers_to_the_gemm_template_with_the_weight_in_place():
+    x, w = torch.randn(2, 64, 32).bfloat16(), torch.randn(32, 48).bfloat16()
+    art = compile_with_dynamo(lambda a, b: torch.relu(a @ b), [x, w])
+    ks = kernels(art)
+    assert [k.template for k in ks] == [Template.GEMM_EPILOGUE, Template.ELEMENTWISE]
+    assert ks[0].params.weight_layout == 1 and ks[0].params.x_layout == 0 and ks[0].out_shapes == [(2, 64, 48)]
+    assert_unsupported(lambda a, b: a @ b, [torch.randn(2, 8, 16), torch.randn(2, 16, 8)])     # batched right operand
+
+
+def test_linear_chain_is_recognised_for_autograd():
+    from conductor_b200.compiler.autograd import differentiable_kind, linear_chain_layers
+
+    mlp, x = wl.make_mlp(32, 64, 16), torch.randn(8, 32).bfloat16()
+    art = compile_with_dynamo(mlp, [x])
+    assert differentiable_kind(art.launches, art.dag.inputs) == "linear_chain"
+    layers = linear_chain_layers(art.launches, art.dag.inputs)
+    assert [has_bias for _, has_bias in layers] == [True, True] and layers[0][0].params.activation == 1
+    art2 = compile_with_dynamo(lambda a, b, c: a * b + c, [torch.randn(4, 4)] * 3)
+    assert differentiable_kind(art2.launches, art2.dag.inputs) == ""
+
+
 def test_broadcast_classification():
     assert classify_broadcast((4, 8), (4, 8)) == IN_FULL
     assert classify_broadcast((8,), (4, 8)) == IN_ROW
