@@ -193,6 +193,9 @@ __device__ __forceinline__ void store_scalar_f(void* base, int dt, int64_t i, fl
     case CDR_F32: static_cast<float*>(base)[i] = v; break;
     case CDR_BF16: static_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v); break;
     case CDR_F16: static_cast<__half*>(base)[i] = __float2half_rn(v); break;
+    case CDR_BOOL: static_cast<uint8_t*>(base)[i] = v != 0.0f; break;
+    case CDR_I32: static_cast<int32_t*>(base)[i] = static_cast<int32_t>(v); break;
+    case CDR_I64: static_cast<int64_t*>(base)[i] = static_cast<int64_t>(v); break;
     default: break;
   }
 }
@@ -492,7 +495,8 @@ int launch_elementwise(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
       const bool ok = op == CDR_OP_ADD || op == CDR_OP_SUB || op == CDR_OP_MUL || op == CDR_OP_RELU ||
                       op == CDR_OP_NEG || op == CDR_OP_ABS || op == CDR_OP_MAX || op == CDR_OP_MIN ||
                       op == CDR_OP_ADDCMUL || op == CDR_OP_CONST || op == CDR_OP_COPY ||
-                      op == CDR_OP_ADD_IMM || op == CDR_OP_MUL_IMM || op == CDR_OP_RSUB_IMM;
+                      op == CDR_OP_ADD_IMM || op == CDR_OP_MUL_IMM || op == CDR_OP_RSUB_IMM ||
+                      (op >= CDR_OP_GT && op <= CDR_OP_WHERE);
       if (!ok) { set_error("elementwise: op %d has no integer form", op); return CDR_ERR_UNSUPPORTED; }
     }
     int64_t grid = (n + kThreads - 1) / kThreads;
@@ -501,7 +505,16 @@ int launch_elementwise(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
     CDR_CUDA_TRY(cudaGetLastError());
     return CDR_OK;
   }
-  if (!all_float) { set_error("elementwise: mixed integer/float clusters are not supported"); return CDR_ERR_UNSUPPORTED; }
+  if (!all_float) {
+    // Mixed clusters (a bool mask selecting between float tensors, a comparison whose result leaves
+    // the cluster as bool, an integer tensor scaling a float one): the scalar interpreter, which
+    // converts every input to fp32 registers and every output from them.
+    int64_t grid = (n + kThreads - 1) / kThreads;
+    if (grid > scalar_cap) grid = scalar_cap;
+    ew_interp_scalar_f_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(a);
+    CDR_CUDA_TRY(cudaGetLastError());
+    return CDR_OK;
+  }
 
   // Vector path needs: one dtype for all inputs, one for all outputs, 16-byte aligned
   // pointers, and row-broadcast inputs whose row length is a multiple of the unit.

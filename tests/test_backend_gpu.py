@@ -199,6 +199,26 @@ def test_comparison_select_and_activation_coverage():
         compiled(lambda a: F.gelu(a, approximate="tanh"))(x.to(DEV))
 
 
+def test_mixed_dtype_clusters():
+    """A bool mask input, a comparison that leaves the graph as bool, an integer tensor scaling a
+    float one: exact against eager."""
+    gen = torch.Generator().manual_seed(53)
+    a, b = torch.randn(33, 70, generator=gen), torch.randn(33, 70, generator=gen)
+    m = torch.rand(33, 70, generator=gen) > 0.5
+    i = torch.randint(-5, 6, (33, 70), generator=gen)
+    cases = {
+        "where_mask": (lambda m_, a_, b_: torch.where(m_, a_, b_ * 2.0), [m, a, b]),
+        "compare_out": (lambda a_, b_: a_ > b_, [a, b]),
+        "int_times_float": (lambda i_, a_: i_ * a_ + 1.0, [i, a]),
+        "int_compare": (lambda i_: torch.where(i_ > 0, i_, -i_), [i]),
+    }
+    for name, (fn, inputs) in cases.items():
+        want = rp.run_reference(fn, inputs)
+        got = compiled(fn)(*[t.to(DEV) for t in inputs]).cpu()
+        assert got.dtype == want.dtype and got.shape == want.shape, name
+        assert torch.equal(got, want), name
+
+
 def test_mlp_is_differentiable_through_the_backend():
     """loss.backward() through a gcu-compiled Linear -> ReLU -> Linear: every gradient is a launch of
     the GEMM template with transposed-operand layouts (plus one elementwise launch for the ReLU mask)."""
