@@ -19,6 +19,7 @@ namespace cdr {
 
 std::string jit_elementwise_source(const cdr_ew_params& p, const int* in_dt, const int* out_dt, int E);
 std::string jit_row_reduce_source(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E, int64_t cols);
+std::string jit_full_reduce_source(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E);
 std::vector<char> jit_compile(const std::string& src, std::string* log);
 int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out);
 
@@ -173,13 +174,13 @@ int cdr_device_status(int* status_out, int clear) {
 int cdr_template_source(int template_id, const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs, int n_outputs,
                         const void* params, size_t params_bytes, char* buffer, size_t buffer_bytes, int compile) {
   g_error[0] = 0;
-  if (template_id != CDR_T_ELEMENTWISE && template_id != CDR_T_ROW_REDUCE) {
+  if (template_id != CDR_T_ELEMENTWISE && template_id != CDR_T_ROW_REDUCE && template_id != CDR_T_FULL_REDUCE) {
     set_error("template %d has no run-time instances", template_id);
     return CDR_ERR_UNSUPPORTED;
   }
   if (int rc = check_lists(inputs, n_inputs, outputs, n_outputs)) return rc;
   if (int rc = check_params(template_id, params, params_bytes)) return rc;
-  const bool reduce = template_id == CDR_T_ROW_REDUCE;
+  const bool reduce = template_id != CDR_T_ELEMENTWISE;
   const cdr_ew_params* p = reduce ? &static_cast<const cdr_reduce_params*>(params)->chain : static_cast<const cdr_ew_params*>(params);
   if (int rc = validate_ew_program(p, n_inputs, n_outputs)) return rc;
   if (reduce && (n_outputs != 1 || n_inputs < 1)) { set_error("row_reduce: needs >=1 input and exactly one output"); return CDR_ERR_BAD_ARG; }
@@ -198,7 +199,9 @@ int cdr_template_source(int template_id, const cdr_tensor* inputs, int n_inputs,
       int64_t cols = 0;
       for (int i = 0; i < n_inputs; ++i)
         if (p->input_mode[i] == CDR_IN_FULL && inputs[i].rank >= 1) { cols = inputs[i].shape[inputs[i].rank - 1]; break; }
-      src = jit_row_reduce_source(*p, in_dt, out_dt[0], static_cast<const cdr_reduce_params*>(params)->reduce_op, any16 ? 8 : 4, cols);
+      const int rop = static_cast<const cdr_reduce_params*>(params)->reduce_op;
+      src = template_id == CDR_T_FULL_REDUCE ? jit_full_reduce_source(*p, in_dt, out_dt[0], rop, any16 ? 8 : 4)
+                                             : jit_row_reduce_source(*p, in_dt, out_dt[0], rop, any16 ? 8 : 4, cols);
     } else {
       src = jit_elementwise_source(*p, in_dt, out_dt, any16 ? 8 : 4);
     }

@@ -451,6 +451,75 @@ std::string generate_row_reduce_packed(const cdr_ew_params& p, int out_dt, int r
   return s;
 }
 
+
+// Chain + reduction over every element, one launch: a persistent grid walks units of E elements
+// (U per thread in flight), every CTA leaves one partial in scratch, and the CTA that draws the
+// last ticket folds the partials and writes the result.  Args: n_units = elements / E, out[0] =
+// result, out[1] = float partials (one per CTA), out[2] = ticket counter (zero at launch, left zero).
+std::string generate_full_reduce(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E, int U) {
+  const bool packed = E == 8 && can_pack(p, in_dt);
+  std::string s = kPrelude;
+  const int nin = p.n_inputs;
+  s += packed ? chain_source_packed(p) : chain_source(p);
+  const char* ident = reduce_op == CDR_RED_MAX ? "__uint_as_float(0xff800000u)" : reduce_op == CDR_RED_MIN ? "__uint_as_float(0x7f800000u)" : "0.0f";
+  const char* comb = reduce_op == CDR_RED_MAX ? "max_f" : reduce_op == CDR_RED_MIN ? "min_f" : "__fadd_rn";
+  s += std::string("__device__ __forceinline__ float comb(float x, float y) { return ") + comb + "(x, y); }\n";
+  s += "__device__ __forceinline__ float cta_comb(float v, float* part) {\n";
+  s += "#pragma unroll\n  for (int o = 16; o > 0; o >>= 1) v = comb(v, __shfl_xor_sync(0xffffffffu, v, o));\n";
+  s += "  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;\n  __syncthreads();\n";
+  s += "  if (threadIdx.x == 0) {\n    v = part[0];\n#pragma unroll\n    for (int w = 1; w < 8; ++w) v = comb(v, part[w]);\n  }\n";
+  s += "  __syncthreads();\n  return v;\n}\n";
+  s += "extern \"C\" __global__ void __launch_bounds__(256) cdr_jit_k(const __grid_constant__ Args a) {\n";
+  s += "  constexpr int U = " + std::to_string(U) + ", E = " + std::to_string(E) + ";\n";
+  s += "  __shared__ float part[8];\n  __shared__ int is_last;\n";
+  s += "  const i64 stride = (i64)gridDim.x * 256;\n";
+  s += std::string("  float acc0 = ") + ident + ", acc1 = " + ident + ";\n";
+  s += "  for (i64 base = (i64)blockIdx.x * 256 + threadIdx.x; base < a.n_units; base += stride * U) {\n";
+  if (packed) s += "    U4 v[U][" + std::to_string(nin) + "];\n";
+  else s += "    float v[U][" + std::to_string(nin) + "][E];\n";
+  s += "#pragma unroll\n    for (int u = 0; u < U; ++u) {\n      const i64 unit = base + u * stride;\n      if (unit < a.n_units) {\n        const i64 e0 = unit * E;\n";
+  for (int i = 0; i < nin; ++i) {
+    const int m = p.input_mode[i];
+    const std::string I = std::to_string(i);
+    if (packed) {
+      s += packed_load(i, m, "e0", "(e0 % a.cols)", "(e0 / a.cols)", "v[u][" + I + "]", "        ");
+    } else if (m == CDR_IN_FULL || m == CDR_IN_ROW) {
+      s += vector_loads(i, in_dt[i], m, E, "e0", "(e0 % a.cols)", "v[u][" + I + "]", "        ");
+    } else {
+      const std::string idx = m == CDR_IN_COL ? "(e0 / a.cols)" : "0";
+      s += "        { const float t = " + std::string(dt_scalar(in_dt[i])) + "(((const " + dt_c(in_dt[i]) + "*)a.in[" + I + "])[" + idx +
+           "]);\n#pragma unroll\n          for (int e = 0; e < E; ++e) v[u][" + I + "][e] = t; }\n";
+    }
+  }
+  s += "      }\n    }\n";
+  s += "#pragma unroll\n    for (int u = 0; u < U; ++u) {\n      if (base + u * stride < a.n_units) {\n";
+  if (packed) {
+    const char* comp[4] = {"x", "y", "z", "w"};
+    for (int e = 0; e < 4; ++e) {
+      s += "        {\n          u32 in[" + std::to_string(nin) + "], out[1];\n";
+      for (int i = 0; i < nin; ++i) s += "          in[" + std::to_string(i) + "] = v[u][" + std::to_string(i) + "]." + comp[e] + ";\n";
+      s += "          chain(in, out);\n          acc0 = comb(acc0, __uint_as_float(out[0] << 16));\n          acc1 = comb(acc1, __uint_as_float(out[0] & 0xffff0000u));\n        }\n";
+    }
+  } else {
+    s += "#pragma unroll\n        for (int e = 0; e < E; ++e) {\n          float in[" + std::to_string(nin) + "], out[1];\n";
+    for (int i = 0; i < nin; ++i) s += "          in[" + std::to_string(i) + "] = v[u][" + std::to_string(i) + "][e];\n";
+    s += "          chain(in, out);\n          if (e & 1) acc1 = comb(acc1, out[0]); else acc0 = comb(acc0, out[0]);\n        }\n";
+  }
+  s += "      }\n    }\n  }\n";
+  s += "  float r = cta_comb(comb(acc0, acc1), part);\n";
+  s += "  float* partials = (float*)a.out[1];\n  unsigned int* ticket = (unsigned int*)a.out[2];\n";
+  s += "  if (threadIdx.x == 0) {\n    partials[blockIdx.x] = r;\n    __threadfence();\n    is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;\n  }\n";
+  s += "  __syncthreads();\n  if (!is_last) return;\n  __threadfence();\n";
+  s += std::string("  float acc = ") + ident + ";\n";
+  s += "  for (int i = threadIdx.x; i < (int)gridDim.x; i += 256) acc = comb(acc, __ldcg(partials + i));\n";
+  s += "  r = cta_comb(acc, part);\n  if (threadIdx.x == 0) {\n";
+  if (reduce_op == CDR_RED_MEAN) s += "    r = __fdiv_rn(r, (float)(a.n_units * E));\n";
+  if (out_dt == CDR_F32) s += "    ((float*)a.out[0])[0] = r;\n";
+  else s += std::string("    ((u16*)a.out[0])[0] = (u16)") + (out_dt == CDR_BF16 ? "f2bf" : "f2h") + "(r);\n";
+  s += "    *ticket = 0;\n  }\n}\n";
+  return s;
+}
+
 struct JitKernel {
   CUfunction fn = nullptr;
   bool failed = false;
@@ -482,6 +551,10 @@ void reduce_config(const cdr_ew_params& p, const int* in_dt, int E, int64_t cols
   *G = cols / E >= 256 * *U ? 256 : 32;
 }
 }  // namespace
+
+std::string jit_full_reduce_source(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E) {
+  return generate_full_reduce(p, in_dt, out_dt, reduce_op, E, E == 4 ? 4 : 2);
+}
 
 std::string jit_row_reduce_source(const cdr_ew_params& p, const int* in_dt, int out_dt, int reduce_op, int E, int64_t cols) {
   int U, G;
@@ -585,6 +658,24 @@ int launch_row_reduce_jit(const void* const* in, void* out, const int* in_dt, in
   args.cols = cols;
   const int64_t rpb = 256 / G;
   return launch_jit(A, fn, args, (rows + rpb - 1) / rpb, stream, "row_reduce");
+}
+
+// Chain + reduction over every element; n must be a whole number of units of E elements.
+int launch_full_reduce_jit(const void* const* in, void* out, float* partials, unsigned int* ticket, const int* in_dt,
+                           int out_dt, const cdr_ew_params& p, int reduce_op, int64_t n_units, int64_t cols, int E,
+                           int grid, cudaStream_t stream) {
+  const Api& A = api();
+  if (!A.ok) return CDR_ERR_UNSUPPORTED;
+  CUfunction fn = nullptr;
+  if (int rc = get_kernel(A, generate_full_reduce(p, in_dt, out_dt, reduce_op, E, E == 4 ? 4 : 2), &fn)) return rc;
+  JitArgs args{};
+  for (int i = 0; i < p.n_inputs; ++i) args.in[i] = in[i];
+  args.out[0] = out;
+  args.out[1] = partials;
+  args.out[2] = ticket;
+  args.n_units = n_units;
+  args.cols = cols;
+  return launch_jit(A, fn, args, grid, stream, "full_reduce");
 }
 
 }  // namespace cdr

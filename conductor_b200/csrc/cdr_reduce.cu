@@ -24,6 +24,9 @@
 namespace cdr {
 
 int validate_ew_program(const cdr_ew_params* p, int n_in, int n_out);
+int launch_full_reduce_jit(const void* const* in, void* out, float* partials, unsigned int* ticket, const int* in_dt,
+                           int out_dt, const cdr_ew_params& p, int reduce_op, int64_t n_units, int64_t cols, int E,
+                           int grid, cudaStream_t stream);
 int launch_row_reduce_jit(const void* const* in, void* out, const int* in_dt, int out_dt, const cdr_ew_params& p,
                           int reduce_op, int64_t rows, int64_t cols, int E, cudaStream_t stream);
 int64_t expected_input_numel(int mode, int64_t n, int64_t cols);
@@ -587,6 +590,24 @@ int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
   int64_t grid = (n + 255) / 256;
   if (grid > full_reduce_grid()) grid = full_reduce_grid();
   CDR_CUDA_TRY(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned int), stream));
+  // vector-shaped problems get a run-time instance of the streaming skeleton
+  {
+    bool any16 = false, ok = true;
+    for (int i = 0; i < n_in; ++i) any16 |= dtype_size(ins[i].dtype) == 2;
+    const int E = any16 ? 8 : 4;
+    for (int i = 0; i < n_in; ++i) {
+      const int m = p->chain.input_mode[i];
+      if (m == CDR_IN_FULL || m == CDR_IN_ROW) ok &= aligned16(ins[i].data);
+      if (m == CDR_IN_ROW || m == CDR_IN_COL) ok &= cols % E == 0;
+    }
+    if (ok && n % E == 0) {
+      int64_t jgrid = (n / E + 255) / 256;
+      if (jgrid > full_reduce_grid()) jgrid = full_reduce_grid();
+      const int rc = launch_full_reduce_jit(a.g.in, a.g.out, a.partials, a.ticket, a.g.in_dtype, a.g.out_dtype, p->chain,
+                                            p->reduce_op, n / E, cols, E, static_cast<int>(jgrid), stream);
+      if (rc != CDR_ERR_UNSUPPORTED) return rc;
+    }
+  }
   full_reduce_kernel<256><<<static_cast<unsigned>(grid), 256, 0, stream>>>(a);
   CDR_CUDA_TRY(cudaGetLastError());
   return CDR_OK;

@@ -231,7 +231,8 @@ CDR_API int cdr_device_status(int* status_out, int clear);
  * written NUL-terminated into `buffer` (truncated to buffer_bytes).  With `compile` != 0 the source
  * is also compiled for sm_100a with NVRTC -- no GPU needed -- and CDR_ERR_UNSUPPORTED is returned
  * with the compiler log in cdr_last_error() if that fails.  Only dtypes, the last dimension and the
- * program are read from the descriptors.  template_id is CDR_T_ELEMENTWISE or CDR_T_ROW_REDUCE.
+ * program are read from the descriptors.  template_id is CDR_T_ELEMENTWISE, CDR_T_ROW_REDUCE or
+ * CDR_T_FULL_REDUCE.
  * Replaces the generated-DSL dump of the reference
  * (conductor/codegen/dslgen.py:154-177 generate_dsl_file, conductor/utils/artifacts.py:18-237). */
 CDR_API int cdr_template_source(int template_id, const cdr_tensor* inputs, int n_inputs, const cdr_tensor* outputs,

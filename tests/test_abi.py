@@ -117,6 +117,11 @@ def test_generated_elementwise_source_compiles_without_a_gpu(built_library):
                                          ctypes.cast(ctypes.byref(rp), ctypes.c_void_p), ctypes.sizeof(rp), buf, len(buf), 1)
             assert rc == 0 or b"not available" in lib.cdr_last_error(), lib.cdr_last_error()
             assert ("G = 256" if cols == 4096 else "G = 32") in buf.value.decode()
+            # the same chain reduced over every element: persistent grid + ticket fold
+            rc = lib.cdr_template_source(7, make_descriptors([xr, wr]), 2, make_descriptors([torch.zeros(1)]), 1,
+                                         ctypes.cast(ctypes.byref(rp), ctypes.c_void_p), ctypes.sizeof(rp), buf, len(buf), 1)
+            assert rc == 0 or b"not available" in lib.cdr_last_error(), lib.cdr_last_error()
+            assert "atomicAdd(ticket" in buf.value.decode()
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
