@@ -191,7 +191,8 @@ int cdr_template_source(int template_id, const cdr_tensor* inputs, int n_inputs,
   for (int o = 0; o < n_outputs; ++o) { out_dt[o] = outputs[o].dtype; if (!reduce) any16 |= dtype_size(out_dt[o]) == 2; }
   for (int i = 0; i < n_inputs + n_outputs; ++i) {
     const int dt = i < n_inputs ? in_dt[i] : out_dt[i - n_inputs];
-    if (dt != CDR_F32 && dt != CDR_BF16 && dt != CDR_F16) { set_error("only floating-point programs are instantiated at run time"); return CDR_ERR_UNSUPPORTED; }
+    const bool flag_ok = dt == CDR_BOOL && !reduce;   // bool masks and bool results: elementwise only
+    if (dt != CDR_F32 && dt != CDR_BF16 && dt != CDR_F16 && !flag_ok) { set_error("only floating-point programs (with bool operands in elementwise ones) are instantiated at run time"); return CDR_ERR_UNSUPPORTED; }
   }
   std::string src;
   try {

@@ -507,12 +507,34 @@ int launch_elementwise(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
   }
   if (!all_float) {
     // Mixed clusters (a bool mask selecting between float tensors, a comparison whose result leaves
-    // the cluster as bool, an integer tensor scaling a float one): the scalar interpreter, which
-    // converts every input to fp32 registers and every output from them.
-    int64_t grid = (n + kThreads - 1) / kThreads;
-    if (grid > scalar_cap) grid = scalar_cap;
-    ew_interp_scalar_f_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(a);
-    CDR_CUDA_TRY(cudaGetLastError());
+    // the cluster as bool, an integer tensor scaling a float one).  With only float and bool
+    // operands the run-time instance handles them (flags travel as bytes, registers are fp32);
+    // anything else, and the tail, goes through the scalar interpreter, which converts every
+    // input to fp32 registers and every output from them.
+    int64_t done = 0;
+    bool flags_only = true, any16 = false;
+    for (int i = 0; i < n_in; ++i) { flags_only &= is_float_dtype(ins[i].dtype) || ins[i].dtype == CDR_BOOL; any16 |= dtype_size(ins[i].dtype) == 2; }
+    for (int o = 0; o < n_out; ++o) { flags_only &= is_float_dtype(outs[o].dtype) || outs[o].dtype == CDR_BOOL; any16 |= dtype_size(outs[o].dtype) == 2; }
+    const int EJ = any16 ? 8 : 4;
+    bool jit_ok = flags_only && n >= EJ;
+    for (int o = 0; o < n_out; ++o) jit_ok &= aligned16(outs[o].data);
+    for (int i = 0; i < n_in; ++i) {
+      const int m = p->input_mode[i];
+      if (m == CDR_IN_FULL || m == CDR_IN_ROW) jit_ok &= aligned16(ins[i].data);
+      if (m == CDR_IN_ROW || m == CDR_IN_COL) jit_ok &= (cols % EJ == 0);
+    }
+    if (jit_ok) {
+      const int rc = launch_elementwise_jit(a.in, a.out, a.in_dtype, a.out_dtype, *p, n / EJ, cols, EJ, stream);
+      if (rc == CDR_OK) done = (n / EJ) * EJ;
+      else if (rc != CDR_ERR_UNSUPPORTED) return rc;
+    }
+    if (done < n) {
+      a.first = done;
+      int64_t grid = (n - done + kThreads - 1) / kThreads;
+      if (grid > scalar_cap) grid = scalar_cap;
+      ew_interp_scalar_f_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(a);
+      CDR_CUDA_TRY(cudaGetLastError());
+    }
     return CDR_OK;
   }
 

@@ -99,6 +99,10 @@ __device__ __forceinline__ void un_bf16(U4 q, float* f) { u32 w[4] = {q.x, q.y, 
 __device__ __forceinline__ void un_f16(U4 q, float* f) { u32 w[4] = {q.x, q.y, q.z, q.w}; for (int i = 0; i < 4; ++i) { f[2*i] = h2f(w[i] & 0xffffu); f[2*i+1] = h2f(w[i] >> 16); } }
 __device__ __forceinline__ U4 pk_f32(const float* f) { U4 q; q.x = __float_as_uint(f[0]); q.y = __float_as_uint(f[1]); q.z = __float_as_uint(f[2]); q.w = __float_as_uint(f[3]); return q; }
 __device__ __forceinline__ U4 pk_bf16(const float* f) { u32 w[4]; for (int i = 0; i < 4; ++i) w[i] = f2bf(f[2*i]) | (f2bf(f[2*i+1]) << 16); U4 q; q.x = w[0]; q.y = w[1]; q.z = w[2]; q.w = w[3]; return q; }
+__device__ __forceinline__ u32 ld_cs32(const void* p) { u32 v; asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(p)); return v; }
+__device__ __forceinline__ void st_cs32(void* p, u32 v) { asm volatile("st.global.cs.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void un_bool4(u32 w, float* f) { for (int i = 0; i < 4; ++i) f[i] = ((w >> (8 * i)) & 0xffu) ? 1.0f : 0.0f; }
+__device__ __forceinline__ u32 pk_bool4(const float* f) { u32 w = 0; for (int i = 0; i < 4; ++i) w |= (f[i] != 0.0f ? 1u : 0u) << (8 * i); return w; }
 __device__ __forceinline__ u32 badd(u32 a, u32 b) { u32 d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ u32 bsub(u32 a, u32 b) { u32 d; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ u32 bmul(u32 a, u32 b) { u32 d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
@@ -109,10 +113,10 @@ __device__ __forceinline__ u32 babs(u32 a) { u32 d; asm("abs.bf16x2 %0, %1;" : "
 __device__ __forceinline__ U4 pk_f16(const float* f) { u32 w[4]; for (int i = 0; i < 4; ++i) w[i] = f2h(f[2*i]) | (f2h(f[2*i+1]) << 16); U4 q; q.x = w[0]; q.y = w[1]; q.z = w[2]; q.w = w[3]; return q; }
 )SRC";
 
-const char* dt_c(int dt) { return dt == CDR_F32 ? "float" : "u16"; }
+const char* dt_c(int dt) { return dt == CDR_F32 ? "float" : dt == CDR_BOOL ? "unsigned char" : "u16"; }
 const char* dt_un(int dt) { return dt == CDR_F32 ? "un_f32" : dt == CDR_BF16 ? "un_bf16" : "un_f16"; }
 const char* dt_pk(int dt) { return dt == CDR_F32 ? "pk_f32" : dt == CDR_BF16 ? "pk_bf16" : "pk_f16"; }
-const char* dt_scalar(int dt) { return dt == CDR_F32 ? "" : dt == CDR_BF16 ? "bf2f" : "h2f"; }
+const char* dt_scalar(int dt) { return dt == CDR_F32 ? "" : dt == CDR_BF16 ? "bf2f" : dt == CDR_BOOL ? "(float)" : "h2f"; }
 int dt_vec(int dt) { return dt == CDR_F32 ? 4 : 8; }
 
 std::string fimm(float v) {
@@ -188,6 +192,12 @@ std::string vector_loads(int i, int dt, int mode, int E, const std::string& full
   const std::string base = mode == CDR_IN_FULL ? full_base : row_base;
   const std::string ld = mode == CDR_IN_FULL ? "ld_cs" : "ld_nc";
   std::string s;
+  if (dt == CDR_BOOL) {   // one byte per element: 32-bit loads of four flags
+    for (int k = 0; k < E / 4; ++k)
+      s += indent + "un_bool4(ld_cs32((const unsigned char*)a.in[" + I + "] + " + base + " + " + std::to_string(k * 4) + "), " + dst +
+           " + " + std::to_string(k * 4) + ");\n";
+    return s;
+  }
   for (int k = 0; k < E / V; ++k)
     s += indent + dt_un(dt) + "(" + ld + "((const " + T + "*)a.in[" + I + "] + " + base + " + " + std::to_string(k * V) + "), " +
          dst + " + " + std::to_string(k * V) + ");\n";
@@ -330,6 +340,12 @@ std::string generate(const cdr_ew_params& p, const int* in_dt, const int* out_dt
   s += "      }\n";
   for (int o = 0; o < p.n_outputs; ++o) {
     const int dt = out_dt[o], V = dt_vec(dt);
+    if (dt == CDR_BOOL) {
+      for (int k = 0; k < E / 4; ++k)
+        s += "      st_cs32((unsigned char*)a.out[" + std::to_string(o) + "] + e0 + " + std::to_string(k * 4) + ", pk_bool4(o[" +
+             std::to_string(o) + "] + " + std::to_string(k * 4) + "));\n";
+      continue;
+    }
     for (int k = 0; k < E / V; ++k)
       s += "      st_cs((" + std::string(dt_c(dt)) + "*)a.out[" + std::to_string(o) + "] + e0 + " + std::to_string(k * V) + ", " +
            dt_pk(dt) + "(o[" + std::to_string(o) + "] + " + std::to_string(k * V) + "));\n";
