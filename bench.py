@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the compiled-graph hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c2g|c3|c3b|c4|c5] [--impl reference]
 
 One step = one pass of a `torch.compile(fn, backend='gcu')` graph over one batch of seeded
 synthetic input.  Default workload: c2, `mean(relu(x*w + b), dim=-1)` with x bf16 [16384, 4096]
@@ -58,6 +58,12 @@ class Workload:
         elif key == "c2":
             self.name = "c2 mean(relu(x*w+b),-1) x bf16 [16384,4096], w,b bf16 [4096] -> fp32 [16384]"
             self.fn, self.dtype, self.samples = rp.reduce_mean_fusion, "bf16", 16384
+            self.make = lambda seed: rp.inputs_reduce_mean(seed=seed)
+            self.batch_inputs = [0]
+            self.bytes, self.flops, self.bound = 16384 * 4096 * 2 + 2 * 4096 * 2 + 16384 * 4, None, "hbm"
+        elif key == "c2g":
+            self.name = "c2g mean(relu(x*w-b),-1) bf16 [16384,4096]: config 2's traffic through a run-time kernel instance"
+            self.fn, self.dtype, self.samples = rp.reduce_mean_variant, "bf16", 16384
             self.make = lambda seed: rp.inputs_reduce_mean(seed=seed)
             self.batch_inputs = [0]
             self.bytes, self.flops, self.bound = 16384 * 4096 * 2 + 2 * 4096 * 2 + 16384 * 4, None, "hbm"
@@ -386,7 +392,7 @@ def gpu_arm(args, wl: Workload):
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_steps = 20 if wl.key in ("c1", "c2", "c4", "c5") else 8
+        cpu_steps = 20 if wl.key in ("c1", "c2", "c2g", "c4", "c5") else 8
         v, ms, threads = time_reference(wl, cpu_steps, 3)
         cpu_baseline = {"value": v, "unit": "samples/s", "cores": threads, "kind": "port",
                         "sample": f"full batch, {cpu_steps} steps, {ms:.2f} ms/step"}
@@ -411,7 +417,7 @@ def gpu_arm(args, wl: Workload):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (None until a capture exists for the workload)
-TRAFFIC_BYTES: dict = {"c1": 235.0e6, "c2": 137.98e6, "c3": 2097.4e6, "c3b": 3180.9e6, "c4": 81.0e6, "c5": 552.2e6}
+TRAFFIC_BYTES: dict = {"c1": 235.0e6, "c2": 137.98e6, "c2g": 138.2e6, "c3": 2097.4e6, "c3b": 3180.9e6, "c4": 81.0e6, "c5": 552.2e6}
 
 
 def main():

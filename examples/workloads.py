@@ -20,6 +20,12 @@ def reduce_mean_fusion(x, w, b):
     return torch.mean(torch.relu(x * w + b), dim=-1, dtype=torch.float32)
 
 
+def reduce_mean_variant(x, w, b):
+    """Same traffic as config 2 with a chain that has no ahead-of-time kernel instance (x*w - b): runs
+    the run-time instance of the row-reduce skeleton."""
+    return torch.mean(torch.relu(x * w - b), dim=-1, dtype=torch.float32)
+
+
 def softmax_forward(logits):
     return torch.softmax(logits, dim=-1)
 
