@@ -21,7 +21,7 @@ from typing import Any, Optional
 
 import torch
 
-from ..optimization.buffers import Buffer
+from ..optimization.buffers import Buffer, BufferScope
 from ..optimization.fusion import FusionCluster, FusionType, _is_last_dim_reduction
 from ..utils.exceptions import UnsupportedOperationError
 from ..utils.type_mapping import is_float, is_int, to_cdr_dtype
@@ -460,7 +460,71 @@ def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
                         cluster=cluster)
 
 
+def _lower_layer_norm(cluster: FusionCluster) -> list:
+    """layer_norm over the last dimension as three launches of existing templates: row mean, row
+    variance (mean of squared deviations, two-pass) and the normalising elementwise chain with the
+    two statistics as column-broadcast inputs.  Statistics and the chain are fp32; the result is
+    rounded once to the output dtype, like eager's kernel."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    kw = node.metadata.get("kwargs", {})
+    kws = node.metadata.get("kwarg_spec", {})
+    consts = _const_args(node)
+    x = node.inputs[spec[0][1]]
+    out = node.outputs[0]
+    norm_shape = kw.get("normalized_shape", consts[0] if consts else None)
+    if norm_shape is None or len(tuple(norm_shape)) != 1 or tuple(norm_shape)[0] != x.shape[-1]:
+        raise UnsupportedOperationError("layer_norm", f"normalized_shape={norm_shape}; only the last dimension")
+    if not is_float(x.dtype):
+        raise UnsupportedOperationError("layer_norm", f"{x.dtype} input")
+
+    def operand(pos, name):
+        if name in kws and kws[name][0] == "buf":
+            return node.inputs[kws[name][1]]
+        if len(spec) > pos and spec[pos][0] == "buf":
+            return node.inputs[spec[pos][1]]
+        return None
+
+    w, b = operand(2, "weight"), operand(3, "bias")
+    eps = kw.get("eps", next((c for c in consts[1:] if isinstance(c, float)), 1e-5))
+    f32 = torch.float32
+    stat_shape = tuple(x.shape[:-1]) + (1,)
+    mean = Buffer(name=f"{out.name}_mean", scope=BufferScope.SHARED, dtype=f32, shape=stat_shape, is_temporary=True)
+    var = Buffer(name=f"{out.name}_var", scope=BufferScope.SHARED, dtype=f32, shape=stat_shape, is_temporary=True)
+    sig = cluster.signature()
+
+    p1 = CdrReduceParams()
+    p1.chain = _ProgramBuilder([x], x.shape).build([0])
+    p1.reduce_op = ReduceOp.MEAN
+    l1 = KernelLaunch(Template.ROW_REDUCE, f"{sig}:mean", [x], [mean], p1, [stat_shape], [f32], cluster=cluster)
+
+    b2 = _ProgramBuilder([x, mean], x.shape)
+    d = b2._emit(EwOp.SUB, 0, 1, dtype=f32)
+    sq = b2._emit(EwOp.MUL, d, d, dtype=f32)
+    p2 = CdrReduceParams()
+    p2.chain = b2.build([sq])
+    p2.reduce_op = ReduceOp.MEAN
+    l2 = KernelLaunch(Template.ROW_REDUCE, f"{sig}:var", [x, mean], [var], p2, [stat_shape], [f32], cluster=cluster)
+
+    ins = [x, mean, var] + [t for t in (w, b) if t is not None]
+    b3 = _ProgramBuilder(ins, x.shape)
+    d = b3._emit(EwOp.SUB, 0, 1, dtype=f32)
+    r = b3._emit(EwOp.RSQRT, b3._emit(EwOp.ADD_IMM, 2, imm=eps, dtype=f32), dtype=f32)
+    y = b3._emit(EwOp.MUL, d, r, dtype=f32 if (w is not None or b is not None) else out.dtype)
+    nxt = 3
+    if w is not None:
+        y = b3._emit(EwOp.MUL, y, nxt, dtype=f32 if b is not None else out.dtype)
+        nxt += 1
+    if b is not None:
+        y = b3._emit(EwOp.ADD, y, nxt, dtype=out.dtype)
+    l3 = KernelLaunch(Template.ELEMENTWISE, f"{sig}:normalize", ins, [out], b3.build([y]), [out.shape], [out.dtype],
+                      cluster=cluster)
+    return [l1, l2, l3]
+
+
 _LOWERING = {
+    FusionType.NORM: _lower_layer_norm,
     FusionType.ELEMENTWISE: _lower_elementwise,
     FusionType.REDUCTION: _lower_reduction,
     FusionType.SOFTMAX: _lower_softmax,
@@ -474,7 +538,9 @@ class KernelTemplateSelector:
     """Public face of this module; plays the role of ``ChoreoDslGen`` in the reference pipeline
     (``jit_compiler.py:150-163`` calls ``generate_dsl_file(dag, function_name)``)."""
 
-    def select(self, cluster: FusionCluster) -> KernelLaunch:
+    def select(self, cluster: FusionCluster):
+        """One KernelLaunch for the cluster, or a list of them when a cluster needs several
+        (layer_norm: two reductions and a chain)."""
         fn = _LOWERING.get(cluster.cluster_type)
         if fn is None:
             ops = ",".join(n.op_name for n in cluster.nodes)

@@ -33,6 +33,7 @@ class OpType(Enum):
     MATH = "math"
     SOFTMAX = "softmax"
     ATTENTION = "attention"
+    NORM = "norm"
     UNKNOWN = "unknown"
 
 
@@ -142,6 +143,7 @@ class OperatorRegistry:
                        preferred_fusion_level=FusionLevel.GLOBAL), "_softmax")
         r(OperatorInfo("_softmax_backward_data", "softmax_backward", OpType.SOFTMAX, False, 2,
                        template=Template.SOFTMAX_BWD, preferred_fusion_level=FusionLevel.GLOBAL))
+        r(OperatorInfo("layer_norm", "layer_norm", OpType.NORM, False, 3, preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("linear", "linear", OpType.MATRIX, True, 3, template=Template.GEMM_EPILOGUE,
                        preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("matmul", "matmul", OpType.MATRIX, False, 2, template=Template.GEMM_EPILOGUE,

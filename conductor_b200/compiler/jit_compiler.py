@@ -98,7 +98,10 @@ class ChoreoJITCompiler:
                 for n in c.nodes:
                     n.fusion_group = c
             ordered = schedule_clusters(clusters)
-            launches = [self.template_selector.select(c) for c in ordered]
+            launches = []
+            for c in ordered:
+                sel = self.template_selector.select(c)
+                launches.extend(sel if isinstance(sel, list) else [sel])
             name = f"kernel_{graph_hash[:8]}"
             plan_text = self.template_selector.generate_plan_text(launches, name)
         except ConductorError:

@@ -54,6 +54,7 @@ class FusionType(Enum):
     SOFTMAX = "softmax"
     GEMM_EPILOGUE = "gemm_epilogue"
     ATTENTION = "attention"
+    NORM = "norm"
     SHAPE = "shape"
     UNKNOWN = "unknown"
 
@@ -260,6 +261,7 @@ class FusionEngine:
                     OpType.ELEMENTWISE: FusionType.ELEMENTWISE, OpType.REDUCTION: FusionType.REDUCTION,
                     OpType.MATRIX: FusionType.GEMM_EPILOGUE, OpType.SOFTMAX: FusionType.SOFTMAX,
                     OpType.ATTENTION: FusionType.ATTENTION, OpType.SHAPE: FusionType.SHAPE,
+                    OpType.NORM: FusionType.NORM,
                 }.get(info.operation_type, FusionType.UNKNOWN)
             claim([n], ctype)
 

@@ -199,6 +199,27 @@ def test_comparison_select_and_activation_coverage():
         compiled(lambda a: F.gelu(a, approximate="tanh"))(x.to(DEV))
 
 
+def test_layer_norm_as_three_template_launches():
+    """layer_norm over the last dimension lowers to row mean, row variance and a normalising chain."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(54)
+    x = torch.randn(6, 50, 256, generator=gen) * 3 + 1
+    w, b = torch.randn(256, generator=gen), torch.randn(256, generator=gen)
+    cases = {
+        "affine": (lambda x_, w_, b_: F.layer_norm(x_, (256,), w_, b_, 1e-5), [x, w, b], 1e-5),
+        "plain": (lambda x_: F.layer_norm(x_, (256,)), [x], 1e-5),
+        "bf16": (lambda x_, w_, b_: F.layer_norm(x_, (256,), w_, b_), [x.bfloat16(), w.bfloat16(), b.bfloat16()], 2e-2),
+        "ragged": (lambda x_: F.layer_norm(x_, (250,), eps=1e-3) + 1.0, [x[..., :250].contiguous()], 1e-5),
+    }
+    for name, (fn, inputs, tol) in cases.items():
+        want = rp.run_reference(fn, inputs)
+        got = compiled(fn)(*[t.to(DEV) for t in inputs])
+        assert got.dtype == want.dtype
+        assert_close(got.float(), want.float(), tol * 4 if tol < 1e-4 else tol, name)
+    with pytest.raises(Exception):
+        compiled(lambda x_: F.layer_norm(x_, (50, 256)))(x.to(DEV))
+
+
 def test_mixed_dtype_clusters():
     """A bool mask input, a comparison that leaves the graph as bool, an integer tensor scaling a
     float one: exact against eager."""

@@ -178,6 +178,16 @@ def test_matmul_lowers_to_the_gemm_template_with_the_weight_in_place():
     assert_unsupported(lambda a, b: a @ b, [torch.randn(2, 8, 16), torch.randn(2, 16, 8)])     # batched right operand
 
 
+def test_layer_norm_lowers_to_two_reductions_and_a_chain():
+    F = torch.nn.functional
+    art = compile_with_dynamo(lambda x, w, b: F.layer_norm(x, (32,), w, b), [torch.randn(4, 32), torch.randn(32), torch.randn(32)])
+    ks = kernels(art)
+    assert [k.template for k in ks] == [Template.ROW_REDUCE, Template.ROW_REDUCE, Template.ELEMENTWISE]
+    assert ks[0].out_shapes == [(4, 1)] and ks[1].params.reduce_op == ReduceOp.MEAN
+    assert list(ks[2].params.input_mode[:5]) == [IN_FULL, IN_COL, IN_COL, IN_ROW, IN_ROW]
+    assert_unsupported(lambda x: F.layer_norm(x, (4, 32)), [torch.randn(4, 32)])
+
+
 def test_linear_chain_is_recognised_for_autograd():
     from conductor_b200.compiler.autograd import differentiable_kind, linear_chain_layers
 
