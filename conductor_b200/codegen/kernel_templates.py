@@ -61,6 +61,11 @@ class CdrGemmParams(ctypes.Structure):
                 ("x_layout", ctypes.c_int32)]
 
 
+class CdrNormParams(ctypes.Structure):
+    _fields_ = [("eps", ctypes.c_float), ("has_weight", ctypes.c_int32), ("has_bias", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
+
 class CdrAttnParams(ctypes.Structure):
     _fields_ = [("scale", ctypes.c_float), ("causal", ctypes.c_int32)]
 
@@ -85,7 +90,7 @@ class KernelLaunch:
         ins = ", ".join(b.name for b in self.inputs)
         outs = ", ".join(f"{b.name}:{b.scope.value}" for b in self.outputs)
         tname = {0: "alias", 1: "elementwise", 2: "row_reduce", 3: "softmax_fwd", 4: "softmax_bwd",
-                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce"}[self.template]
+                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce", 8: "layer_norm"}[self.template]
         return f"{outs} = {tname}<{self.name}>({ins})"
 
 
@@ -461,10 +466,11 @@ def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
 
 
 def _lower_layer_norm(cluster: FusionCluster) -> list:
-    """layer_norm over the last dimension as three launches of existing templates: row mean, row
-    variance (mean of squared deviations, two-pass) and the normalising elementwise chain with the
-    two statistics as column-broadcast inputs.  Statistics and the chain are fp32; the result is
-    rounded once to the output dtype, like eager's kernel."""
+    """layer_norm over the last dimension: the fused one-pass template when a row is a whole number
+    of 16-byte vectors, fits in registers and everything has one dtype; otherwise three launches of
+    existing templates: row mean, row variance (mean of squared deviations, two-pass) and the
+    normalising elementwise chain with the two statistics as column-broadcast inputs.  Statistics
+    are fp32 either way; the result is rounded once to the output dtype, like eager's kernel."""
     _require_shapes(cluster)
     node = cluster.nodes[0]
     spec = node.metadata.get("arg_spec", [])
@@ -488,6 +494,14 @@ def _lower_layer_norm(cluster: FusionCluster) -> list:
 
     w, b = operand(2, "weight"), operand(3, "bias")
     eps = kw.get("eps", next((c for c in consts[1:] if isinstance(c, float)), 1e-5))
+    # rows that are whole 16-byte vectors and fit in registers, one dtype throughout: the fused kernel
+    cols = x.shape[-1]
+    per_vec = 16 // (4 if x.dtype == torch.float32 else 2)
+    if (cols % per_vec == 0 and cols <= 16384 and out.dtype == x.dtype
+            and all(t is None or (t.dtype == x.dtype and tuple(t.shape) == (cols,)) for t in (w, b))):
+        p = CdrNormParams(float(eps), 1 if w is not None else 0, 1 if b is not None else 0, 0)
+        return [KernelLaunch(Template.LAYER_NORM, cluster.signature(), [x] + [t for t in (w, b) if t is not None], [out], p,
+                             [out.shape], [out.dtype], cluster=cluster)]
     f32 = torch.float32
     stat_shape = tuple(x.shape[:-1]) + (1,)
     mean = Buffer(name=f"{out.name}_mean", scope=BufferScope.SHARED, dtype=f32, shape=stat_shape, is_temporary=True)

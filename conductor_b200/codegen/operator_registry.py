@@ -51,7 +51,7 @@ class ReduceOp:
 class Template:
     """cdr_template ids."""
 
-    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE = range(1, 8)
+    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE, LAYER_NORM = range(1, 9)
 
 
 @dataclass(frozen=True)

@@ -27,6 +27,7 @@ SOURCES = {
     "cdr_jit.cu": [],
     "cdr_reduce.cu": ["--fmad=false"],
     "cdr_softmax.cu": ["--fmad=false"],
+    "cdr_layernorm.cu": [],
     "cdr_gemm.cu": [],
     "cdr_attention.cu": [],
 }

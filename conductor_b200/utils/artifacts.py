@@ -24,7 +24,7 @@ from .logging import get_logger
 logger = get_logger(__name__)
 
 _TEMPLATE_NAMES = {0: "alias", 1: "elementwise", 2: "row_reduce", 3: "softmax_fwd", 4: "softmax_bwd",
-                   5: "gemm_epilogue", 6: "attention", 7: "full_reduce"}
+                   5: "gemm_epilogue", 6: "attention", 7: "full_reduce", 8: "layer_norm"}
 _KINDS = ("fx", "dag", "clusters", "plan", "source")
 
 

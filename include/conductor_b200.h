@@ -90,8 +90,10 @@ enum cdr_template {
   CDR_T_SOFTMAX_BWD = 4,  /* inputs (grad_out, y): dx = y * (g - sum(g*y)), no params    */
   CDR_T_GEMM_EPILOGUE = 5,/* out = act(x @ W^T + bias) or act(x @ W + bias), params = cdr_gemm_params */
   CDR_T_ATTENTION = 6,    /* fused scaled-dot-product attention, params = cdr_attn_params*/
-  CDR_T_FULL_REDUCE = 7   /* elementwise chain + reduction over every element,
+  CDR_T_FULL_REDUCE = 7,  /* elementwise chain + reduction over every element,
                              params = cdr_reduce_params; needs workspace                 */
+  CDR_T_LAYER_NORM = 8    /* layer normalisation over the last dim, inputs (x[, weight][, bias]),
+                             params = cdr_norm_params                                    */
 };
 
 /* ---- elementwise programs -------------------------------------------------
@@ -196,6 +198,13 @@ typedef struct cdr_gemm_params {
   int32_t weight_layout; /* enum cdr_weight_layout                    */
   int32_t x_layout;      /* enum cdr_x_layout                         */
 } cdr_gemm_params;
+
+typedef struct cdr_norm_params {
+  float eps;
+  int32_t has_weight; /* 1: a [cols] scale follows x in the inputs           */
+  int32_t has_bias;   /* 1: a [cols] shift is the last input                 */
+  int32_t reserved;
+} cdr_norm_params;
 
 typedef struct cdr_attn_params {
   float scale;    /* softmax scale, e.g. 1/sqrt(head_dim) */

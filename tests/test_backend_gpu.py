@@ -199,8 +199,9 @@ def test_comparison_select_and_activation_coverage():
         compiled(lambda a: F.gelu(a, approximate="tanh"))(x.to(DEV))
 
 
-def test_layer_norm_as_three_template_launches():
-    """layer_norm over the last dimension lowers to row mean, row variance and a normalising chain."""
+def test_layer_norm_fused_and_decomposed():
+    """layer_norm over the last dimension: the fused one-pass template (affine, plain, bf16, long rows)
+    and the three-launch decomposition (ragged rows)."""
     F = torch.nn.functional
     gen = torch.Generator().manual_seed(54)
     x = torch.randn(6, 50, 256, generator=gen) * 3 + 1
@@ -210,6 +211,8 @@ def test_layer_norm_as_three_template_launches():
         "plain": (lambda x_: F.layer_norm(x_, (256,)), [x], 1e-5),
         "bf16": (lambda x_, w_, b_: F.layer_norm(x_, (256,), w_, b_), [x.bfloat16(), w.bfloat16(), b.bfloat16()], 2e-2),
         "ragged": (lambda x_: F.layer_norm(x_, (250,), eps=1e-3) + 1.0, [x[..., :250].contiguous()], 1e-5),
+        "long_rows": (lambda x_, w_: F.layer_norm(x_, (8192,), w_), [torch.randn(5, 8192, generator=gen) - 2, torch.randn(8192, generator=gen)], 1e-5),
+        "short_rows": (lambda x_, w_, b_: F.layer_norm(x_, (16,), w_, b_), [x[..., :16].contiguous(), w[:16].contiguous(), b[:16].contiguous()], 1e-5),
     }
     for name, (fn, inputs, tol) in cases.items():
         want = rp.run_reference(fn, inputs)

@@ -178,9 +178,14 @@ def test_matmul_lowers_to_the_gemm_template_with_the_weight_in_place():
     assert_unsupported(lambda a, b: a @ b, [torch.randn(2, 8, 16), torch.randn(2, 16, 8)])     # batched right operand
 
 
-def test_layer_norm_lowers_to_two_reductions_and_a_chain():
+def test_layer_norm_lowering():
     F = torch.nn.functional
     art = compile_with_dynamo(lambda x, w, b: F.layer_norm(x, (32,), w, b), [torch.randn(4, 32), torch.randn(32), torch.randn(32)])
+    (k,) = kernels(art)                     # whole vectors, one dtype: the fused template
+    assert k.template == Template.LAYER_NORM and k.params.has_weight == 1 and k.params.has_bias == 1
+    assert abs(k.params.eps - 1e-5) < 1e-12 and len(k.inputs) == 3
+    # a ragged row (30 floats) falls back to two reductions and a chain
+    art = compile_with_dynamo(lambda x, w, b: F.layer_norm(x, (30,), w, b), [torch.randn(4, 30), torch.randn(30), torch.randn(30)])
     ks = kernels(art)
     assert [k.template for k in ks] == [Template.ROW_REDUCE, Template.ROW_REDUCE, Template.ELEMENTWISE]
     assert ks[0].out_shapes == [(4, 1)] and ks[1].params.reduce_op == ReduceOp.MEAN
