@@ -459,6 +459,34 @@ def test_full_size_softmax(executor):
     assert dx.sum(-1).abs().max().item() < 1e-3               # softmax gradients sum to zero per row
 
 
+def test_layer_norm_template(executor):
+    """CDR_T_LAYER_NORM through the C ABI against a float64 evaluation: row lengths from one vector
+    to the 1024-thread variant, with and without scale / shift, bf16, and the refusals."""
+    from conductor_b200.codegen.kernel_templates import CdrNormParams
+
+    gen = torch.Generator().manual_seed(91)
+    for rows, cols in ((3, 4), (17, 96), (64, 1024), (9, 4096), (5, 16384)):
+        x = torch.randn(rows, cols, generator=gen) * 2 + 0.5
+        w, b = torch.randn(cols, generator=gen), torch.randn(cols, generator=gen)
+        xd = x.double()
+        norm = (xd - xd.mean(-1, keepdim=True)) / torch.sqrt(xd.var(-1, unbiased=False, keepdim=True) + 1e-5)
+        dx, dw, db = cuda(x, w, b)
+        out = torch.empty_like(dx)
+        abi.launch(Template.LAYER_NORM, [dx, dw, db], [out], CdrNormParams(1e-5, 1, 1, 0))
+        assert_close(out, (norm * w.double() + b.double()).float(), 4e-5, f"layer_norm {rows}x{cols}")
+        abi.launch(Template.LAYER_NORM, [dx], [out], CdrNormParams(1e-5, 0, 0, 0))
+        assert_close(out, norm.float(), 4e-5, f"layer_norm plain {rows}x{cols}")
+        abi.launch(Template.LAYER_NORM, [dx, db], [out], CdrNormParams(1e-5, 0, 1, 0))
+        assert_close(out, (norm + b.double()).float(), 4e-5, f"layer_norm shift only {rows}x{cols}")
+    xb = (torch.randn(33, 512, generator=gen) * 3).bfloat16()
+    outb = torch.empty(33, 512, dtype=torch.bfloat16, device=DEV)
+    abi.launch(Template.LAYER_NORM, [xb.to(DEV)], [outb], CdrNormParams(1e-5, 0, 0, 0))
+    assert_close(outb.float(), torch.nn.functional.layer_norm(xb.float(), (512,)), BF16_TOL, "layer_norm bf16")
+    ragged = torch.randn(4, 30, device=DEV)
+    assert abi.launch(Template.LAYER_NORM, [ragged], [torch.empty_like(ragged)], CdrNormParams(1e-5, 0, 0, 0), check=False) == -2
+    assert abi.launch(Template.LAYER_NORM, [dx, dw], [out], CdrNormParams(1e-5, 1, 1, 0), check=False) == -1   # bias missing
+
+
 # ---------------------------------------------------------------- K4 GEMM + bias + ReLU
 from conductor_b200.codegen.kernel_templates import CdrAttnParams, CdrGemmParams  # noqa: E402
 
