@@ -85,12 +85,13 @@ class KernelLaunch:
     alias_of: Optional[Buffer] = None   # SHAPE clusters: output is a view of this buffer
     cluster: Optional[FusionCluster] = None
     needs_workspace: bool = False
+    view_strides: Optional[tuple] = None  # COPY launches: element strides of the view of inputs[0] that is gathered
 
     def describe(self) -> str:
         ins = ", ".join(b.name for b in self.inputs)
         outs = ", ".join(f"{b.name}:{b.scope.value}" for b in self.outputs)
         tname = {0: "alias", 1: "elementwise", 2: "row_reduce", 3: "softmax_fwd", 4: "softmax_bwd",
-                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce", 8: "layer_norm"}[self.template]
+                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce", 8: "layer_norm", 9: "copy"}[self.template]
         return f"{outs} = {tname}<{self.name}>({ins})"
 
 
@@ -461,6 +462,25 @@ def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
     src = node.inputs[0]
     if src.shape is not None and math.prod(src.shape) != math.prod(out.shape):
         raise UnsupportedOperationError(node.op_name, "element count changes")
+    info = get_op_desc(node.op_name)
+    if info is not None and info.canonical_name == "permute":
+        # transpose / permute / t / swapaxes / movedim: replay the call on a meta tensor to get the
+        # view's strides, then gather that view into a contiguous buffer (every buffer of a plan is
+        # contiguous, so the layout change has to move data)
+        if src.shape is None:
+            raise UnsupportedOperationError(node.op_name, "unknown input shape")
+        try:
+            view = getattr(torch.empty(src.shape, dtype=src.dtype, device="meta"), node.op_name)(
+                *_const_args(node), **node.metadata.get("kwargs", {}))
+        except Exception as exc:
+            raise UnsupportedOperationError(node.op_name, f"cannot evaluate the layout change: {exc}") from exc
+        if tuple(view.shape) != tuple(out.shape):
+            raise UnsupportedOperationError(node.op_name, f"shape {tuple(view.shape)} != {tuple(out.shape)}")
+        if view.is_contiguous():
+            return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
+                                cluster=cluster)
+        return KernelLaunch(Template.COPY, cluster.signature(), [src], [out], None, [out.shape], [out.dtype],
+                            cluster=cluster, view_strides=tuple(view.stride()))
     return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
                         cluster=cluster)
 

@@ -51,7 +51,7 @@ class ReduceOp:
 class Template:
     """cdr_template ids."""
 
-    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE, LAYER_NORM = range(1, 9)
+    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE, LAYER_NORM, COPY = range(1, 10)
 
 
 @dataclass(frozen=True)
@@ -151,6 +151,9 @@ class OperatorRegistry:
         r(OperatorInfo("scaled_dot_product_attention", "attention", OpType.ATTENTION, False, 3,
                        template=Template.ATTENTION, preferred_fusion_level=FusionLevel.GLOBAL), "attention")
         # metadata-only reshapes of contiguous tensors: no kernel
+        # layout changes that move data: one launch of the strided-copy template
+        for perm_op in ("transpose", "permute", "t", "swapaxes", "movedim"):
+            r(OperatorInfo(perm_op, "permute", OpType.SHAPE, False, 1))
         for shape_op in ("view", "reshape", "flatten", "unsqueeze", "squeeze", "contiguous", "detach", "clone_view"):
             r(OperatorInfo(shape_op, shape_op, OpType.SHAPE, False, 1, requires_device_kernel=False))
 

@@ -15,6 +15,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from ..codegen.operator_registry import Template
 from ..codegen.kernel_templates import CdrTensor, KernelLaunch
 from ..utils.exceptions import DeviceError, ExecutionError, UnsupportedOperationError
 from ..utils.type_mapping import to_cdr_dtype
@@ -81,13 +82,17 @@ class GCUKernelExecutor:
 
     def execute(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor],
                 outputs: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
-        """Run `launch`; allocates the outputs when none are passed.  Asynchronous."""
+        """Run `launch`; allocates the outputs when none are passed.  Asynchronous.  Inputs that are
+        not contiguous are first gathered with the strided-copy template (never by torch)."""
         if not inputs:
             raise ExecutionError("kernel launch without inputs", kernel_name=launch.name)
         device = inputs[0].device
         if device.type != "cuda":
             raise DeviceError(f"kernel templates run on CUDA tensors, got {device}")
-        ins = [t if t.is_contiguous() else t.contiguous() for t in inputs]
+        if launch.template == Template.COPY:
+            ins = list(inputs)                      # the view's strides are the point
+        else:
+            ins = [t if t.is_contiguous() else self.make_contiguous(t) for t in inputs]
         if outputs is None:
             outputs = [torch.empty(shape, dtype=dt, device=device)
                        for shape, dt in zip(launch.out_shapes, launch.out_dtypes)]
@@ -107,6 +112,11 @@ class GCUKernelExecutor:
                                      ws.numel() if ws is not None else 0, stream)
         raise_for_status(self.lib, rc, launch.name)
         return list(outputs)
+
+    def make_contiguous(self, t: torch.Tensor) -> torch.Tensor:
+        """Contiguous copy of a strided view through the strided-copy template."""
+        launch = KernelLaunch(Template.COPY, "contiguous", [], [], None, [tuple(t.shape)], [t.dtype])
+        return self.execute(launch, [t])[0]
 
     def execute_host(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor], device: int = 0) -> list[torch.Tensor]:
         """Reference calling convention: CPU tensors in, CPU tensors out, synchronous

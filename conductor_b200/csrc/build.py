@@ -28,6 +28,7 @@ SOURCES = {
     "cdr_reduce.cu": ["--fmad=false"],
     "cdr_softmax.cu": ["--fmad=false"],
     "cdr_layernorm.cu": [],
+    "cdr_copy.cu": [],
     "cdr_gemm.cu": [],
     "cdr_attention.cu": [],
 }

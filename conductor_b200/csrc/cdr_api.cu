@@ -104,7 +104,8 @@ int check_params(int template_id, const void* params, size_t bytes) {
     case CDR_T_ROW_REDUCE:
     case CDR_T_FULL_REDUCE: want = sizeof(cdr_reduce_params); break;
     case CDR_T_SOFTMAX_FWD:
-    case CDR_T_SOFTMAX_BWD: return CDR_OK;
+    case CDR_T_SOFTMAX_BWD:
+    case CDR_T_COPY: return CDR_OK;
     case CDR_T_GEMM_EPILOGUE: want = sizeof(cdr_gemm_params); break;
     case CDR_T_ATTENTION: want = sizeof(cdr_attn_params); break;
     case CDR_T_LAYER_NORM: want = sizeof(cdr_norm_params); break;
@@ -258,6 +259,7 @@ int cdr_launch(int template_id, const cdr_tensor* inputs, int n_inputs, const cd
     case CDR_T_ATTENTION:
       return launch_attention(inputs, n_inputs, outputs, n_outputs, static_cast<const cdr_attn_params*>(params),
                               workspace, workspace_bytes, s);
+    case CDR_T_COPY: return launch_strided_copy(inputs, n_inputs, outputs, n_outputs, s);
     case CDR_T_LAYER_NORM:
       return launch_layer_norm(inputs, n_inputs, outputs, n_outputs, static_cast<const cdr_norm_params*>(params), s);
     default:

@@ -76,6 +76,7 @@ int launch_softmax_bwd(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
                        cudaStream_t stream);
 int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                          const cdr_gemm_params* p, cudaStream_t stream);
+int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, cudaStream_t stream);
 int launch_layer_norm(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, const cdr_norm_params* p,
                       cudaStream_t stream);
 int launch_attention(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,

@@ -92,8 +92,11 @@ enum cdr_template {
   CDR_T_ATTENTION = 6,    /* fused scaled-dot-product attention, params = cdr_attn_params*/
   CDR_T_FULL_REDUCE = 7,  /* elementwise chain + reduction over every element,
                              params = cdr_reduce_params; needs workspace                 */
-  CDR_T_LAYER_NORM = 8    /* layer normalisation over the last dim, inputs (x[, weight][, bias]),
+  CDR_T_LAYER_NORM = 8,   /* layer normalisation over the last dim, inputs (x[, weight][, bias]),
                              params = cdr_norm_params                                    */
+  CDR_T_COPY = 9          /* gather a strided view (the input descriptor's strides are honoured) into a
+                             contiguous output of the same shape: transpose / permute / contiguous();
+                             no params                                                    */
 };
 
 /* ---- elementwise programs -------------------------------------------------

@@ -223,6 +223,35 @@ def test_layer_norm_fused_and_decomposed():
         compiled(lambda x_: F.layer_norm(x_, (50, 256)))(x.to(DEV))
 
 
+def test_layout_changes_and_multi_head_attention():
+    """transpose / permute / t move data with the strided-copy template; with them a multi-head
+    self-attention block (view -> transpose -> attention -> transpose -> reshape) compiles."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(55)
+    a = torch.randn(12, 40, generator=gen)
+    t4 = torch.randn(2, 3, 8, 16, generator=gen)
+    exact = {"t_add": (lambda x: x.t() + 1.0, [a]), "permute": (lambda x: x.permute(0, 2, 1, 3).contiguous() * 2.0, [t4]),
+             "transpose_sum": (lambda x: x.transpose(-1, -2).sum(-1), [t4])}
+    for name, (fn, inputs) in exact.items():
+        want = rp.run_reference(fn, inputs)
+        got = compiled(fn)(*[t.to(DEV) for t in inputs]).cpu()
+        assert got.shape == want.shape, name
+        assert_close(got, want, 1e-5, name)
+
+    def mha(x):
+        B, S, E = x.shape
+        H, D = 4, E // 4
+        q = x.view(B, S, H, D).transpose(1, 2)
+        o = F.scaled_dot_product_attention(q, q * 0.5, q + 1.0, is_causal=True)
+        return o.transpose(1, 2).reshape(B, S, E)
+
+    x = torch.randn(2, 256, 256, generator=gen).bfloat16()
+    want = rp.run_reference(mha, [x])
+    got = compiled(mha)(x.to(DEV))
+    assert got.shape == want.shape
+    assert_close(got.float(), want.float(), 2e-2, "multi-head attention block")
+
+
 def test_mixed_dtype_clusters():
     """A bool mask input, a comparison that leaves the graph as bool, an integer tensor scaling a
     float one: exact against eager."""

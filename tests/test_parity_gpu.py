@@ -459,6 +459,26 @@ def test_full_size_softmax(executor):
     assert dx.sum(-1).abs().max().item() < 1e-3               # softmax gradients sum to zero per row
 
 
+def test_strided_copy_template(executor):
+    """CDR_T_COPY gathers a strided view into a contiguous tensor, bit-exactly: vector path (inner
+    dimension contiguous), scalar path (transposes of the inner dimension), every element size."""
+    gen = torch.Generator().manual_seed(92)
+    views = []
+    x = torch.randn(2, 24, 4, 64, generator=gen).bfloat16().to(DEV)
+    views += [x.transpose(1, 2), x.permute(2, 0, 1, 3), x.permute(0, 1, 3, 2), x[:, ::2], x[..., 8:40]]
+    y = torch.randn(37, 53, generator=gen).to(DEV)
+    views += [y.t(), y[3:, 5:], y.t()[::3]]
+    views += [torch.arange(3 * 5 * 7, device=DEV).reshape(3, 5, 7).permute(2, 0, 1),
+              (torch.rand(9, 11, generator=gen) > 0.5).to(DEV).t(),
+              torch.arange(60, dtype=torch.int64, device=DEV).reshape(6, 10).t()]
+    for v in views:
+        out = torch.empty(v.shape, dtype=v.dtype, device=DEV)
+        abi.launch(Template.COPY, [v], [out])
+        assert torch.equal(out, v), (tuple(v.shape), v.stride(), v.dtype)
+    out = torch.empty(5, 4, device=DEV)
+    assert abi.launch(Template.COPY, [y[:4, :5]], [out], check=False) == -1          # shapes differ
+
+
 def test_layer_norm_template(executor):
     """CDR_T_LAYER_NORM through the C ABI against a float64 evaluation: row lengths from one vector
     to the 1024-thread variant, with and without scale / shift, bf16, and the refusals."""
