@@ -252,6 +252,39 @@ def test_layout_changes_and_multi_head_attention():
     assert_close(got.float(), want.float(), 2e-2, "multi-head attention block")
 
 
+def test_transformer_block_compiles_and_matches_eager():
+    """A pre-norm transformer block written with functional ops: layer norm, three projections,
+    multi-head causal attention, output projection, residuals, GELU MLP -- every piece runs on a
+    kernel template; the whole block is compared with eager bf16 on the CPU."""
+    F = torch.nn.functional
+    torch.manual_seed(56)
+    B, S, E, H = 2, 128, 256, 4
+    D = E // H
+
+    def p(*shape, scale=0.05):
+        return (torch.randn(*shape) * scale).bfloat16()
+
+    params = [p(E) + 1, p(E), p(E, E), p(E), p(E, E), p(E), p(E, E), p(E), p(E, E), p(E), p(E) + 1, p(E), p(4 * E, E), p(4 * E),
+              p(E, 4 * E), p(E)]
+
+    def block(x, g1, b1, wq, bq, wk, bk, wv, bv, wo, bo, g2, b2, w1, c1, w2, c2):
+        h = F.layer_norm(x, (E,), g1, b1)
+        q = F.linear(h, wq, bq).view(B, S, H, D).transpose(1, 2)
+        k = F.linear(h, wk, bk).view(B, S, H, D).transpose(1, 2)
+        v = F.linear(h, wv, bv).view(B, S, H, D).transpose(1, 2)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, E)
+        x = x + F.linear(a, wo, bo)
+        h = F.layer_norm(x, (E,), g2, b2)
+        return x + F.linear(F.gelu(F.linear(h, w1, c1)), w2, c2)
+
+    x = torch.randn(B, S, E).bfloat16()
+    want = rp.run_reference(block, [x] + params)
+    f = compiled(block)
+    got = f(*[t.to(DEV) for t in [x] + params])
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    assert_close(got.float(), want.float(), 3e-2, "transformer block")
+
+
 def test_mixed_dtype_clusters():
     """A bool mask input, a comparison that leaves the graph as bool, an integer tensor scaling a
     float one: exact against eager."""
