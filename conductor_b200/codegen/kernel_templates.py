@@ -86,6 +86,7 @@ class KernelLaunch:
     cluster: Optional[FusionCluster] = None
     needs_workspace: bool = False
     view_strides: Optional[tuple] = None  # COPY launches: element strides of the view of inputs[0] that is gathered
+    view_offset: int = 0                  # COPY launches: first element of that view, relative to inputs[0]'s own
 
     def describe(self) -> str:
         ins = ", ".join(b.name for b in self.inputs)
@@ -460,27 +461,37 @@ def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
     if out.shape is None or not node.inputs:
         raise UnsupportedOperationError(node.op_name, "unknown output shape")
     src = node.inputs[0]
-    if src.shape is not None and math.prod(src.shape) != math.prod(out.shape):
-        raise UnsupportedOperationError(node.op_name, "element count changes")
     info = get_op_desc(node.op_name)
-    if info is not None and info.canonical_name == "permute":
-        # transpose / permute / t / swapaxes / movedim: replay the call on a meta tensor to get the
-        # view's strides, then gather that view into a contiguous buffer (every buffer of a plan is
-        # contiguous, so the layout change has to move data)
+    canonical = info.canonical_name if info is not None else None
+    if canonical != "slice" and src.shape is not None and math.prod(src.shape) != math.prod(out.shape):
+        raise UnsupportedOperationError(node.op_name, "element count changes")
+    if canonical in ("permute", "slice"):
+        # transpose / permute / t / swapaxes / movedim, and basic slicing (x[a:b, ::2], narrow,
+        # select): replay the call on a meta tensor to get the view's strides and first element,
+        # then gather that view into a contiguous buffer (every buffer of a plan is contiguous, so
+        # the layout change has to move data)
         if src.shape is None:
             raise UnsupportedOperationError(node.op_name, "unknown input shape")
+        if len(node.inputs) != 1:
+            raise UnsupportedOperationError(node.op_name, "indexing by a tensor")
         try:
-            view = getattr(torch.empty(src.shape, dtype=src.dtype, device="meta"), node.op_name)(
-                *_const_args(node), **node.metadata.get("kwargs", {}))
+            meta = torch.empty(src.shape, dtype=src.dtype, device="meta")
+            consts = _const_args(node)
+            if node.op_name in ("getitem", "__getitem__"):
+                view = meta[consts[0]]
+            else:
+                view = getattr(meta, node.op_name)(*consts, **node.metadata.get("kwargs", {}))
         except Exception as exc:
             raise UnsupportedOperationError(node.op_name, f"cannot evaluate the layout change: {exc}") from exc
         if tuple(view.shape) != tuple(out.shape):
             raise UnsupportedOperationError(node.op_name, f"shape {tuple(view.shape)} != {tuple(out.shape)}")
-        if view.is_contiguous():
+        if not isinstance(view, torch.Tensor):
+            raise UnsupportedOperationError(node.op_name, "the call returns several views")
+        if view.is_contiguous() and view.storage_offset() == 0 and view.numel() == meta.numel():
             return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
                                 cluster=cluster)
         return KernelLaunch(Template.COPY, cluster.signature(), [src], [out], None, [out.shape], [out.dtype],
-                            cluster=cluster, view_strides=tuple(view.stride()))
+                            cluster=cluster, view_strides=tuple(view.stride()), view_offset=int(view.storage_offset()))
     return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
                         cluster=cluster)
 

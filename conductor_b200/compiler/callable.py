@@ -184,11 +184,11 @@ class Callable:
             if launch.template == 0:                       # alias: reshape, no kernel
                 env[launch.outputs[0]] = ins[0].reshape(self._shard_shape(launch.out_shapes[0], rows))
                 continue
-            if launch.view_strides is not None:            # transpose / permute: gather the strided view
+            if launch.view_strides is not None:            # transpose / permute / slice: gather the strided view
                 if rows is not None:
                     raise ExecutionError("a plan with layout changes cannot run on a block of its rows", kernel_name=launch.name)
                 src = ins[0]
-                ins = [torch.as_strided(src, launch.out_shapes[0], launch.view_strides, src.storage_offset())]
+                ins = [torch.as_strided(src, launch.out_shapes[0], launch.view_strides, src.storage_offset() + launch.view_offset)]
             outs = None
             if rows is not None:
                 outs = [torch.empty(self._shard_shape(sh, rows), dtype=dt, device=device)

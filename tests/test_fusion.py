@@ -238,3 +238,18 @@ def test_params_struct_sizes_match_header():
     assert ctypes.sizeof(kt.CdrEwInstr) == 24
     assert ctypes.sizeof(kt.CdrEwParams) == 16 + 32 + 16 + 24 * 24
     assert ctypes.sizeof(kt.CdrReduceParams) == ctypes.sizeof(kt.CdrEwParams) + 8
+
+
+def test_basic_slicing_lowers_to_a_strided_copy_with_an_offset():
+    """x[:, 4:12:2] is a view of the input with strides (16, 2) starting at element 4: one COPY launch
+    carrying those, then the elementwise chain on the contiguous result.  Indexing by a tensor is not
+    a view and is refused."""
+    art = compile_with_dynamo(lambda x: x[:, 4:12:2] * 2.0, [torch.randn(8, 16)])
+    copy = [l for l in art.launches if l.template == Template.COPY]
+    assert len(copy) == 1
+    assert copy[0].view_strides == (16, 2) and copy[0].view_offset == 4 and tuple(copy[0].out_shapes[0]) == (8, 4)
+    art = compile_with_dynamo(lambda x: x.select(0, 3) + 1.0, [torch.randn(8, 16)])
+    copy = [l for l in art.launches if l.template == Template.COPY]
+    assert copy[0].view_strides == (1,) and copy[0].view_offset == 48
+    with pytest.raises(Exception):
+        compile_with_dynamo(lambda x, i: x[i] * 2.0, [torch.randn(8, 16), torch.tensor([1, 3])])
