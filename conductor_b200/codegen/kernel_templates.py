@@ -477,7 +477,10 @@ def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
         try:
             meta = torch.empty(src.shape, dtype=src.dtype, device="meta")
             consts = _const_args(node)
-            if node.op_name in ("getitem", "__getitem__"):
+            if "view_call" in node.metadata:     # one member of chunk / split / unbind
+                method, m_args, m_kwargs, index = node.metadata["view_call"]
+                view = getattr(meta, method)(*m_args, **m_kwargs)[index]
+            elif node.op_name in ("getitem", "__getitem__"):
                 view = meta[consts[0]]
             else:
                 view = getattr(meta, node.op_name)(*consts, **node.metadata.get("kwargs", {}))

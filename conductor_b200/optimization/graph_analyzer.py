@@ -22,6 +22,7 @@ import torch
 
 from ..codegen.operation_factory import get_operation_factory
 from ..utils.constants import BufferScope
+from ..utils.exceptions import UnsupportedOperationError
 from ..utils.logging import get_logger
 from .buffers import Buffer, BufferManager
 from .graph_nodes import ConductorNode
@@ -74,6 +75,10 @@ class ComputationDAG:
 def _sanitize(name: str) -> str:
     s = re.sub(r"[^0-9a-zA-Z_]", "_", str(name))
     return s if s and not s[0].isdigit() else f"buf_{s}"
+
+
+# calls that return a tuple of views of their first argument
+_MULTI_VIEW_OPS = ("chunk", "split", "unbind", "tensor_split", "split_with_sizes")
 
 
 def _meta_tensor(node: torch.fx.Node):
@@ -182,6 +187,23 @@ class GraphAnalyzer:
         args = list(node.args)
         kwargs = dict(node.kwargs)
         extra_const: list[Buffer] = []
+        if op_name in _MULTI_VIEW_OPS:
+            # chunk / split / unbind return a tuple of views; the tuple itself is no value of the
+            # plan -- each getitem on it becomes a slice of the tuple op's own input
+            if any(u.op != "call_function" or self._factory.extract_operation_name(u) not in ("getitem", "__getitem__")
+                   for u in node.users):
+                raise UnsupportedOperationError(op_name, "the tuple of views is used other than by indexing")
+            return None
+        view_call = None
+        if op_name in ("getitem", "__getitem__") and isinstance(args[0], torch.fx.Node) and \
+                args[0].op in ("call_function", "call_method") and \
+                self._factory.extract_operation_name(args[0]) in _MULTI_VIEW_OPS:
+            tup = args[0]
+            if not isinstance(args[1], int) or not tup.args or not isinstance(tup.args[0], torch.fx.Node) or \
+                    any(isinstance(a, torch.fx.Node) for a in list(tup.args[1:]) + list(tup.kwargs.values())):
+                raise UnsupportedOperationError(op_name, "unsupported indexing of a tuple of views")
+            view_call = (self._factory.extract_operation_name(tup), tuple(tup.args[1:]), dict(tup.kwargs), args[1])
+            op_name, args, kwargs = "view_of", [tup.args[0]], {}
         if node.op == "call_module":
             op_name, args, kwargs, extra_const = self._lower_module_call(node, gm, dag)
 
@@ -189,6 +211,8 @@ class GraphAnalyzer:
         cnode.metadata["fx_name"] = node.name
         cnode.metadata["fx_op"] = node.op
         cnode.metadata["fx_target"] = node.target
+        if view_call is not None:
+            cnode.metadata["view_call"] = view_call
         arg_spec = []
         for a in args:
             arg_spec.append(self._bind_operand(a, cnode))

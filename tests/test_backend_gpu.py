@@ -272,6 +272,31 @@ def test_basic_slicing_goes_through_the_strided_copy():
         assert torch.equal(got, want), name
 
 
+def test_fused_qkv_projection_split_into_heads():
+    """One [E, 3E] projection, chunk(3) into q / k / v, heads via view + transpose, causal attention:
+    the members of the chunk are gathered straight from the projection's output."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(58)
+    B, S, E, H = 2, 128, 256, 4
+    x = (0.5 * torch.randn(B, S, E, generator=gen)).bfloat16()
+    w = (torch.randn(3 * E, E, generator=gen) / 16).bfloat16()
+    b = (0.1 * torch.randn(3 * E, generator=gen)).bfloat16()
+
+    def attn(x_, w_, b_):
+        q, k, v = F.linear(x_, w_, b_).chunk(3, dim=-1)
+        q, k, v = (t.view(B, S, H, E // H).transpose(1, 2) for t in (q, k, v))
+        return F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, E)
+
+    want = rp.run_reference(attn, [x, w, b])
+    got = compiled(attn)(x.to(DEV), w.to(DEV), b.to(DEV))
+    assert got.shape == want.shape
+    assert_close(got.float(), want.float(), 2e-2, "fused qkv attention")
+    for name, fn in {"split": lambda t: (lambda a, c: a - c)(*t.split(E // 2, dim=-1)),
+                     "unbind": lambda t: t.unbind(0)[1] * 2.0}.items():
+        want = rp.run_reference(fn, [x])
+        assert torch.equal(compiled(fn)(x.to(DEV)).cpu(), want), name
+
+
 def test_transformer_block_compiles_and_matches_eager():
     """A pre-norm transformer block written with functional ops: layer norm, three projections,
     multi-head causal attention, output projection, residuals, GELU MLP -- every piece runs on a

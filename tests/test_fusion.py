@@ -253,3 +253,16 @@ def test_basic_slicing_lowers_to_a_strided_copy_with_an_offset():
     assert copy[0].view_strides == (1,) and copy[0].view_offset == 48
     with pytest.raises(Exception):
         compile_with_dynamo(lambda x, i: x[i] * 2.0, [torch.randn(8, 16), torch.tensor([1, 3])])
+
+
+def test_chunk_split_unbind_members_become_slices_of_the_source():
+    """chunk / split / unbind return a tuple of views; the tuple is no value of the plan -- every
+    getitem on it lowers to one strided copy of the tuple op's own input."""
+    art = compile_with_dynamo(lambda x: x.chunk(2, -1)[0] * x.chunk(2, -1)[1], [torch.randn(8, 16)])
+    views = sorted((l.view_offset, l.view_strides, tuple(l.out_shapes[0])) for l in art.launches if l.template == Template.COPY)
+    assert views == [(0, (16, 1), (8, 8)), (8, (16, 1), (8, 8))]
+    art = compile_with_dynamo(lambda x: (lambda q, k, v: q * k + v)(*x.unbind(0)), [torch.randn(3, 8, 16)])
+    assert sorted(l.view_offset for l in art.launches if l.template == Template.COPY) == [0, 128, 256]
+    art = compile_with_dynamo(lambda x: torch.split(x, [4, 12], dim=-1)[1] + 1.0, [torch.randn(8, 16)])
+    copy = [l for l in art.launches if l.template == Template.COPY]
+    assert len(copy) == 1 and copy[0].view_offset == 4 and tuple(copy[0].out_shapes[0]) == (8, 12)
