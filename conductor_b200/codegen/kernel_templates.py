@@ -153,6 +153,67 @@ class _ProgramBuilder:
             return self._emit(EwOp.CONST, imm=val, dtype=dtype)
         raise UnsupportedOperationError(node.op_name, f"operand {val!r} cannot be lowered")
 
+    def _lower_composite(self, node, spec, kw, odt, is_num) -> int:
+        """leaky_relu, elu, softplus, hardswish, hardsigmoid, masked_fill, lerp and inference-mode
+        dropout as short sequences of existing opcodes.  Intermediates stay fp32 (never rounded to a
+        16-bit output type); only the last instruction rounds, as eager's fused kernels do."""
+        f32 = torch.float32
+        name = node.op_name.rstrip("_")
+
+        def num(pos, key, default):
+            if key in kw:
+                return kw[key]
+            if len(spec) > pos:
+                if not is_num(spec[pos]):
+                    raise UnsupportedOperationError(node.op_name, f"{key} must be a Python number")
+                return spec[pos][1]
+            return default
+
+        x = self._operand(node, spec[0], odt)
+        const = lambda v: self._emit(EwOp.CONST, imm=v, dtype=f32)  # noqa: E731
+        if name == "dropout":
+            if num(2, "training", True) and num(1, "p", 0.5) != 0:
+                raise UnsupportedOperationError(node.op_name, "training-mode dropout")
+            return x
+        if name == "leaky_relu":                              # max(x, 0) + slope * min(x, 0)
+            slope = num(1, "negative_slope", 0.01)
+            zero = const(0.0)
+            neg = self._emit(EwOp.MUL_IMM, self._emit(EwOp.MIN, x, zero, dtype=f32), imm=slope, dtype=f32)
+            return self._emit(EwOp.ADD, self._emit(EwOp.MAX, x, zero, dtype=f32), neg, dtype=odt)
+        if name == "elu":                                     # x > 0 ? x : alpha * (exp(x) - 1)
+            alpha = num(1, "alpha", 1.0)
+            em1 = self._emit(EwOp.ADD_IMM, self._emit(EwOp.EXP, x, dtype=f32), imm=-1.0, dtype=f32)
+            neg = self._emit(EwOp.MUL_IMM, em1, imm=alpha, dtype=f32)
+            return self._emit(EwOp.WHERE, self._emit(EwOp.GT, x, const(0.0), dtype=f32), x, neg, dtype=odt)
+        if name == "softplus":                                # beta*x > threshold ? x : log(1 + exp(beta*x)) / beta
+            beta, threshold = num(1, "beta", 1.0), num(2, "threshold", 20.0)
+            bx = self._emit(EwOp.MUL_IMM, x, imm=beta, dtype=f32)
+            soft = self._emit(EwOp.LOG, self._emit(EwOp.ADD_IMM, self._emit(EwOp.EXP, bx, dtype=f32), imm=1.0, dtype=f32), dtype=f32)
+            soft = self._emit(EwOp.MUL_IMM, soft, imm=1.0 / beta, dtype=f32)
+            return self._emit(EwOp.WHERE, self._emit(EwOp.GT, bx, const(threshold), dtype=f32), x, soft, dtype=odt)
+        if name in ("hardswish", "hardsigmoid"):              # clamp(x + 3, 0, 6) / 6 [* x]
+            t = self._emit(EwOp.ADD_IMM, x, imm=3.0, dtype=f32)
+            t = self._emit(EwOp.MIN, self._emit(EwOp.MAX, t, const(0.0), dtype=f32), const(6.0), dtype=f32)
+            if name == "hardsigmoid":
+                return self._emit(EwOp.MUL_IMM, t, imm=1.0 / 6.0, dtype=odt)
+            return self._emit(EwOp.MUL_IMM, self._emit(EwOp.MUL, x, t, dtype=f32), imm=1.0 / 6.0, dtype=odt)
+        if name == "masked_fill":                             # mask ? value : x
+            if len(spec) < 3 or not is_num(spec[2]):
+                raise UnsupportedOperationError(node.op_name, "the fill value must be a Python number")
+            mask = self._operand(node, spec[1], odt)
+            return self._emit(EwOp.WHERE, mask, self._emit(EwOp.CONST, imm=spec[2][1], dtype=odt), x, dtype=odt)
+        if name == "lerp":                                    # x + w * (y - x)
+            if len(spec) < 3:
+                raise UnsupportedOperationError(node.op_name, "needs start, end and weight")
+            y = self._operand(node, spec[1], odt)
+            d = self._emit(EwOp.SUB, y, x, dtype=f32)
+            if is_num(spec[2]):
+                wd = self._emit(EwOp.MUL_IMM, d, imm=spec[2][1], dtype=f32)
+            else:
+                wd = self._emit(EwOp.MUL, self._operand(node, spec[2], odt), d, dtype=f32)
+            return self._emit(EwOp.ADD, x, wd, dtype=odt)
+        raise UnsupportedOperationError(node.op_name, "no lowering")
+
     def lower(self, node) -> None:
         info = get_op_desc(node.op_name)
         out = node.outputs[0]
@@ -189,6 +250,9 @@ class _ProgramBuilder:
             if hi is not None:
                 r = self._emit(EwOp.MIN, r, self._emit(EwOp.CONST, imm=hi, dtype=odt), dtype=odt)
             self.reg_of[out] = r
+            return
+        if canon == "composite":                              # activations written out over the opcode set
+            self.reg_of[out] = self._lower_composite(node, spec, kw, odt, is_num)
             return
         if canon == "pow":                                    # pow / square / reciprocal
             x = self._operand(node, spec[0], odt)

@@ -133,6 +133,11 @@ class OperatorRegistry:
         # lowered to existing instructions: clamp -> max/min with constants, pow -> mul / sqrt / reciprocal
         r(_ew("clamp", EwOp.MAX, 1), "clip", "clamp_", "hardtanh", "relu6")
         r(_ew("pow", EwOp.MUL, 2), "square", "reciprocal")
+        # activations and selections written out over the opcode set by the program builder
+        r(_ew("composite", EwOp.WHERE, 1), "leaky_relu", "leaky_relu_", "elu", "elu_", "softplus", "hardswish",
+          "hardsigmoid", "dropout")
+        r(_ew("composite2", EwOp.WHERE, 2, canonical="composite"), "masked_fill", "masked_fill_")
+        r(_ew("composite3", EwOp.WHERE, 3, canonical="composite"), "lerp")
         # dtype casts are a rounding-only instruction
         r(_ew("to_dtype", EwOp.COPY, 1), "float", "bfloat16", "half", "to", "type")
         r(_red("sum", ReduceOp.SUM))

@@ -252,6 +252,39 @@ def test_layout_changes_and_multi_head_attention():
     assert_close(got.float(), want.float(), 2e-2, "multi-head attention block")
 
 
+def test_composite_activations_and_selections():
+    """leaky_relu / elu / softplus / hardswish / hardsigmoid / masked_fill / lerp / inference-mode
+    dropout are written out over the elementwise opcodes: selections exact, the rest within 1e-5
+    in fp32 and 2e-2 in bf16 (intermediates stay fp32, one rounding at the end)."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(59)
+    x = 4.0 * torch.randn(72, 160, generator=gen)
+    y = torch.randn(72, 160, generator=gen)
+    mask = torch.rand(72, 160, generator=gen) > 0.5
+    x[0, :4] = torch.tensor([0.0, 25.0, -30.0, 3.0])
+    exact = {"masked_fill": (lambda a, m: a.masked_fill(m, -1e9) * 1.0, [x, mask]),
+             "dropout_eval": (lambda a: F.dropout(a, 0.3, training=False) + 1.0, [x])}
+    close = {"leaky_relu": (lambda a: F.leaky_relu(a, 0.1), [x]), "elu": (lambda a: F.elu(a, 1.5), [x]),
+             "softplus": (lambda a: F.softplus(a, beta=2.0, threshold=10.0), [x]), "hardswish": (lambda a: F.hardswish(a), [x]),
+             "hardsigmoid": (lambda a: F.hardsigmoid(a), [x]), "lerp": (lambda a, b: torch.lerp(a, b, 0.3), [x, y]),
+             "lerp_tensor": (lambda a, b: torch.lerp(a, b, torch.sigmoid(b)), [x, y]),
+             "masked_softmax": (lambda a, m: torch.softmax(a.masked_fill(m, float("-inf")), -1), [x, mask & (torch.arange(160) > 0)])}
+    for name, (fn, inputs) in {**exact, **close}.items():
+        want = rp.run_reference(fn, inputs)
+        got = compiled(fn)(*[t.to(DEV) for t in inputs]).cpu()
+        if name in exact:
+            assert torch.equal(got, want), name
+        else:
+            assert_close(got, want, 1e-5, name)
+    for name in ("leaky_relu", "elu", "softplus", "hardswish"):
+        fn, inputs = close[name]
+        xb = inputs[0].bfloat16()
+        want = rp.run_reference(fn, [xb])
+        got = compiled(fn)(xb.to(DEV)).cpu()
+        assert got.dtype == torch.bfloat16
+        assert_close(got.float(), want.float(), 2e-2, name + " bf16")
+
+
 def test_basic_slicing_goes_through_the_strided_copy():
     """x[a:b], x[..., ::2], narrow, select: a view with an offset and strides, gathered by the
     strided-copy template; results are bit-identical to eager (no arithmetic on the copied part)."""

@@ -266,3 +266,17 @@ def test_chunk_split_unbind_members_become_slices_of_the_source():
     art = compile_with_dynamo(lambda x: torch.split(x, [4, 12], dim=-1)[1] + 1.0, [torch.randn(8, 16)])
     copy = [l for l in art.launches if l.template == Template.COPY]
     assert len(copy) == 1 and copy[0].view_offset == 4 and tuple(copy[0].out_shapes[0]) == (8, 12)
+
+
+def test_composite_activations_stay_one_elementwise_launch():
+    """leaky_relu, elu, softplus, hardswish, masked_fill, lerp expand into a few opcodes inside the
+    chain they belong to -- still one launch; training-mode dropout is refused."""
+    F = torch.nn.functional
+    x, y = torch.randn(8, 16), torch.randn(8, 16)
+    fn = lambda a, b: torch.lerp(F.leaky_relu(a, 0.1), F.elu(b), 0.25).masked_fill(b > 0, 0.0)  # noqa: E731
+    art = compile_with_dynamo(fn, [x, y])
+    assert [l.template for l in art.launches] == [Template.ELEMENTWISE]
+    ops = [ins.op for ins in art.launches[0].params.instr[: art.launches[0].params.n_instr]]
+    assert EwOp.WHERE in ops and EwOp.EXP in ops and EwOp.MIN in ops
+    with pytest.raises(Exception):
+        compile_with_dynamo(lambda a: F.dropout(a, 0.5, training=True) * 2.0, [x])
