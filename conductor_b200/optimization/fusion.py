@@ -38,6 +38,9 @@ logger = get_logger(__name__)
 
 # limits of one elementwise program (include/conductor_b200.h)
 MAX_EW_INSTR = 24
+# instructions the program builder emits for each written-out activation / selection
+_COMPOSITE_INSTR = {"leaky_relu": 5, "elu": 6, "softplus": 8, "hardswish": 7, "hardsigmoid": 6, "masked_fill": 2,
+                    "lerp": 3, "dropout": 1}
 MAX_EW_INPUTS = 8
 MAX_EW_OUTPUTS = 4
 
@@ -172,8 +175,25 @@ class FusionHeuristics:
                     if b.consumers and all(c in inside for c in b.consumers) and not b.is_output]
         return FusionCluster(nodes=list(nodes), internal_buffers=internal).estimate_performance_gain()
 
+    @staticmethod
+    def instruction_estimate(node: ConductorNode) -> int:
+        """Upper bound on the program instructions one elementwise node lowers to: composites and
+        clamps expand into several opcodes, and every Python-number operand may cost a CONST."""
+        if not node.is_elementwise():
+            return 0
+        info = get_op_desc(node.op_name)
+        canon = info.canonical_name if info is not None else node.op_name
+        if canon == "composite":
+            return _COMPOSITE_INSTR.get(node.op_name.rstrip("_"), 8)
+        if canon == "clamp":
+            return 4
+        if canon in ("add", "sub", "mul", "div"):            # immediate forms: no CONST
+            return 1
+        consts = sum(1 for k, _ in node.metadata.get("arg_spec", []) if k == "const")
+        return 1 + consts
+
     def check_memory_constraints(self, cluster: FusionCluster) -> bool:
-        n_instr = sum(1 for n in cluster.nodes if n.is_elementwise())
+        n_instr = sum(self.instruction_estimate(n) for n in cluster.nodes)
         return (n_instr <= MAX_EW_INSTR and len(cluster.external_inputs) <= MAX_EW_INPUTS
                 and len(cluster.external_outputs) <= max(MAX_EW_OUTPUTS, 1))
 
@@ -339,7 +359,8 @@ class FusionEngine:
         ext_in = {b for n in nodes for b in n.inputs if b.producer not in inside}
         ext_out = {b for n in nodes for b in n.outputs
                    if b.is_output or any(c not in inside for c in b.consumers)}
-        return len(nodes) <= MAX_EW_INSTR - 4 and len(ext_in) <= MAX_EW_INPUTS and len(ext_out) <= MAX_EW_OUTPUTS
+        n_instr = sum(FusionHeuristics.instruction_estimate(n) for n in nodes)
+        return n_instr <= MAX_EW_INSTR - 4 and len(ext_in) <= MAX_EW_INPUTS and len(ext_out) <= MAX_EW_OUTPUTS
 
     def _grow_reduction(self, red, claimed) -> list[ConductorNode]:
         """The reduction plus the elementwise producers that feed only it (transitively)."""
@@ -358,7 +379,8 @@ class FusionEngine:
                 if b.shape != full_shape:
                     continue
                 trial_in = {x for m in group + [p] for x in m.inputs if x.producer not in inside | {p}}
-                if len(group) + 1 > MAX_EW_INSTR - 4 or len(trial_in) > MAX_EW_INPUTS:
+                n_instr = sum(FusionHeuristics.instruction_estimate(m) for m in group + [p])
+                if n_instr > MAX_EW_INSTR - 4 or len(trial_in) > MAX_EW_INPUTS:
                     continue
                 group.append(p)
                 inside.add(p)

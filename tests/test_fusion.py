@@ -280,3 +280,7 @@ def test_composite_activations_stay_one_elementwise_launch():
     assert EwOp.WHERE in ops and EwOp.EXP in ops and EwOp.MIN in ops
     with pytest.raises(Exception):
         compile_with_dynamo(lambda a: F.dropout(a, 0.5, training=True) * 2.0, [x])
+    # a chain whose expansion would not fit one 24-instruction program is split by the fusion pass
+    long = lambda a, b: (F.softplus(F.elu(F.hardswish(F.leaky_relu(a)))) + b).sum(-1)  # noqa: E731
+    art = compile_with_dynamo(long, [x, y])
+    assert [l.template for l in art.launches] == [Template.ELEMENTWISE, Template.ROW_REDUCE]
