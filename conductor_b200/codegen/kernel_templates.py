@@ -138,6 +138,7 @@ class _ProgramBuilder:
         self.reg_of: dict[Buffer, int] = {b: i for i, b in enumerate(self.inputs)}
         self.instr: list[tuple] = []
         self.is_int = bool(self.inputs) and all(is_int(b.dtype) for b in self.inputs)
+        self.shape_override: dict[Buffer, tuple] = {}   # inputs replaced by an expanded copy
 
     def _emit(self, op, a=0, b=0, c=0, imm=0.0, dtype=torch.float32) -> int:
         if len(self.instr) >= CDR_EW_MAX_INSTR:
@@ -345,7 +346,7 @@ class _ProgramBuilder:
         for i, b in enumerate(self.inputs):
             if b.shape is None:
                 raise UnsupportedOperationError("elementwise", f"input {b.name} has no static shape")
-            p.input_mode[i] = classify_broadcast(b.shape, self.iter_shape)
+            p.input_mode[i] = classify_broadcast(self.shape_override.get(b, b.shape), self.iter_shape)
         for i, r in enumerate(out_regs):
             p.out_reg[i] = r
         for i, (op, a, b, c, imm, rt) in enumerate(self.instr):
@@ -359,7 +360,31 @@ def _require_shapes(cluster: FusionCluster) -> None:
             raise UnsupportedOperationError(cluster.signature(), f"buffer {b.name} has no static shape")
 
 
-def _lower_elementwise(cluster: FusionCluster) -> KernelLaunch:
+def _expand_general_broadcasts(inputs, iter_shape, cluster: FusionCluster):
+    """The elementwise kernels index an input as full-size, one row, one column or a scalar.  Any
+    other broadcast (a middle dimension of 1, a missing leading batch dimension) is materialised
+    first: one strided copy of the input's expand() view, whose broadcast dimensions have stride 0.
+    Returns the launches to run first and the input list with those inputs replaced."""
+    pre, replaced = [], []
+    for b in inputs:
+        try:
+            classify_broadcast(b.shape, iter_shape)
+            replaced.append(b)
+            continue
+        except UnsupportedOperationError as exc:
+            try:
+                view = torch.empty(b.shape, dtype=b.dtype, device="meta").expand(tuple(iter_shape))
+            except Exception:
+                raise exc from None
+        full = Buffer(name=f"{b.name}_expanded", scope=BufferScope.SHARED, dtype=b.dtype, shape=tuple(iter_shape),
+                      is_temporary=True)
+        pre.append(KernelLaunch(Template.COPY, f"{cluster.signature()}:expand", [b], [full], None, [full.shape],
+                                [full.dtype], cluster=cluster, view_strides=tuple(view.stride())))
+        replaced.append(full)
+    return pre, replaced
+
+
+def _lower_elementwise(cluster: FusionCluster):
     _require_shapes(cluster)
     outs = cluster.external_outputs
     if not outs or len(outs) > CDR_EW_MAX_OUTPUTS:
@@ -368,7 +393,9 @@ def _lower_elementwise(cluster: FusionCluster) -> KernelLaunch:
     for b in outs:
         if b.shape != iter_shape:
             raise UnsupportedOperationError(cluster.signature(), "outputs of different shapes")
+    pre, launch_inputs = _expand_general_broadcasts(cluster.external_inputs, iter_shape, cluster)
     builder = _ProgramBuilder(cluster.external_inputs, iter_shape)
+    builder.shape_override = {b: r.shape for b, r in zip(cluster.external_inputs, launch_inputs) if r is not b}
     for node in cluster._topological_sort():
         if node.outputs[0].shape != iter_shape:
             raise UnsupportedOperationError(cluster.signature(), "intermediate of a different shape")
@@ -378,8 +405,9 @@ def _lower_elementwise(cluster: FusionCluster) -> KernelLaunch:
         if r < len(builder.inputs):         # output is a pure alias of an input: materialise a copy
             out_regs[i] = builder._emit(EwOp.COPY, r, dtype=b.dtype)
     params = builder.build(out_regs)
-    return KernelLaunch(Template.ELEMENTWISE, cluster.signature(), list(cluster.external_inputs), list(outs),
-                        params, [b.shape for b in outs], [b.dtype for b in outs], cluster=cluster)
+    launch = KernelLaunch(Template.ELEMENTWISE, cluster.signature(), list(launch_inputs), list(outs),
+                          params, [b.shape for b in outs], [b.dtype for b in outs], cluster=cluster)
+    return pre + [launch] if pre else launch
 
 
 def _lower_reduction(cluster: FusionCluster) -> KernelLaunch:
@@ -391,7 +419,9 @@ def _lower_reduction(cluster: FusionCluster) -> KernelLaunch:
     red = red[0]
     last = _is_last_dim_reduction(red)
     if last is False:
-        raise UnsupportedOperationError(red.op_name, "only the last dimension (or all) can be reduced")
+        if len(order) != 1:
+            raise UnsupportedOperationError(red.op_name, "a fused chain in front of a reduction over inner dimensions")
+        return _lower_inner_reduction(cluster, red)
     full_shape = red.inputs[0].shape
     if not full_shape:
         raise UnsupportedOperationError(red.op_name, "rank-0 input")
@@ -410,6 +440,46 @@ def _lower_reduction(cluster: FusionCluster) -> KernelLaunch:
     template = Template.FULL_REDUCE if last is None else Template.ROW_REDUCE
     return KernelLaunch(template, cluster.signature(), list(cluster.external_inputs), [out], p, [out.shape],
                         [out.dtype], cluster=cluster, needs_workspace=template == Template.FULL_REDUCE)
+
+
+def _lower_inner_reduction(cluster: FusionCluster, red) -> list:
+    """sum / mean / amax / amin over dimensions other than the last: the reduced dimensions are moved
+    behind the kept ones with one strided copy (skipped when they already trail), the result is
+    seen as [kept, reduced] and goes through the row-reduce template."""
+    src, out = red.inputs[0], red.outputs[0]
+    rank = len(src.shape)
+    kw = red.metadata.get("kwargs", {})
+    consts = _const_args(red)
+    dim = kw.get("dim", consts[0] if consts else None)
+    dims = [dim] if isinstance(dim, int) else list(dim or [])
+    if not dims or not all(isinstance(d, int) and -rank <= d < rank for d in dims):
+        raise UnsupportedOperationError(red.op_name, f"dim={dim!r}")
+    dims = sorted({d % rank for d in dims})
+    if not is_float(out.dtype) or not is_float(src.dtype):
+        raise UnsupportedOperationError(red.op_name, f"{src.dtype} reduction")
+    keep = [d for d in range(rank) if d not in dims]
+    view = torch.empty(src.shape, dtype=src.dtype, device="meta").permute(keep + dims)
+    n_keep = math.prod(src.shape[d] for d in keep)
+    n_red = math.prod(src.shape[d] for d in dims)
+    if n_red == 0 or n_keep == 0:
+        raise UnsupportedOperationError(red.op_name, "empty reduction")
+    sig = cluster.signature()
+    launches, cur = [], src
+    if not view.is_contiguous():
+        moved = Buffer(name=f"{out.name}_moved", scope=BufferScope.SHARED, dtype=src.dtype, shape=tuple(view.shape),
+                       is_temporary=True)
+        launches.append(KernelLaunch(Template.COPY, f"{sig}:move", [src], [moved], None, [moved.shape], [moved.dtype],
+                                     cluster=cluster, view_strides=tuple(view.stride())))
+        cur = moved
+    flat = Buffer(name=f"{out.name}_rows", scope=BufferScope.SHARED, dtype=src.dtype, shape=(n_keep, n_red),
+                  is_temporary=True)
+    launches.append(KernelLaunch(0, f"{sig}:rows", [cur], [flat], None, [flat.shape], [flat.dtype], alias_of=cur,
+                                 cluster=cluster))
+    p = CdrReduceParams()
+    p.chain = _ProgramBuilder([flat], flat.shape).build([0])
+    p.reduce_op = get_op_desc(red.op_name).reduce_op
+    launches.append(KernelLaunch(Template.ROW_REDUCE, sig, [flat], [out], p, [out.shape], [out.dtype], cluster=cluster))
+    return launches
 
 
 def _const_args(node):

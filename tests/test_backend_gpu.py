@@ -285,6 +285,33 @@ def test_composite_activations_and_selections():
         assert_close(got.float(), want.float(), 2e-2, name + " bf16")
 
 
+def test_reductions_over_inner_dimensions():
+    """sum / mean / amax / amin over dimensions other than the last: reduced dimensions are moved to
+    the back by the strided copy, then one row reduction; amax / amin exact, sums within 1e-5.
+    Their results broadcast back along a middle or leading dimension, which the elementwise kernels
+    do not index directly: the operand is expanded by a stride-0 copy first (as is `expand`)."""
+    gen = torch.Generator().manual_seed(60)
+    x = torch.randn(6, 40, 72, generator=gen)
+    cases = {"sum0": lambda a: a.sum(0), "mean1_keepdim": lambda a: a.mean(1, keepdim=True), "amax01": lambda a: a.amax((0, 1)),
+             "amin_neg2": lambda a: a.amin(-2), "sum12": lambda a: a.sum((1, 2)), "chain_sum02": lambda a: (a * 2.0 + 1.0).sum((0, 2)),
+             "column_norm": lambda a: a / a.abs().sum(1, keepdim=True), "centre_over_batch": lambda a: a - a.mean(0),
+             "expand_first_column": lambda a: a[:, :1].expand(6, 40, 72) + a,
+             "broadcast_to": lambda a: torch.broadcast_to(a[:, :, :1], (6, 40, 72)) - a}
+    for name, fn in cases.items():
+        want = rp.run_reference(fn, [x])
+        got = compiled(fn)(x.to(DEV)).cpu()
+        assert got.shape == want.shape, name
+        if name.startswith("am"):
+            assert torch.equal(got, want), name
+        else:
+            assert_close(got, want, 1e-5, name)
+    xb = x.bfloat16()
+    want = rp.run_reference(cases["sum0"], [xb])
+    got = compiled(cases["sum0"])(xb.to(DEV)).cpu()
+    assert got.dtype == want.dtype
+    assert_close(got.float(), want.float(), 2e-2, "sum0 bf16")
+
+
 def test_basic_slicing_goes_through_the_strided_copy():
     """x[a:b], x[..., ::2], narrow, select: a view with an offset and strides, gathered by the
     strided-copy template; results are bit-identical to eager (no arithmetic on the copied part)."""

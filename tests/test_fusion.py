@@ -284,3 +284,25 @@ def test_composite_activations_stay_one_elementwise_launch():
     long = lambda a, b: (F.softplus(F.elu(F.hardswish(F.leaky_relu(a)))) + b).sum(-1)  # noqa: E731
     art = compile_with_dynamo(long, [x, y])
     assert [l.template for l in art.launches] == [Template.ELEMENTWISE, Template.ROW_REDUCE]
+
+
+def test_reduction_over_inner_dimensions_moves_them_to_the_back():
+    """x.sum(0) of [4, 8, 16]: one strided copy to [8, 16, 4] (strides 16, 1, 128), an alias to
+    [128, 4], one row reduction.  Trailing dimensions need no copy."""
+    art = compile_with_dynamo(lambda x: x.sum(0), [torch.randn(4, 8, 16)])
+    assert [l.template for l in art.launches] == [Template.COPY, 0, Template.ROW_REDUCE]
+    assert art.launches[0].view_strides == (16, 1, 128) and tuple(art.launches[1].out_shapes[0]) == (128, 4)
+    art = compile_with_dynamo(lambda x: x.amax((1, 2)), [torch.randn(4, 8, 16)])
+    assert [l.template for l in art.launches] == [0, Template.ROW_REDUCE]
+    assert tuple(art.launches[0].out_shapes[0]) == (4, 128)
+
+
+def test_general_broadcast_is_materialised_by_a_stride_zero_copy():
+    """[6, 1, 8] against [6, 4, 8] is neither a row, a column nor a scalar of the [rows, cols] view:
+    the operand is expanded by one COPY launch whose view has stride 0 on the broadcast dimension."""
+    art = compile_with_dynamo(lambda a, b: a * b, [torch.randn(6, 4, 8), torch.randn(6, 1, 8)])
+    assert [l.template for l in art.launches] == [Template.COPY, Template.ELEMENTWISE]
+    assert art.launches[0].view_strides == (8, 0, 1) and tuple(art.launches[0].out_shapes[0]) == (6, 4, 8)
+    assert list(art.launches[1].params.input_mode[:2]) == [IN_FULL, IN_FULL]
+    art = compile_with_dynamo(lambda a: a.expand(3, 4, 8) + 1.0, [torch.randn(4, 8)])
+    assert art.launches[0].template == Template.COPY and art.launches[0].view_strides == (0, 8, 1)
