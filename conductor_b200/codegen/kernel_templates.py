@@ -705,8 +705,141 @@ def _lower_layer_norm(cluster: FusionCluster) -> list:
     return [l1, l2, l3]
 
 
+def _row_statistic(cluster, tag, inputs, reduce_op, emit_chain):
+    """One ROW_REDUCE launch over inputs[0]'s rows into a fresh fp32 [.., 1] buffer; `emit_chain`
+    gets the program builder and returns the register to reduce."""
+    x = inputs[0]
+    stat_shape = tuple(x.shape[:-1]) + (1,)
+    out = Buffer(name=f"{cluster.nodes[0].outputs[0].name}_{tag}", scope=BufferScope.SHARED, dtype=torch.float32,
+                 shape=stat_shape, is_temporary=True)
+    b = _ProgramBuilder(inputs, x.shape)
+    p = CdrReduceParams()
+    p.chain = b.build([emit_chain(b)])
+    p.reduce_op = reduce_op
+    return out, KernelLaunch(Template.ROW_REDUCE, f"{cluster.signature()}:{tag}", list(inputs), [out], p, [stat_shape],
+                             [torch.float32], cluster=cluster)
+
+
+def _last_dim_only(node, x, pos=1):
+    kw = node.metadata.get("kwargs", {})
+    consts = _const_args(node)
+    dim = kw.get("dim", consts[pos - 1] if len(consts) >= pos else None)
+    if isinstance(dim, (list, tuple)) and len(dim) == 1:
+        dim = dim[0]
+    if not isinstance(dim, int) or dim % len(x.shape) != len(x.shape) - 1:
+        raise UnsupportedOperationError(node.op_name, f"dim={dim!r}; only the last dimension is supported")
+    return kw, consts
+
+
+def _lower_rms_norm(cluster: FusionCluster) -> list:
+    """rms_norm over the last dimension: mean(x^2) per row in fp32, then x * rsqrt(ms + eps) [* w]
+    with one rounding to the output dtype."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    kw = node.metadata.get("kwargs", {})
+    kws = node.metadata.get("kwarg_spec", {})
+    consts = _const_args(node)
+    x, out = node.inputs[spec[0][1]], node.outputs[0]
+    norm_shape = kw.get("normalized_shape", consts[0] if consts else None)
+    if norm_shape is None or tuple(norm_shape) != (x.shape[-1],) or not is_float(x.dtype):
+        raise UnsupportedOperationError("rms_norm", f"normalized_shape={norm_shape}; only the last dimension of a float tensor")
+    w = None
+    if "weight" in kws and kws["weight"][0] == "buf":
+        w = node.inputs[kws["weight"][1]]
+    elif len(spec) > 2 and spec[2][0] == "buf":
+        w = node.inputs[spec[2][1]]
+    eps = kw.get("eps", next((c for c in consts[1:] if isinstance(c, float)), None))
+    if eps is None:
+        eps = torch.finfo(x.dtype).eps
+    f32 = torch.float32
+    ms, l1 = _row_statistic(cluster, "meansq", [x], ReduceOp.MEAN, lambda b: b._emit(EwOp.MUL, 0, 0, dtype=f32))
+    ins = [x, ms] + ([w] if w is not None else [])
+    b2 = _ProgramBuilder(ins, x.shape)
+    r = b2._emit(EwOp.RSQRT, b2._emit(EwOp.ADD_IMM, 1, imm=eps, dtype=f32), dtype=f32)
+    y = b2._emit(EwOp.MUL, 0, r, dtype=f32 if w is not None else out.dtype)
+    if w is not None:
+        y = b2._emit(EwOp.MUL, y, 2, dtype=out.dtype)
+    l2 = KernelLaunch(Template.ELEMENTWISE, f"{cluster.signature()}:normalize", ins, [out], b2.build([y]), [out.shape],
+                      [out.dtype], cluster=cluster)
+    return [l1, l2]
+
+
+def _lower_log_softmax(cluster: FusionCluster) -> list:
+    """log_softmax / logsumexp over the last dimension in the stable form: row maximum m, then
+    s = sum(exp(x - m)), then x - m - log(s) (or m + log(s)); statistics in fp32."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    x, out = node.inputs[spec[0][1]], node.outputs[0]
+    if not is_float(x.dtype) or not x.shape:
+        raise UnsupportedOperationError(node.op_name, f"{x.dtype} input")
+    _last_dim_only(node, x)
+    f32 = torch.float32
+    m, l1 = _row_statistic(cluster, "max", [x], ReduceOp.MAX, lambda b: 0)
+    ssum, l2 = _row_statistic(cluster, "sumexp", [x, m], ReduceOp.SUM,
+                              lambda b: b._emit(EwOp.EXP, b._emit(EwOp.SUB, 0, 1, dtype=f32), dtype=f32))
+    if node.op_name == "logsumexp":
+        b3 = _ProgramBuilder([m, ssum], m.shape)
+        y = b3._emit(EwOp.ADD, 0, b3._emit(EwOp.LOG, 1, dtype=f32), dtype=out.dtype)
+        ins = [m, ssum]
+    else:
+        b3 = _ProgramBuilder([x, m, ssum], x.shape)
+        y = b3._emit(EwOp.SUB, b3._emit(EwOp.SUB, 0, 1, dtype=f32), b3._emit(EwOp.LOG, 2, dtype=f32), dtype=out.dtype)
+        ins = [x, m, ssum]
+    l3 = KernelLaunch(Template.ELEMENTWISE, f"{cluster.signature()}:finish", ins, [out], b3.build([y]), [out.shape],
+                      [out.dtype], cluster=cluster)
+    return [l1, l2, l3]
+
+
+def _lower_variance(cluster: FusionCluster) -> list:
+    """var / std over the last dimension, two-pass: row mean, then the mean of squared deviations
+    scaled by n / (n - correction) (and its square root for std)."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    x, out = node.inputs[spec[0][1]], node.outputs[0]
+    if not is_float(x.dtype) or not x.shape:
+        raise UnsupportedOperationError(node.op_name, f"{x.dtype} input")
+    kw, consts = _last_dim_only(node, x)
+    correction = kw.get("correction", None)
+    if correction is None:
+        unbiased = kw.get("unbiased", next((c for c in consts[1:] if isinstance(c, bool)), True))
+        correction = 1 if unbiased else 0
+    n = x.shape[-1]
+    if n - correction <= 0:
+        raise UnsupportedOperationError(node.op_name, "rows too short for the correction")
+    f32 = torch.float32
+    mean, l1 = _row_statistic(cluster, "mean", [x], ReduceOp.MEAN, lambda b: 0)
+
+    def sq_dev(b):
+        d = b._emit(EwOp.SUB, 0, 1, dtype=f32)
+        return b._emit(EwOp.MUL, d, d, dtype=f32)
+
+    ssq, l2 = _row_statistic(cluster, "sumsq", [x, mean], ReduceOp.SUM, sq_dev)
+    b3 = _ProgramBuilder([ssq], ssq.shape)
+    is_std = node.op_name == "std"
+    y = b3._emit(EwOp.MUL_IMM, 0, imm=1.0 / (n - correction), dtype=f32 if is_std else out.dtype)
+    if is_std:
+        y = b3._emit(EwOp.SQRT, y, dtype=out.dtype)
+    l3 = KernelLaunch(Template.ELEMENTWISE, f"{cluster.signature()}:finish", [ssq], [out], b3.build([y]), [out.shape],
+                      [out.dtype], cluster=cluster)
+    return [l1, l2, l3]
+
+
+def _lower_norm(cluster: FusionCluster) -> list:
+    name = cluster.nodes[0].op_name
+    if name == "rms_norm":
+        return _lower_rms_norm(cluster)
+    if name in ("log_softmax", "logsumexp"):
+        return _lower_log_softmax(cluster)
+    if name in ("var", "std"):
+        return _lower_variance(cluster)
+    return _lower_layer_norm(cluster)
+
+
 _LOWERING = {
-    FusionType.NORM: _lower_layer_norm,
+    FusionType.NORM: _lower_norm,
     FusionType.ELEMENTWISE: _lower_elementwise,
     FusionType.REDUCTION: _lower_reduction,
     FusionType.SOFTMAX: _lower_softmax,

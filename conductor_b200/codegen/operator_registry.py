@@ -149,6 +149,9 @@ class OperatorRegistry:
         r(OperatorInfo("_softmax_backward_data", "softmax_backward", OpType.SOFTMAX, False, 2,
                        template=Template.SOFTMAX_BWD, preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("layer_norm", "layer_norm", OpType.NORM, False, 3, preferred_fusion_level=FusionLevel.GLOBAL))
+        # row statistics lowered to several launches of the reduce and elementwise templates
+        for name, arity in (("rms_norm", 2), ("log_softmax", 1), ("logsumexp", 1), ("var", 1), ("std", 1)):
+            r(OperatorInfo(name, name, OpType.NORM, False, arity, preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("linear", "linear", OpType.MATRIX, True, 3, template=Template.GEMM_EPILOGUE,
                        preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("matmul", "matmul", OpType.MATRIX, False, 2, template=Template.GEMM_EPILOGUE,

@@ -312,6 +312,33 @@ def test_reductions_over_inner_dimensions():
     assert_close(got.float(), want.float(), 2e-2, "sum0 bf16")
 
 
+def test_row_statistics_lowered_to_several_launches():
+    """rms_norm, log_softmax, logsumexp, var, std over the last dimension: row reductions with fp32
+    statistics and a finishing elementwise launch; 1e-5 in fp32, 2e-2 in bf16."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(61)
+    x = 3.0 * torch.randn(96, 200, generator=gen) + 1.0
+    x[0] += 80.0                                   # a row where the unshifted exp would overflow
+    w = torch.rand(200, generator=gen) + 0.5
+    cases = {"rms_norm_w": (lambda a, g: F.rms_norm(a, (200,), g, 1e-6), [x, w]), "rms_norm": (lambda a: F.rms_norm(a, (200,)), [x]),
+             "log_softmax": (lambda a: F.log_softmax(a, -1), [x]), "logsumexp": (lambda a: torch.logsumexp(a, -1), [x]),
+             "logsumexp_keepdim": (lambda a: a.logsumexp(1, keepdim=True), [x]), "var": (lambda a: a.var(-1), [x]),
+             "std_keepdim": (lambda a: a.std(-1, keepdim=True), [x]), "var_biased": (lambda a: torch.var(a, dim=-1, correction=0), [x]),
+             "nll_of_log_softmax": (lambda a: -(F.log_softmax(a * 0.5, -1) * torch.softmax(a, -1)).sum(-1), [x])}
+    for name, (fn, inputs) in cases.items():
+        want = rp.run_reference(fn, inputs)
+        got = compiled(fn)(*[t.to(DEV) for t in inputs]).cpu()
+        assert got.shape == want.shape and got.dtype == want.dtype, name
+        assert_close(got, want, 1e-5, name)
+    for name in ("rms_norm_w", "log_softmax", "var"):
+        fn, inputs = cases[name]
+        inputs = [t.bfloat16() for t in inputs]
+        want = rp.run_reference(fn, inputs)
+        got = compiled(fn)(*[t.to(DEV) for t in inputs]).cpu()
+        assert got.dtype == torch.bfloat16
+        assert_close(got.float(), want.float(), 2e-2, name + " bf16")
+
+
 def test_basic_slicing_goes_through_the_strided_copy():
     """x[a:b], x[..., ::2], narrow, select: a view with an offset and strides, gathered by the
     strided-copy template; results are bit-identical to eager (no arithmetic on the copied part)."""

@@ -306,3 +306,21 @@ def test_general_broadcast_is_materialised_by_a_stride_zero_copy():
     assert list(art.launches[1].params.input_mode[:2]) == [IN_FULL, IN_FULL]
     art = compile_with_dynamo(lambda a: a.expand(3, 4, 8) + 1.0, [torch.randn(4, 8)])
     assert art.launches[0].template == Template.COPY and art.launches[0].view_strides == (0, 8, 1)
+
+
+def test_row_statistics_lower_to_reduce_and_elementwise_launches():
+    """rms_norm: mean of squares then the normalising chain; log_softmax / logsumexp: row maximum,
+    shifted exp-sum, finish; var / std: two-pass.  Only the last dimension."""
+    F = torch.nn.functional
+    x, w = torch.randn(8, 16), torch.randn(16)
+    art = compile_with_dynamo(lambda a, g: F.rms_norm(a, (16,), g, 1e-6), [x, w])
+    assert [l.template for l in art.launches] == [Template.ROW_REDUCE, Template.ELEMENTWISE]
+    assert art.launches[0].params.reduce_op == ReduceOp.MEAN
+    art = compile_with_dynamo(lambda a: F.log_softmax(a, -1), [x])
+    assert [l.template for l in art.launches] == [Template.ROW_REDUCE, Template.ROW_REDUCE, Template.ELEMENTWISE]
+    assert [l.params.reduce_op for l in art.launches[:2]] == [ReduceOp.MAX, ReduceOp.SUM]
+    art = compile_with_dynamo(lambda a: a.std(-1), [x])
+    ops = [i.op for i in art.launches[2].params.instr[: art.launches[2].params.n_instr]]
+    assert ops == [EwOp.MUL_IMM, EwOp.SQRT] and abs(art.launches[2].params.instr[0].imm - 1.0 / 15.0) < 1e-7
+    with pytest.raises(Exception):
+        compile_with_dynamo(lambda a: F.log_softmax(a, 0), [x])
