@@ -501,12 +501,28 @@ def _lower_softmax(cluster: FusionCluster) -> KernelLaunch:
         x = node.inputs[0]
         dim = kw.get("dim", consts[0] if consts else None)
         dtype = kw.get("dtype", consts[2] if len(consts) > 2 else None)
-        if dim is None or (dim % len(x.shape)) != len(x.shape) - 1:
-            raise UnsupportedOperationError("softmax", f"dim={dim}; only the last dimension is supported")
+        if not isinstance(dim, int) or not x.shape:
+            raise UnsupportedOperationError("softmax", f"dim={dim!r}")
         if dtype is not None and dtype != x.dtype:
             raise UnsupportedOperationError("softmax", "dtype conversion inside softmax")
         if kw.get("_half_to_float", consts[1] if len(consts) > 1 and isinstance(consts[1], bool) else False):
             raise UnsupportedOperationError("softmax", "half_to_float")
+        d, rank = dim % len(x.shape), len(x.shape)
+        if d != rank - 1:
+            # softmax over an inner dimension: swap it with the last one by a strided copy, run the
+            # row kernel, swap back
+            sig = cluster.signature()
+            fwd = torch.empty(x.shape, dtype=x.dtype, device="meta").transpose(d, -1)
+            moved = Buffer(name=f"{out.name}_moved", scope=BufferScope.SHARED, dtype=x.dtype, shape=tuple(fwd.shape),
+                           is_temporary=True)
+            rows = Buffer(name=f"{out.name}_rows", scope=BufferScope.SHARED, dtype=x.dtype, shape=tuple(fwd.shape),
+                          is_temporary=True)
+            back = torch.empty(fwd.shape, dtype=x.dtype, device="meta").transpose(d, -1)
+            return [KernelLaunch(Template.COPY, f"{sig}:move", [x], [moved], None, [moved.shape], [x.dtype],
+                                 cluster=cluster, view_strides=tuple(fwd.stride())),
+                    KernelLaunch(Template.SOFTMAX_FWD, sig, [moved], [rows], None, [rows.shape], [x.dtype], cluster=cluster),
+                    KernelLaunch(Template.COPY, f"{sig}:restore", [rows], [out], None, [out.shape], [out.dtype],
+                                 cluster=cluster, view_strides=tuple(back.stride()))]
         return KernelLaunch(Template.SOFTMAX_FWD, cluster.signature(), [x], [out], None, [out.shape], [out.dtype],
                             cluster=cluster)
     if node.op_name == "_softmax_backward_data":
@@ -547,6 +563,15 @@ def _lower_gemm(cluster: FusionCluster) -> KernelLaunch:
         x, w = bufs
         if len(w.shape) != 2 or len(x.shape) < 2 or x.shape[-1] != w.shape[0]:
             raise UnsupportedOperationError(node.op_name, f"shapes {x.shape} x {w.shape}: the right operand must be 2-D")
+        layout = W_KN
+    elif node.op_name == "addmm":                             # addmm(bias[N], x[M,K], W[K,N]) = bias + x @ W
+        kw = node.metadata.get("kwargs", {})
+        if len(ops) != 3 or len(spec) != 3 or kw.get("beta", 1) != 1 or kw.get("alpha", 1) != 1:
+            raise UnsupportedOperationError("addmm", "expected (bias, x, weight) with beta = alpha = 1")
+        bias, x, w = (node.inputs[s[1]] for s in ops)
+        if len(w.shape) != 2 or len(x.shape) != 2 or x.shape[-1] != w.shape[0] or _strip_ones(bias.shape) != (w.shape[1],):
+            raise UnsupportedOperationError("addmm", f"shapes {bias.shape} + {x.shape} x {w.shape}: the addend must be one row")
+        bufs = [x, w, bias]
         layout = W_KN
     else:
         raise UnsupportedOperationError(node.op_name, "no GEMM lowering")

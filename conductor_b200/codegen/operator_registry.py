@@ -156,6 +156,8 @@ class OperatorRegistry:
                        preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("matmul", "matmul", OpType.MATRIX, False, 2, template=Template.GEMM_EPILOGUE,
                        preferred_fusion_level=FusionLevel.GLOBAL), "mm", "bmm")
+        r(OperatorInfo("addmm", "addmm", OpType.MATRIX, False, 3, template=Template.GEMM_EPILOGUE,
+                       preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("scaled_dot_product_attention", "attention", OpType.ATTENTION, False, 3,
                        template=Template.ATTENTION, preferred_fusion_level=FusionLevel.GLOBAL), "attention")
         # metadata-only reshapes of contiguous tensors: no kernel

@@ -339,6 +339,18 @@ def test_row_statistics_lowered_to_several_launches():
         assert_close(got.float(), want.float(), 2e-2, name + " bf16")
 
 
+def test_softmax_over_an_inner_dimension():
+    """softmax over a dimension other than the last: transposing copy, row kernel, transposing copy."""
+    gen = torch.Generator().manual_seed(62)
+    x = 2.0 * torch.randn(5, 48, 72, generator=gen)
+    for name, fn in {"dim1": lambda a: torch.softmax(a, 1), "dim0_scaled": lambda a: torch.softmax(a, 0) * 2.0,
+                     "neg2": lambda a: a.softmax(-2)}.items():
+        want = rp.run_reference(fn, [x])
+        got = compiled(fn)(x.to(DEV)).cpu()
+        assert got.shape == want.shape, name
+        assert_close(got, want, 1e-5, name)
+
+
 def test_basic_slicing_goes_through_the_strided_copy():
     """x[a:b], x[..., ::2], narrow, select: a view with an offset and strides, gathered by the
     strided-copy template; results are bit-identical to eager (no arithmetic on the copied part)."""
@@ -478,6 +490,10 @@ def test_matmul_operator_forms():
     x2 = x[0].contiguous()
     assert_close(compiled(lambda a, b: torch.mm(a, b))(x2.to(DEV), w.to(DEV)).float(),
                  rp.run_reference(lambda a, b: torch.mm(a, b), [x2, w]).float(), 2e-2, "mm")
+    bias = (0.5 * torch.randn(384, generator=gen)).bfloat16()
+    addmm = lambda c, a, b: torch.relu(torch.addmm(c, a, b))  # noqa: E731  bias row + x @ W in the GEMM's epilogue
+    assert_close(compiled(addmm)(bias.to(DEV), x2.to(DEV), w.to(DEV)).float(),
+                 rp.run_reference(addmm, [bias, x2, w]).float(), 2e-2, "addmm")
 
 
 def test_integer_graph_is_bit_exact():

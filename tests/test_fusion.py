@@ -91,8 +91,8 @@ def test_c3_softmax_forward_and_backward():
     assert [b.name for b in k.inputs] == ["l_grad_", "l_y_"]
 
 
-def test_softmax_over_other_dim_is_refused():
-    assert_unsupported(lambda x: torch.softmax(x, 0), [torch.randn(4, 8)])
+def test_softmax_with_a_dtype_change_is_refused():
+    assert_unsupported(lambda x: torch.softmax(x, -1, dtype=torch.float32), [torch.randn(4, 8).bfloat16()])
 
 
 def test_c4_mlp_two_gemm_epilogue_clusters():
@@ -324,3 +324,20 @@ def test_row_statistics_lower_to_reduce_and_elementwise_launches():
     assert ops == [EwOp.MUL_IMM, EwOp.SQRT] and abs(art.launches[2].params.instr[0].imm - 1.0 / 15.0) < 1e-7
     with pytest.raises(Exception):
         compile_with_dynamo(lambda a: F.log_softmax(a, 0), [x])
+
+
+def test_addmm_lowers_to_the_gemm_template_with_a_bias_row():
+    b, x, w = torch.randn(48).bfloat16(), torch.randn(64, 32).bfloat16(), torch.randn(32, 48).bfloat16()
+    art = compile_with_dynamo(lambda c, a, m: torch.addmm(c, a, m), [b, x, w])
+    (launch,) = art.launches
+    assert launch.template == Template.GEMM_EPILOGUE and launch.params.has_bias == 1 and launch.params.weight_layout == 1
+    assert [t.name for t in launch.inputs] == ["l_a_", "l_m_", "l_c_"]
+    with pytest.raises(Exception):            # a full [M, N] addend is not an epilogue bias
+        compile_with_dynamo(lambda c, a, m: torch.addmm(c, a, m), [torch.randn(64, 48).bfloat16(), x, w])
+
+
+def test_softmax_over_an_inner_dimension_is_bracketed_by_transposing_copies():
+    art = compile_with_dynamo(lambda a: torch.softmax(a, 1), [torch.randn(4, 8, 16)])
+    assert [l.template for l in art.launches] == [Template.COPY, Template.SOFTMAX_FWD, Template.COPY]
+    assert art.launches[0].view_strides == (128, 1, 16) and tuple(art.launches[1].out_shapes[0]) == (4, 16, 8)
+    assert art.launches[2].view_strides == (128, 1, 8) and tuple(art.launches[2].out_shapes[0]) == (4, 8, 16)
