@@ -87,6 +87,7 @@ class KernelLaunch:
     needs_workspace: bool = False
     view_strides: Optional[tuple] = None  # COPY launches: element strides of the view of inputs[0] that is gathered
     view_offset: int = 0                  # COPY launches: first element of that view, relative to inputs[0]'s own
+    out_view: Optional[tuple] = None      # COPY launches that fill one part of outputs[0] (cat): (shape, strides, offset)
 
     def describe(self) -> str:
         ins = ", ".join(b.name for b in self.inputs)
@@ -614,9 +615,44 @@ def _lower_attention(cluster: FusionCluster) -> KernelLaunch:
                         cluster=cluster, needs_workspace=True)
 
 
-def _lower_shape(cluster: FusionCluster) -> KernelLaunch:
+def _lower_cat(cluster: FusionCluster) -> list:
+    """cat / concat: one strided copy per part, each writing its slice of the result."""
     node = cluster.nodes[0]
     out = node.outputs[0]
+    spec = node.metadata.get("arg_spec", [])
+    kw = node.metadata.get("kwargs", {})
+    if not spec or spec[0][0] != "seq" or any(s[0] != "buf" for s in spec[0][1]):
+        raise UnsupportedOperationError(node.op_name, "expected a sequence of tensors")
+    parts = [node.inputs[s[1]] for s in spec[0][1]]
+    consts = _const_args(node)
+    dim = kw.get("dim", consts[0] if consts else 0)
+    rank = len(out.shape)
+    if not isinstance(dim, int) or any(p.shape is None or len(p.shape) != rank or p.dtype != out.dtype for p in parts):
+        raise UnsupportedOperationError(node.op_name, "parts must share rank and dtype")
+    dim %= rank
+    full = torch.empty(out.shape, dtype=out.dtype, device="meta")
+    launches, start = [], 0
+    for i, part in enumerate(parts):
+        n = part.shape[dim]
+        if n == 0:
+            continue
+        view = full.narrow(dim, start, n)
+        if tuple(view.shape) != tuple(part.shape):
+            raise UnsupportedOperationError(node.op_name, f"part {i} has shape {part.shape}")
+        launches.append(KernelLaunch(Template.COPY, f"{cluster.signature()}:part{i}", [part], [out], None, [out.shape],
+                                     [out.dtype], cluster=cluster,
+                                     out_view=(tuple(view.shape), tuple(view.stride()), int(view.storage_offset()))))
+        start += n
+    if start != out.shape[dim] or not launches:
+        raise UnsupportedOperationError(node.op_name, "parts do not cover the result")
+    return launches
+
+
+def _lower_shape(cluster: FusionCluster):
+    node = cluster.nodes[0]
+    out = node.outputs[0]
+    if node.op_name in ("cat", "concat", "concatenate"):
+        return _lower_cat(cluster)
     if out.shape is None or not node.inputs:
         raise UnsupportedOperationError(node.op_name, "unknown output shape")
     src = node.inputs[0]

@@ -166,6 +166,7 @@ class OperatorRegistry:
             r(OperatorInfo(perm_op, "permute", OpType.SHAPE, False, 1))
         for slice_op in ("getitem", "__getitem__", "narrow", "select", "view_of", "expand", "broadcast_to"):
             r(OperatorInfo(slice_op, "slice", OpType.SHAPE, False, 1))
+        r(OperatorInfo("cat", "cat", OpType.SHAPE, False, 2), "concat", "concatenate")
         for shape_op in ("view", "reshape", "flatten", "unsqueeze", "squeeze", "contiguous", "detach", "clone_view"):
             r(OperatorInfo(shape_op, shape_op, OpType.SHAPE, False, 1, requires_device_kernel=False))
 

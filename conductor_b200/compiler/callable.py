@@ -190,6 +190,15 @@ class Callable:
                 src = ins[0]
                 ins = [torch.as_strided(src, launch.out_shapes[0], launch.view_strides, src.storage_offset() + launch.view_offset)]
             outs = None
+            if launch.out_view is not None:                # cat: this launch fills one slice of the result
+                if rows is not None:
+                    raise ExecutionError("a plan with a concatenation cannot run on a block of its rows", kernel_name=launch.name)
+                whole = env.get(launch.outputs[0])
+                if whole is None:
+                    whole = env[launch.outputs[0]] = torch.empty(launch.out_shapes[0], dtype=launch.out_dtypes[0], device=device)
+                shape, strides, offset = launch.out_view
+                ex.execute(launch, ins, [torch.as_strided(whole, shape, strides, whole.storage_offset() + offset)])
+                continue
             if rows is not None:
                 outs = [torch.empty(self._shard_shape(sh, rows), dtype=dt, device=device)
                         for sh, dt in zip(launch.out_shapes, launch.out_dtypes)]

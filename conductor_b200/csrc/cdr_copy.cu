@@ -1,10 +1,13 @@
-// K7 -- strided gather into a contiguous tensor: the materialising form of transpose / permute /
-// .contiguous() on a view.
+// K7 -- strided copy: the materialising form of transpose / permute / slicing / expand /
+// .contiguous() on a view, and (with a strided output) the scatter of one part into a
+// concatenation.
 //
 // The reference forces every kernel operand contiguous on the host before a call
 // (conductor/compiler/host_wrapper.py:380-392, `tensor.contiguous()`); here the copy is a template
 // of its own so that a permuted view never has to leave the device path.  The input descriptor
-// carries the view's shape and element strides, the output is contiguous with the same shape.
+// carries the view's shape and element strides; the output has the same shape and is normally
+// contiguous, but may itself be a strided view (non-overlapping; the caller's responsibility) --
+// `cat` writes each part into its slice of the result that way.
 // HBM-bound.  When the view's innermost dimension is contiguous in memory and a whole number of
 // 16-byte vectors (the head-dimension case: [B, S, H, D] -> [B, H, S, D]), every thread moves one
 // 16-byte vector with streaming accesses; otherwise elements are gathered one by one (reads
@@ -22,29 +25,32 @@ struct CopyArgs {
   int32_t unit_bytes;           // 16 on the vector path, the element size otherwise
   int64_t shape[CDR_MAX_RANK];  // output shape in units (innermost dimension divided on the vector path)
   int64_t stride[CDR_MAX_RANK]; // input strides in bytes
+  int64_t ostride[CDR_MAX_RANK];// output strides in bytes
 };
 
 template <int UNIT>
 __global__ void __launch_bounds__(256) strided_copy_kernel(const __grid_constant__ CopyArgs a) {
   const int64_t step = static_cast<int64_t>(gridDim.x) * 256;
   for (int64_t u = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; u < a.n_units; u += step) {
-    int64_t rest = u, off = 0;
+    int64_t rest = u, off = 0, ooff = 0;
 #pragma unroll 1
     for (int d = a.rank - 1; d >= 0; --d) {
       const int64_t q = rest / a.shape[d];
-      off += (rest - q * a.shape[d]) * a.stride[d];
+      const int64_t r = rest - q * a.shape[d];
+      off += r * a.stride[d];
+      ooff += r * a.ostride[d];
       rest = q;
     }
     if (UNIT == 16) {
-      st_stream16(a.out + u * 16, ld_stream16(a.in + off));
+      st_stream16(a.out + ooff, ld_stream16(a.in + off));
     } else if (UNIT == 8) {
-      *reinterpret_cast<uint64_t*>(a.out + u * 8) = *reinterpret_cast<const uint64_t*>(a.in + off);
+      *reinterpret_cast<uint64_t*>(a.out + ooff) = *reinterpret_cast<const uint64_t*>(a.in + off);
     } else if (UNIT == 4) {
-      *reinterpret_cast<uint32_t*>(a.out + u * 4) = *reinterpret_cast<const uint32_t*>(a.in + off);
+      *reinterpret_cast<uint32_t*>(a.out + ooff) = *reinterpret_cast<const uint32_t*>(a.in + off);
     } else if (UNIT == 2) {
-      *reinterpret_cast<uint16_t*>(a.out + u * 2) = *reinterpret_cast<const uint16_t*>(a.in + off);
+      *reinterpret_cast<uint16_t*>(a.out + ooff) = *reinterpret_cast<const uint16_t*>(a.in + off);
     } else {
-      a.out[u] = a.in[off];
+      a.out[ooff] = a.in[off];
     }
   }
 }
@@ -58,31 +64,38 @@ int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs,
   if (x.rank != out.rank || x.dtype != out.dtype) { set_error("copy: input and output differ in rank or dtype"); return CDR_ERR_BAD_ARG; }
   for (int d = 0; d < x.rank; ++d)
     if (x.shape[d] != out.shape[d]) { set_error("copy: input and output differ in shape"); return CDR_ERR_BAD_ARG; }
-  if (!is_contiguous(out)) { set_error("copy: the output must be contiguous"); return CDR_ERR_BAD_ARG; }
   const int64_t n = numel(out);
   if (n == 0) return CDR_OK;
   if (!x.data || !out.data) { set_error("copy: null pointer"); return CDR_ERR_BAD_ARG; }
   const int esz = dtype_size(x.dtype);
   if (esz <= 0) { set_error("copy: dtype %d unsupported", x.dtype); return CDR_ERR_UNSUPPORTED; }
-  for (int d = 0; d < x.rank; ++d)
-    if (x.stride[d] < 0) { set_error("copy: negative strides are not supported"); return CDR_ERR_UNSUPPORTED; }
+  for (int d = 0; d < x.rank; ++d) {
+    if (x.stride[d] < 0 || out.stride[d] < 0) { set_error("copy: negative strides are not supported"); return CDR_ERR_UNSUPPORTED; }
+    if (out.stride[d] == 0 && out.shape[d] > 1) { set_error("copy: the output view overlaps itself (stride 0)"); return CDR_ERR_BAD_ARG; }
+  }
 
   CopyArgs a{};
   a.in = static_cast<const unsigned char*>(x.data);
   a.out = static_cast<unsigned char*>(out.data);
   a.rank = x.rank;
-  for (int d = 0; d < x.rank; ++d) { a.shape[d] = x.shape[d]; a.stride[d] = x.stride[d] * esz; }
-  if (a.rank == 0) { a.rank = 1; a.shape[0] = 1; a.stride[0] = 0; }
-  // vector path: innermost dimension contiguous, a whole number of 16-byte vectors, every other
-  // stride and both base pointers 16-byte aligned
+  for (int d = 0; d < x.rank; ++d) {
+    a.shape[d] = x.shape[d];
+    a.stride[d] = x.stride[d] * esz;
+    a.ostride[d] = out.stride[d] * esz;
+  }
+  if (a.rank == 0) { a.rank = 1; a.shape[0] = 1; a.stride[0] = 0; a.ostride[0] = 0; }
+  // vector path: innermost dimension contiguous on both sides, a whole number of 16-byte vectors,
+  // every other stride and both base pointers 16-byte aligned
   const int last = a.rank - 1;
   const int per_vec = 16 / esz;
-  bool vec = x.rank > 0 && x.stride[last] == 1 && x.shape[last] % per_vec == 0 && aligned16(x.data) && aligned16(out.data);
-  for (int d = 0; d < last; ++d) vec &= (a.stride[d] % 16) == 0;
+  bool vec = x.rank > 0 && x.stride[last] == 1 && out.stride[last] == 1 && x.shape[last] % per_vec == 0 &&
+             aligned16(x.data) && aligned16(out.data);
+  for (int d = 0; d < last; ++d) vec &= a.shape[d] == 1 || ((a.stride[d] % 16) == 0 && (a.ostride[d] % 16) == 0);
   if (vec) {
     a.unit_bytes = 16;
     a.shape[last] = x.shape[last] / per_vec;
     a.stride[last] = 16;
+    a.ostride[last] = 16;
     a.n_units = n / per_vec;
   } else {
     a.unit_bytes = esz;

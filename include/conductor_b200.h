@@ -94,9 +94,10 @@ enum cdr_template {
                              params = cdr_reduce_params; needs workspace                 */
   CDR_T_LAYER_NORM = 8,   /* layer normalisation over the last dim, inputs (x[, weight][, bias]),
                              params = cdr_norm_params                                    */
-  CDR_T_COPY = 9          /* gather a strided view (the input descriptor's strides are honoured) into a
-                             contiguous output of the same shape: transpose / permute / contiguous();
-                             no params                                                    */
+  CDR_T_COPY = 9          /* copy a strided view (the input descriptor's strides are honoured; stride 0
+                             broadcasts) into an output of the same shape: transpose / permute / slice /
+                             expand / contiguous().  The output's strides are honoured too (positive,
+                             non-overlapping), which writes one part of a concatenation; no params */
 };
 
 /* ---- elementwise programs -------------------------------------------------

@@ -351,6 +351,26 @@ def test_softmax_over_an_inner_dimension():
         assert_close(got, want, 1e-5, name)
 
 
+def test_concatenation_writes_parts_into_slices_of_the_result():
+    """torch.cat: one strided copy per part into its slice of the result; exact.  The rotate-half
+    form used by rotary embeddings (cat of a negated half and the other half) compiles with it."""
+    gen = torch.Generator().manual_seed(63)
+    a = torch.randn(4, 24, 64, generator=gen)
+    b = torch.randn(4, 24, 64, generator=gen)
+    cos = torch.cos(torch.randn(24, 64, generator=gen))
+    cases = {"last": lambda p, q: torch.cat([p, q], -1) * 2.0, "middle_ragged": lambda p, q: torch.cat((p, q[:, :5], p[:, 3:4]), dim=1),
+             "first": lambda p, q: torch.cat([p, q, p], 0), "odd_columns": lambda p, q: torch.cat([p[..., :3], q[..., 3:]], -1) + 1.0}
+    for name, fn in cases.items():
+        want = rp.run_reference(fn, [a, b])
+        got = compiled(fn)(a.to(DEV), b.to(DEV)).cpu()
+        assert got.shape == want.shape and torch.equal(got, want), name
+    rope = lambda p, c: p * c + torch.cat([-p[..., 32:], p[..., :32]], -1) * (1.0 - c)  # noqa: E731
+    assert_close(compiled(rope)(a.to(DEV), cos.to(DEV)).cpu(), rp.run_reference(rope, [a, cos]), 1e-5, "rotate half")
+    ab = a.bfloat16()
+    fn = cases["last"]
+    assert torch.equal(compiled(fn)(ab.to(DEV), ab.to(DEV)).cpu(), rp.run_reference(fn, [ab, ab]))
+
+
 def test_basic_slicing_goes_through_the_strided_copy():
     """x[a:b], x[..., ::2], narrow, select: a view with an offset and strides, gathered by the
     strided-copy template; results are bit-identical to eager (no arithmetic on the copied part)."""

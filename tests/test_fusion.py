@@ -341,3 +341,12 @@ def test_softmax_over_an_inner_dimension_is_bracketed_by_transposing_copies():
     assert [l.template for l in art.launches] == [Template.COPY, Template.SOFTMAX_FWD, Template.COPY]
     assert art.launches[0].view_strides == (128, 1, 16) and tuple(art.launches[1].out_shapes[0]) == (4, 16, 8)
     assert art.launches[2].view_strides == (128, 1, 8) and tuple(art.launches[2].out_shapes[0]) == (4, 8, 16)
+
+
+def test_cat_lowers_to_one_copy_per_part_into_the_result():
+    x, y = torch.randn(4, 8, 16), torch.randn(4, 2, 16)
+    art = compile_with_dynamo(lambda a, b: torch.cat((a, b), dim=1), [x, y])
+    assert [l.template for l in art.launches] == [Template.COPY, Template.COPY]
+    assert art.launches[0].outputs[0] is art.launches[1].outputs[0]
+    assert [l.out_view for l in art.launches] == [((4, 8, 16), (160, 16, 1), 0), ((4, 2, 16), (160, 16, 1), 128)]
+    assert tuple(art.launches[0].out_shapes[0]) == (4, 10, 16)

@@ -477,6 +477,19 @@ def test_strided_copy_template(executor):
         assert torch.equal(out, v), (tuple(v.shape), v.stride(), v.dtype)
     out = torch.empty(5, 4, device=DEV)
     assert abi.launch(Template.COPY, [y[:4, :5]], [out], check=False) == -1          # shapes differ
+    # a strided output view: parts written into slices of one result (concatenation), vector and
+    # scalar paths, neighbours untouched
+    whole = torch.full((2, 24, 4, 96), -7.0, device=DEV).bfloat16()
+    abi.launch(Template.COPY, [x], [whole[..., 16:80]])
+    assert torch.equal(whole[..., 16:80], x) and bool((whole[..., :16] == -7).all()) and bool((whole[..., 80:] == -7).all())
+    wide = torch.zeros(37, 60, device=DEV)
+    abi.launch(Template.COPY, [y], [wide[:, 3:56]])
+    assert torch.equal(wide[:, 3:56], y) and bool((wide[:, :3] == 0).all()) and bool((wide[:, 56:] == 0).all())
+    square = torch.zeros(9, 9, device=DEV)
+    abi.launch(Template.COPY, [y[:7, :7].t()], [square.t()[2:, 1:8]])                 # both sides strided
+    assert torch.equal(square[1:8, 2:], y[:7, :7]) and float(square[0].abs().sum() + square[:, :2].abs().sum()) == 0.0
+    assert abi.launch(Template.COPY, [y[:, :1]], [wide[:, :1].expand(37, 1)], check=False) == 0
+    assert abi.launch(Template.COPY, [y], [torch.zeros(37, 1, device=DEV).expand(37, 53)], check=False) != 0   # stride-0 output
 
 
 def test_layer_norm_template(executor):
