@@ -449,6 +449,43 @@ def test_transformer_block_compiles_and_matches_eager():
     assert_close(got.float(), want.float(), 3e-2, "transformer block")
 
 
+def test_llama_style_block_compiles_and_matches_eager():
+    """RMS norm, fused QKV projection split by chunk, rotary embedding in the rotate-half form
+    (slices, negation, cat, broadcast cos / sin), causal attention, SwiGLU MLP, residuals: every
+    piece on a kernel template, compared with eager bf16 on the CPU."""
+    F = torch.nn.functional
+    B, S, E, H = 2, 128, 256, 4
+    D = E // H
+    gen = torch.Generator().manual_seed(64)
+
+    def r(*shape, scale=1.0):
+        return (scale * torch.randn(*shape, generator=gen)).bfloat16()
+
+    def rotate_half(t):
+        return torch.cat([-t[..., D // 2:], t[..., :D // 2]], -1)
+
+    def block(x, g1, wqkv, wo, g2, wgate, wup, wdown, cos, sin):
+        h = F.rms_norm(x, (E,), g1, 1e-6)
+        q, k, v = F.linear(h, wqkv).chunk(3, dim=-1)
+        q, k, v = (t.view(B, S, H, D).transpose(1, 2) for t in (q, k, v))
+        q = q * cos + rotate_half(q) * sin
+        k = k * cos + rotate_half(k) * sin
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, E)
+        x = x + F.linear(a, wo)
+        h = F.rms_norm(x, (E,), g2, 1e-6)
+        return x + F.linear(F.silu(F.linear(h, wgate)) * F.linear(h, wup), wdown)
+
+    pos = torch.arange(S).float()[:, None] * (10000.0 ** (-torch.arange(0, D, 2).float() / D))[None, :]
+    ang = torch.cat([pos, pos], -1)
+    inputs = [r(B, S, E, scale=0.5), (torch.rand(E, generator=gen) + 0.5).bfloat16(), r(3 * E, E, scale=1 / 16),
+              r(E, E, scale=1 / 16), (torch.rand(E, generator=gen) + 0.5).bfloat16(), r(2 * E, E, scale=1 / 16),
+              r(2 * E, E, scale=1 / 16), r(E, 2 * E, scale=1 / 22), ang.cos().bfloat16(), ang.sin().bfloat16()]
+    want = rp.run_reference(block, inputs)
+    got = compiled(block)(*[t.to(DEV) for t in inputs])
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    assert_close(got.float(), want.float(), 3e-2, "llama-style block")
+
+
 def test_mixed_dtype_clusters():
     """A bool mask input, a comparison that leaves the graph as bool, an integer tensor scaling a
     float one: exact against eager."""
