@@ -660,17 +660,27 @@ def _lower_shape(cluster: FusionCluster):
     canonical = info.canonical_name if info is not None else None
     if canonical != "slice" and src.shape is not None and math.prod(src.shape) != math.prod(out.shape):
         raise UnsupportedOperationError(node.op_name, "element count changes")
+    # A value that is itself a view of an earlier buffer (a slice, a transposed view, a reshape of
+    # one) carries that view's description; a layout change applied to it is composed with it and
+    # gathers straight from the earlier buffer, so slice -> view -> transpose costs one copy.  The
+    # intermediate launches stay in the list and are dropped later if nothing else reads them.
+    base, base_view = getattr(src, "_view_of", None) or (src, None)
+
+    def meta_of_src():
+        m = torch.empty(base.shape, dtype=base.dtype, device="meta")
+        return m if base_view is None else m.as_strided(*base_view)
+
     if canonical in ("permute", "slice"):
         # transpose / permute / t / swapaxes / movedim, and basic slicing (x[a:b, ::2], narrow,
-        # select): replay the call on a meta tensor to get the view's strides and first element,
-        # then gather that view into a contiguous buffer (every buffer of a plan is contiguous, so
-        # the layout change has to move data)
+        # select, members of chunk / split / unbind, expand): replay the call on a meta tensor to
+        # get the view's strides and first element, then gather that view into a contiguous buffer
+        # (every buffer of a plan is contiguous, so the layout change has to move data)
         if src.shape is None:
             raise UnsupportedOperationError(node.op_name, "unknown input shape")
         if len(node.inputs) != 1:
             raise UnsupportedOperationError(node.op_name, "indexing by a tensor")
         try:
-            meta = torch.empty(src.shape, dtype=src.dtype, device="meta")
+            meta = meta_of_src()
             consts = _const_args(node)
             if "view_call" in node.metadata:     # one member of chunk / split / unbind
                 method, m_args, m_kwargs, index = node.metadata["view_call"]
@@ -681,17 +691,37 @@ def _lower_shape(cluster: FusionCluster):
                 view = getattr(meta, node.op_name)(*consts, **node.metadata.get("kwargs", {}))
         except Exception as exc:
             raise UnsupportedOperationError(node.op_name, f"cannot evaluate the layout change: {exc}") from exc
-        if tuple(view.shape) != tuple(out.shape):
-            raise UnsupportedOperationError(node.op_name, f"shape {tuple(view.shape)} != {tuple(out.shape)}")
         if not isinstance(view, torch.Tensor):
             raise UnsupportedOperationError(node.op_name, "the call returns several views")
-        if view.is_contiguous() and view.storage_offset() == 0 and view.numel() == meta.numel():
-            return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
+        if tuple(view.shape) != tuple(out.shape):
+            raise UnsupportedOperationError(node.op_name, f"shape {tuple(view.shape)} != {tuple(out.shape)}")
+        if view.is_contiguous() and view.storage_offset() == 0 and view.numel() == math.prod(base.shape):
+            return KernelLaunch(0, cluster.signature(), [base], [out], None, [out.shape], [out.dtype], alias_of=base,
                                 cluster=cluster)
-        return KernelLaunch(Template.COPY, cluster.signature(), [src], [out], None, [out.shape], [out.dtype],
+        out._view_of = (base, (tuple(view.shape), tuple(view.stride()), int(view.storage_offset())))
+        return KernelLaunch(Template.COPY, cluster.signature(), [base], [out], None, [out.shape], [out.dtype],
                             cluster=cluster, view_strides=tuple(view.stride()), view_offset=int(view.storage_offset()))
+    if base_view is not None:                    # reshape of a view: keep the description when it stays a view
+        try:
+            view = meta_of_src().view(tuple(out.shape))
+            out._view_of = (base, (tuple(view.shape), tuple(view.stride()), int(view.storage_offset())))
+        except Exception:
+            pass
     return KernelLaunch(0, cluster.signature(), [src], [out], None, [out.shape], [out.dtype], alias_of=src,
                         cluster=cluster)
+
+
+def prune_dead_launches(launches: list) -> list:
+    """Drop launches whose outputs nothing reads (left behind when a later layout change was
+    composed with the view they materialised).  A launch is kept when one of its outputs is a
+    result of the graph or an input of a kept launch."""
+    needed: set = set()
+    kept = []
+    for launch in reversed(launches):
+        if any(b.is_output or b in needed for b in launch.outputs):
+            kept.append(launch)
+            needed.update(launch.inputs)
+    return kept[::-1]
 
 
 def _lower_layer_norm(cluster: FusionCluster) -> list:

@@ -15,7 +15,7 @@ from typing import Any, Optional
 
 import torch
 
-from ..codegen.kernel_templates import KernelLaunch, KernelTemplateSelector
+from ..codegen.kernel_templates import KernelLaunch, KernelTemplateSelector, prune_dead_launches
 from ..optimization.fusion import FusionCluster, LocalPriorityFusionEngine, schedule_clusters
 from ..optimization.graph_analyzer import ComputationDAG, GraphAnalyzer
 from ..utils.cache import CompilationCache
@@ -102,6 +102,7 @@ class ChoreoJITCompiler:
             for c in ordered:
                 sel = self.template_selector.select(c)
                 launches.extend(sel if isinstance(sel, list) else [sel])
+            launches = prune_dead_launches(launches)
             name = f"kernel_{graph_hash[:8]}"
             plan_text = self.template_selector.generate_plan_text(launches, name)
         except ConductorError:

@@ -350,3 +350,25 @@ def test_cat_lowers_to_one_copy_per_part_into_the_result():
     assert art.launches[0].outputs[0] is art.launches[1].outputs[0]
     assert [l.out_view for l in art.launches] == [((4, 8, 16), (160, 16, 1), 0), ((4, 2, 16), (160, 16, 1), 128)]
     assert tuple(art.launches[0].out_shapes[0]) == (4, 10, 16)
+
+
+def test_layout_changes_compose_into_one_copy():
+    """chunk -> view -> transpose: each step is a view of the projection's output, so the transposed
+    head layout is gathered straight from it by ONE copy; the intermediate copies and aliases have
+    no reader left and are dropped.  A value that something else reads is still materialised."""
+    B, S, E, H = 2, 8, 32, 4
+
+    def heads(x):
+        q, k, v = x.chunk(3, dim=-1)
+        return tuple(t.view(B, S, H, E // H).transpose(1, 2) * 2.0 for t in (q, k, v))
+
+    art = compile_with_dynamo(heads, [torch.randn(B, S, 3 * E)])
+    copies = [l for l in art.launches if l.template == Template.COPY]
+    assert len(copies) == 3 and not [l for l in art.launches if l.template == 0]
+    assert all(l.inputs[0].name == "l_x_" for l in copies)
+    assert sorted(l.view_offset for l in copies) == [0, E, 2 * E]
+    assert all(l.view_strides == (S * 3 * E, E // H, 3 * E, 1) for l in copies)
+
+    art = compile_with_dynamo(lambda x: (x[:, 1:].t() + 1.0, x[:, 1:] * 2.0), [torch.randn(6, 9)])
+    copies = [l for l in art.launches if l.template == Template.COPY]
+    assert sorted(l.view_strides for l in copies) == [(1, 9), (9, 1)] and all(l.view_offset == 1 for l in copies)
