@@ -377,8 +377,14 @@ def _expand_general_broadcasts(inputs, iter_shape, cluster: FusionCluster):
                 view = torch.empty(b.shape, dtype=b.dtype, device="meta").expand(tuple(iter_shape))
             except Exception:
                 raise exc from None
-        full = Buffer(name=f"{b.name}_expanded", scope=BufferScope.SHARED, dtype=b.dtype, shape=tuple(iter_shape),
-                      is_temporary=True)
+        done = getattr(b, "_expanded", None)
+        if done is None:
+            done = b._expanded = {}
+        if tuple(iter_shape) in done:               # an earlier cluster of this plan already expanded it
+            replaced.append(done[tuple(iter_shape)])
+            continue
+        full = done[tuple(iter_shape)] = Buffer(name=f"{b.name}_expanded", scope=BufferScope.SHARED, dtype=b.dtype,
+                                                shape=tuple(iter_shape), is_temporary=True)
         pre.append(KernelLaunch(Template.COPY, f"{cluster.signature()}:expand", [b], [full], None, [full.shape],
                                 [full.dtype], cluster=cluster, view_strides=tuple(view.stride())))
         replaced.append(full)
