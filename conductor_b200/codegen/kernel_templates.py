@@ -924,8 +924,39 @@ def _lower_variance(cluster: FusionCluster) -> list:
     return [l1, l2, l3]
 
 
+def _lower_pointwise_loss(cluster: FusionCluster) -> list:
+    """mse_loss / l1_loss: the chain (x - y)^2 or |x - y| in fp32 in front of a mean or sum over
+    everything (one full-reduce launch), or on its own for reduction='none'."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    kw = node.metadata.get("kwargs", {})
+    if len(spec) < 2 or spec[0][0] != "buf" or spec[1][0] != "buf":
+        raise UnsupportedOperationError(node.op_name, "expected (input, target)")
+    x, y, out = node.inputs[spec[0][1]], node.inputs[spec[1][1]], node.outputs[0]
+    consts = _const_args(node)
+    reduction = kw.get("reduction", next((c for c in consts if isinstance(c, str)), "mean"))
+    if tuple(x.shape) != tuple(y.shape) or not is_float(x.dtype) or reduction not in ("mean", "sum", "none"):
+        raise UnsupportedOperationError(node.op_name, f"shapes {x.shape} / {y.shape}, reduction={reduction!r}")
+    f32 = torch.float32
+    last_dt = out.dtype if reduction == "none" else f32
+    b = _ProgramBuilder([x, y], x.shape)
+    d = b._emit(EwOp.SUB, 0, 1, dtype=f32)
+    r = b._emit(EwOp.MUL, d, d, dtype=last_dt) if node.op_name == "mse_loss" else b._emit(EwOp.ABS, d, dtype=last_dt)
+    if reduction == "none":
+        return [KernelLaunch(Template.ELEMENTWISE, cluster.signature(), [x, y], [out], b.build([r]), [out.shape],
+                             [out.dtype], cluster=cluster)]
+    p = CdrReduceParams()
+    p.chain = b.build([r])
+    p.reduce_op = ReduceOp.MEAN if reduction == "mean" else ReduceOp.SUM
+    return [KernelLaunch(Template.FULL_REDUCE, cluster.signature(), [x, y], [out], p, [out.shape], [out.dtype],
+                         cluster=cluster, needs_workspace=True)]
+
+
 def _lower_norm(cluster: FusionCluster) -> list:
     name = cluster.nodes[0].op_name
+    if name in ("mse_loss", "l1_loss"):
+        return _lower_pointwise_loss(cluster)
     if name == "rms_norm":
         return _lower_rms_norm(cluster)
     if name in ("log_softmax", "logsumexp"):

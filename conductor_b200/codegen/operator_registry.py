@@ -150,7 +150,8 @@ class OperatorRegistry:
                        template=Template.SOFTMAX_BWD, preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("layer_norm", "layer_norm", OpType.NORM, False, 3, preferred_fusion_level=FusionLevel.GLOBAL))
         # row statistics lowered to several launches of the reduce and elementwise templates
-        for name, arity in (("rms_norm", 2), ("log_softmax", 1), ("logsumexp", 1), ("var", 1), ("std", 1)):
+        for name, arity in (("rms_norm", 2), ("log_softmax", 1), ("logsumexp", 1), ("var", 1), ("std", 1),
+                            ("mse_loss", 2), ("l1_loss", 2)):
             r(OperatorInfo(name, name, OpType.NORM, False, arity, preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("linear", "linear", OpType.MATRIX, True, 3, template=Template.GEMM_EPILOGUE,
                        preferred_fusion_level=FusionLevel.GLOBAL))

@@ -339,6 +339,25 @@ def test_row_statistics_lowered_to_several_launches():
         assert_close(got.float(), want.float(), 2e-2, name + " bf16")
 
 
+def test_pointwise_losses():
+    """mse_loss / l1_loss: difference chain in fp32 + mean or sum over everything in one launch."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(65)
+    x, y = torch.randn(300, 257, generator=gen), torch.randn(300, 257, generator=gen)
+    cases = {"mse": lambda a, b: F.mse_loss(a, b), "mse_sum": lambda a, b: F.mse_loss(a, b, reduction="sum"),
+             "l1": lambda a, b: F.l1_loss(a * 2.0, b), "l1_none": lambda a, b: F.l1_loss(a, b, reduction="none") * 2.0}
+    for name, fn in cases.items():
+        want = rp.run_reference(fn, [x, y])
+        got = compiled(fn)(x.to(DEV), y.to(DEV)).cpu()
+        assert got.shape == want.shape and got.dtype == want.dtype, name
+        assert_close(got, want, 1e-5, name)
+    xb, yb = x.bfloat16(), y.bfloat16()
+    want = rp.run_reference(cases["mse"], [xb, yb])
+    got = compiled(cases["mse"])(xb.to(DEV), yb.to(DEV)).cpu()
+    assert got.dtype == torch.bfloat16
+    assert_close(got.float(), want.float(), 2e-2, "mse bf16")
+
+
 def test_softmax_over_an_inner_dimension():
     """softmax over a dimension other than the last: transposing copy, row kernel, transposing copy."""
     gen = torch.Generator().manual_seed(62)

@@ -372,3 +372,13 @@ def test_layout_changes_compose_into_one_copy():
     art = compile_with_dynamo(lambda x: (x[:, 1:].t() + 1.0, x[:, 1:] * 2.0), [torch.randn(6, 9)])
     copies = [l for l in art.launches if l.template == Template.COPY]
     assert sorted(l.view_strides for l in copies) == [(1, 9), (9, 1)] and all(l.view_offset == 1 for l in copies)
+
+
+def test_pointwise_losses_lower_to_one_full_reduce_launch():
+    F = torch.nn.functional
+    x, y = torch.randn(8, 16), torch.randn(8, 16)
+    (launch,) = compile_with_dynamo(lambda a, b: F.mse_loss(a, b), [x, y]).launches
+    assert launch.template == Template.FULL_REDUCE and launch.params.reduce_op == ReduceOp.MEAN
+    assert [launch.params.chain.instr[i].op for i in range(launch.params.chain.n_instr)] == [EwOp.SUB, EwOp.MUL]
+    (launch,) = compile_with_dynamo(lambda a, b: F.l1_loss(a, b, reduction="sum"), [x, y]).launches
+    assert launch.params.reduce_op == ReduceOp.SUM and launch.params.chain.instr[1].op == EwOp.ABS
