@@ -247,8 +247,9 @@ class FusionEngine:
                     grp = self._match_softmax_backward(n, claimed)
                     if grp:
                         claim(grp, FusionType.SOFTMAX, pattern="softmax_bwd_written_out")
-            for n in order:                                   # linear (+relu epilogue)
-                if n in claimed or n.op_name != "linear":
+            for n in order:                                   # linear / matmul / addmm (+relu epilogue)
+                info = get_op_desc(n.op_name)
+                if n in claimed or info is None or info.operation_type is not OpType.MATRIX:
                     continue
                 grp = [n]
                 out = n.outputs[0]

@@ -554,7 +554,7 @@ def test_mlp_is_differentiable_through_the_backend():
 
 def test_matmul_operator_forms():
     """`x @ w`, torch.mm and torch.matmul with a 2-D right operand lower to the GEMM template with the
-    weight read in place; a relu behind it runs as its own cluster."""
+    weight read in place; a relu behind it joins as the GEMM's epilogue."""
     gen = torch.Generator().manual_seed(51)
     x = torch.randn(3, 200, 256, generator=gen).bfloat16()
     w = (torch.randn(256, 384, generator=gen) / 16).bfloat16()

@@ -173,7 +173,8 @@ def test_matmul_lowers_to_the_gemm_template_with_the_weight_in_place():
     x, w = torch.randn(2, 64, 32).bfloat16(), torch.randn(32, 48).bfloat16()
     art = compile_with_dynamo(lambda a, b: torch.relu(a @ b), [x, w])
     ks = kernels(art)
-    assert [k.template for k in ks] == [Template.GEMM_EPILOGUE, Template.ELEMENTWISE]
+    assert [k.template for k in ks] == [Template.GEMM_EPILOGUE]          # the relu joins as the epilogue
+    assert ks[0].params.activation == 1
     assert ks[0].params.weight_layout == 1 and ks[0].params.x_layout == 0 and ks[0].out_shapes == [(2, 64, 48)]
     assert_unsupported(lambda a, b: a @ b, [torch.randn(2, 8, 16), torch.randn(2, 16, 8)])     # batched right operand
 
