@@ -242,6 +242,8 @@ class _ProgramBuilder:
         if canon == "clamp":                                  # clamp / clip / hardtanh / relu6
             lo, hi = {"relu6": (0.0, 6.0), "hardtanh": (-1.0, 1.0)}.get(node.op_name, (None, None))
             nums = [s[1] if is_num(s) else None for s in spec[1:3]] + [None, None]
+            if node.op_name.rstrip("_") == "clamp_max":      # clamp_max(x, hi): the one bound is the upper one
+                nums = [None, nums[0]]
             lo = kw.get("min", kw.get("min_val", nums[0] if nums[0] is not None else lo))
             hi = kw.get("max", kw.get("max_val", nums[1] if nums[1] is not None else hi))
             if any(is_buf(s) for s in spec[1:]) or any(k[0] == "buf" for k in kws.values()):
@@ -683,12 +685,14 @@ def _lower_shape(cluster: FusionCluster):
         # (every buffer of a plan is contiguous, so the layout change has to move data)
         if src.shape is None:
             raise UnsupportedOperationError(node.op_name, "unknown input shape")
-        if len(node.inputs) != 1:
+        if len(node.inputs) != 1 and node.op_name != "expand_as":
             raise UnsupportedOperationError(node.op_name, "indexing by a tensor")
         try:
             meta = meta_of_src()
             consts = _const_args(node)
-            if "view_call" in node.metadata:     # one member of chunk / split / unbind
+            if node.op_name == "expand_as":      # the second tensor only gives the shape
+                view = meta.expand(tuple(out.shape))
+            elif "view_call" in node.metadata:     # one member of chunk / split / unbind
                 method, m_args, m_kwargs, index = node.metadata["view_call"]
                 view = getattr(meta, method)(*m_args, **m_kwargs)[index]
             elif node.op_name in ("getitem", "__getitem__"):
@@ -953,8 +957,57 @@ def _lower_pointwise_loss(cluster: FusionCluster) -> list:
                          cluster=cluster, needs_workspace=True)]
 
 
+def _lower_vector_norm(cluster: FusionCluster) -> list:
+    """x.norm(dim=-1) / linalg.vector_norm with p = 2 over the last dimension: fp32 row sum of squares,
+    then its square root."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    kw = node.metadata.get("kwargs", {})
+    x, out = node.inputs[spec[0][1]], node.outputs[0]
+    consts = _const_args(node)
+    p = kw.get("p", kw.get("ord", consts[0] if consts else 2))
+    dim = kw.get("dim", consts[1] if len(consts) > 1 else None)
+    if isinstance(dim, (list, tuple)) and len(dim) == 1:
+        dim = dim[0]
+    if p not in (2, 2.0, "fro", None) or not isinstance(dim, int) or dim % len(x.shape) != len(x.shape) - 1 or not is_float(x.dtype):
+        raise UnsupportedOperationError(node.op_name, f"p={p!r}, dim={dim!r}; only the 2-norm over the last dimension")
+    f32 = torch.float32
+    ssq, l1 = _row_statistic(cluster, "sumsq", [x], ReduceOp.SUM, lambda b: b._emit(EwOp.MUL, 0, 0, dtype=f32))
+    b2 = _ProgramBuilder([ssq], ssq.shape)
+    y = b2._emit(EwOp.SQRT, 0, dtype=out.dtype)
+    return [l1, KernelLaunch(Template.ELEMENTWISE, f"{cluster.signature()}:sqrt", [ssq], [out], b2.build([y]), [out.shape],
+                             [out.dtype], cluster=cluster)]
+
+
+def _lower_normalize(cluster: FusionCluster) -> list:
+    """F.normalize(x, p=2, dim=last, eps): x / max(||x||_2, eps) with the row norm in fp32."""
+    _require_shapes(cluster)
+    node = cluster.nodes[0]
+    spec = node.metadata.get("arg_spec", [])
+    kw = node.metadata.get("kwargs", {})
+    x, out = node.inputs[spec[0][1]], node.outputs[0]
+    consts = _const_args(node)
+    p = kw.get("p", consts[0] if consts else 2.0)
+    dim = kw.get("dim", consts[1] if len(consts) > 1 else 1)
+    eps = kw.get("eps", consts[2] if len(consts) > 2 else 1e-12)
+    if p not in (2, 2.0) or not isinstance(dim, int) or dim % len(x.shape) != len(x.shape) - 1 or not is_float(x.dtype):
+        raise UnsupportedOperationError("normalize", f"p={p!r}, dim={dim!r}; only the 2-norm over the last dimension")
+    f32 = torch.float32
+    ssq, l1 = _row_statistic(cluster, "sumsq", [x], ReduceOp.SUM, lambda b: b._emit(EwOp.MUL, 0, 0, dtype=f32))
+    b2 = _ProgramBuilder([x, ssq], x.shape)
+    n = b2._emit(EwOp.MAX, b2._emit(EwOp.SQRT, 1, dtype=f32), b2._emit(EwOp.CONST, imm=eps, dtype=f32), dtype=f32)
+    y = b2._emit(EwOp.DIV, 0, n, dtype=out.dtype)
+    return [l1, KernelLaunch(Template.ELEMENTWISE, f"{cluster.signature()}:divide", [x, ssq], [out], b2.build([y]),
+                             [out.shape], [out.dtype], cluster=cluster)]
+
+
 def _lower_norm(cluster: FusionCluster) -> list:
     name = cluster.nodes[0].op_name
+    if name in ("norm", "vector_norm", "linalg_vector_norm"):
+        return _lower_vector_norm(cluster)
+    if name == "normalize":
+        return _lower_normalize(cluster)
     if name in ("mse_loss", "l1_loss"):
         return _lower_pointwise_loss(cluster)
     if name == "rms_norm":

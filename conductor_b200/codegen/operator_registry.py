@@ -131,7 +131,7 @@ class OperatorRegistry:
         r(_ew("gelu", EwOp.GELU, 1))
         r(_ew("erf", EwOp.ERF, 1))
         # lowered to existing instructions: clamp -> max/min with constants, pow -> mul / sqrt / reciprocal
-        r(_ew("clamp", EwOp.MAX, 1), "clip", "clamp_", "hardtanh", "relu6")
+        r(_ew("clamp", EwOp.MAX, 1), "clip", "clamp_", "hardtanh", "relu6", "clamp_min", "clamp_max", "clamp_min_", "clamp_max_")
         r(_ew("pow", EwOp.MUL, 2), "square", "reciprocal")
         # activations and selections written out over the opcode set by the program builder
         r(_ew("composite", EwOp.WHERE, 1), "leaky_relu", "leaky_relu_", "elu", "elu_", "softplus", "hardswish",
@@ -151,7 +151,7 @@ class OperatorRegistry:
         r(OperatorInfo("layer_norm", "layer_norm", OpType.NORM, False, 3, preferred_fusion_level=FusionLevel.GLOBAL))
         # row statistics lowered to several launches of the reduce and elementwise templates
         for name, arity in (("rms_norm", 2), ("log_softmax", 1), ("logsumexp", 1), ("var", 1), ("std", 1),
-                            ("mse_loss", 2), ("l1_loss", 2)):
+                            ("mse_loss", 2), ("l1_loss", 2), ("norm", 1), ("vector_norm", 1), ("linalg_vector_norm", 1), ("normalize", 1)):
             r(OperatorInfo(name, name, OpType.NORM, False, arity, preferred_fusion_level=FusionLevel.GLOBAL))
         r(OperatorInfo("linear", "linear", OpType.MATRIX, True, 3, template=Template.GEMM_EPILOGUE,
                        preferred_fusion_level=FusionLevel.GLOBAL))
@@ -165,7 +165,7 @@ class OperatorRegistry:
         # layout changes that move data: one launch of the strided-copy template
         for perm_op in ("transpose", "permute", "t", "swapaxes", "movedim"):
             r(OperatorInfo(perm_op, "permute", OpType.SHAPE, False, 1))
-        for slice_op in ("getitem", "__getitem__", "narrow", "select", "view_of", "expand", "broadcast_to"):
+        for slice_op in ("getitem", "__getitem__", "narrow", "select", "view_of", "expand", "broadcast_to", "expand_as"):
             r(OperatorInfo(slice_op, "slice", OpType.SHAPE, False, 1))
         r(OperatorInfo("cat", "cat", OpType.SHAPE, False, 2), "concat", "concatenate")
         for shape_op in ("view", "reshape", "flatten", "unsqueeze", "squeeze", "contiguous", "detach", "clone_view"):

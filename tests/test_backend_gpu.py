@@ -358,6 +358,29 @@ def test_pointwise_losses():
     assert_close(got.float(), want.float(), 2e-2, "mse bf16")
 
 
+def test_vector_norm_normalize_and_one_sided_clamps():
+    """x.norm(dim=-1), linalg.vector_norm, F.normalize (row 2-norm in fp32, then sqrt / divide),
+    clamp_min / clamp_max and expand_as."""
+    F = torch.nn.functional
+    gen = torch.Generator().manual_seed(66)
+    x = torch.randn(96, 200, generator=gen)
+    x[3] = 0.0                                     # a zero row: normalize divides by eps, not by 0
+    close = {"norm": lambda a: a.norm(dim=-1), "vector_norm": lambda a: torch.linalg.vector_norm(a, dim=-1, keepdim=True),
+             "normalize": lambda a: F.normalize(a, dim=-1), "normalize_default_dim": lambda a: F.normalize(a) * 2.0}
+    exact = {"one_sided": lambda a: a.clamp_min(0.5) + a.clamp_max(-0.5), "expand_as": lambda a: a[:, :1].expand_as(a) + a}
+    for name, fn in {**close, **exact}.items():
+        want = rp.run_reference(fn, [x])
+        got = compiled(fn)(x.to(DEV)).cpu()
+        assert got.shape == want.shape, name
+        if name in exact:
+            assert torch.equal(got, want), name
+        else:
+            assert_close(got, want, 1e-5, name)
+    xb = x.bfloat16()
+    want = rp.run_reference(close["normalize"], [xb])
+    assert_close(compiled(close["normalize"])(xb.to(DEV)).cpu().float(), want.float(), 2e-2, "normalize bf16")
+
+
 def test_softmax_over_an_inner_dimension():
     """softmax over a dimension other than the last: transposing copy, row kernel, transposing copy."""
     gen = torch.Generator().manual_seed(62)

@@ -383,3 +383,14 @@ def test_pointwise_losses_lower_to_one_full_reduce_launch():
     assert [launch.params.chain.instr[i].op for i in range(launch.params.chain.n_instr)] == [EwOp.SUB, EwOp.MUL]
     (launch,) = compile_with_dynamo(lambda a, b: F.l1_loss(a, b, reduction="sum"), [x, y]).launches
     assert launch.params.reduce_op == ReduceOp.SUM and launch.params.chain.instr[1].op == EwOp.ABS
+
+
+def test_normalize_and_norm_lower_to_a_row_statistic_and_a_chain():
+    F = torch.nn.functional
+    x = torch.randn(8, 16)
+    art = compile_with_dynamo(lambda a: F.normalize(a, dim=-1), [x])
+    assert [l.template for l in art.launches] == [Template.ROW_REDUCE, Template.ELEMENTWISE]
+    ops = [art.launches[1].params.instr[i].op for i in range(art.launches[1].params.n_instr)]
+    assert ops == [EwOp.SQRT, EwOp.CONST, EwOp.MAX, EwOp.DIV]
+    assert_unsupported(lambda a: F.normalize(a, dim=0), [x])
+    assert_unsupported(lambda a: a.norm(p=1, dim=-1), [x])
