@@ -28,15 +28,20 @@ struct CopyArgs {
   int64_t ostride[CDR_MAX_RANK];// output strides in bytes
 };
 
-template <int UNIT>
+// IDX is the type the unit index is decomposed in: 32-bit when the unit count allows it (a 64-bit
+// division costs several times a 32-bit one, and a rank-4 view needs four per 16 bytes moved).
+template <int UNIT, typename IDX>
 __global__ void __launch_bounds__(256) strided_copy_kernel(const __grid_constant__ CopyArgs a) {
-  const int64_t step = static_cast<int64_t>(gridDim.x) * 256;
-  for (int64_t u = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; u < a.n_units; u += step) {
-    int64_t rest = u, off = 0, ooff = 0;
+  const IDX step = static_cast<IDX>(gridDim.x) * 256;
+  const IDX n_units = static_cast<IDX>(a.n_units);
+  for (IDX u = static_cast<IDX>(blockIdx.x) * 256 + threadIdx.x; u < n_units; u += step) {
+    IDX rest = u;
+    int64_t off = 0, ooff = 0;
 #pragma unroll 1
     for (int d = a.rank - 1; d >= 0; --d) {
-      const int64_t q = rest / a.shape[d];
-      const int64_t r = rest - q * a.shape[d];
+      const IDX extent = static_cast<IDX>(a.shape[d]);
+      const IDX q = rest / extent;
+      const int64_t r = static_cast<int64_t>(rest - q * extent);
       off += r * a.stride[d];
       ooff += r * a.ostride[d];
       rest = q;
@@ -105,13 +110,19 @@ int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs,
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   if (grid > cap) grid = cap;
   const unsigned g = static_cast<unsigned>(grid);
+  // the grid-stride loop's index may run one stride past n_units before it stops
+  const bool narrow = a.n_units + grid * 256 < (int64_t{1} << 32);
+#define CDR_COPY_LAUNCH(UNIT)                                                     \
+  if (narrow) strided_copy_kernel<UNIT, uint32_t><<<g, 256, 0, stream>>>(a);      \
+  else strided_copy_kernel<UNIT, int64_t><<<g, 256, 0, stream>>>(a)
   switch (a.unit_bytes) {
-    case 16: strided_copy_kernel<16><<<g, 256, 0, stream>>>(a); break;
-    case 8: strided_copy_kernel<8><<<g, 256, 0, stream>>>(a); break;
-    case 4: strided_copy_kernel<4><<<g, 256, 0, stream>>>(a); break;
-    case 2: strided_copy_kernel<2><<<g, 256, 0, stream>>>(a); break;
-    default: strided_copy_kernel<1><<<g, 256, 0, stream>>>(a); break;
+    case 16: CDR_COPY_LAUNCH(16); break;
+    case 8: CDR_COPY_LAUNCH(8); break;
+    case 4: CDR_COPY_LAUNCH(4); break;
+    case 2: CDR_COPY_LAUNCH(2); break;
+    default: CDR_COPY_LAUNCH(1); break;
   }
+#undef CDR_COPY_LAUNCH
   CDR_CUDA_TRY(cudaGetLastError());
   return CDR_OK;
 }
