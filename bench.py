@@ -1,26 +1,36 @@
 #!/usr/bin/env python
-"""Benchmark of the compiled-graph hot path.
+"""Benchmark of the compiled-graph hot path: all five benchmark configurations in one run.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c2g|c3|c3b|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload all|c1|c2|c3|c3b|c4|c5] [--impl reference]
 
-One step = one pass of a `torch.compile(fn, backend='gcu')` graph over one batch of seeded
-synthetic input.  Default workload: c2, `mean(relu(x*w + b), dim=-1)` with x bf16 [16384, 4096]
--- the configuration the samples/s metric is quoted on.  With N > 1 (launched under
-torch.distributed.run, one process per GPU) every rank runs the same graph on its own batch:
-rows are independent, so the path shards with no collective (weak scaling).
+A *pass* is one run of a `torch.compile(fn, backend='gcu')` graph over one batch of seeded
+synthetic input.  A *step* is `passes_per_step` back-to-back passes that walk a rotating pool of
+distinct input batches (larger than L2 in total); the count is chosen per configuration so that
+the K timed steps last at least half a second, and is reported.  Six graphs are timed: c1 mul_add,
+c2 mean(relu(x*w+b)), c3 softmax forward, c3b softmax backward, c4 MLP, c5 causal attention.
 
-Prints ONE JSON line on rank 0:
+With N > 1 (launched under torch.distributed.run, one process per GPU) the FIXED configuration is
+partitioned by rows / tokens / sequences: rank r runs block r of `row_partition(rows, N)` through
+the row-count-polymorphic plan (`Callable(batch_size=...)`), with no collective on the data path
+(strong scaling).  Each rank additionally runs the whole configuration (`weak`, replicas), and one
+NCCL all-gather of the outputs is timed separately.
+
+Prints ONE JSON line on rank 0.  Headline keys (`value`, `ms_per_step`, `roofline`, `e2e`,
+`cpu_baseline`) are configuration c2; `per_config` carries the same keys for all six.
   value     samples/s over all ranks, inputs resident in HBM, plan replayed from a CUDA graph
   e2e       the same metric through the public API with HOST tensors: pinned host -> device copy
-            of the step's inputs, kernel(s), device -> host read of the result, every step
-  roofline  the dominant kernel's achieved HBM GB/s (or TFLOP/s) against the measured peak
-  cpu_baseline  the reference's executed path (PyTorch eager on the host cores) on the same batch
+            of the step's inputs, kernel(s), device -> host read of the result, every pass
+  roofline  achieved HBM GB/s (or TFLOP/s) of the configuration's kernel(s) over the timed region,
+            against the measured peak
+  cpu_baseline  the reference package itself (its `gcu` backend ends in PyTorch eager on the host
+            cores) on the same batch, timed in a child process
 `--impl reference` times only that CPU path and prints it with "impl": "reference".
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -31,17 +41,28 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 import torch  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
-POOL_BYTES_MIN = 4 * L2_BYTES          # rotating input pool is at least this large
+POOL_BYTES_MIN = 4 * L2_BYTES          # rotating pool (inputs + outputs) is at least this large
+MAX_POOL = 64
+MAX_SEQ = 256                          # passes captured in one CUDA graph
+REGION_S = 0.6                         # every timed region lasts at least this long
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+ALL = ["c1", "c2", "c3", "c3b", "c4", "c5"]
+HEADLINE = "c2"
+METRIC = "compiled-graph samples/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the full
+# configuration, from the ncu captures summarised under profiles/
+TRAFFIC_BYTES: dict = {"c1": 235.0e6, "c2": 137.98e6, "c3": 2097.4e6, "c3b": 3180.9e6, "c4": 81.0e6, "c5": 552.2e6}
 
 
 # ---------------------------------------------------------------- workloads
 class Workload:
-    """name, graph, per-rank inputs, algorithmic bytes/flops of the dominant kernel."""
+    """One benchmark configuration: graph, seeded inputs, rows, algorithmic bytes / flops."""
 
     def __init__(self, key):
         from examples import workloads as rp
@@ -51,54 +72,77 @@ class Workload:
         self.module = None
         if key == "c1":
             self.name = "c1 mul_add a*b+c fp32 [4096,4096]"
-            self.fn, self.dtype, self.samples = rp.mul_add, "f32", 4096
+            self.fn, self.dtype, self.rows = rp.mul_add, "f32", 4096
             self.make = lambda seed: rp.inputs_mul_add(seed=seed)
-            self.batch_inputs = [0, 1, 2]
-            self.bytes, self.flops, self.bound = 4 * 4096 * 4096 * 4, None, "hbm"
+            self.user_batch = [0, 1, 2]
+            self.bytes_per_row, self.flops_per_row, self.bound = 4 * 4096 * 4, None, "hbm"
+            self.fixed_bytes = 0
         elif key == "c2":
             self.name = "c2 mean(relu(x*w+b),-1) x bf16 [16384,4096], w,b bf16 [4096] -> fp32 [16384]"
-            self.fn, self.dtype, self.samples = rp.reduce_mean_fusion, "bf16", 16384
+            self.fn, self.dtype, self.rows = rp.reduce_mean_fusion, "bf16", 16384
             self.make = lambda seed: rp.inputs_reduce_mean(seed=seed)
-            self.batch_inputs = [0]
-            self.bytes, self.flops, self.bound = 16384 * 4096 * 2 + 2 * 4096 * 2 + 16384 * 4, None, "hbm"
-        elif key == "c2g":
-            self.name = "c2g mean(relu(x*w-b),-1) bf16 [16384,4096]: config 2's traffic through a run-time kernel instance"
-            self.fn, self.dtype, self.samples = rp.reduce_mean_variant, "bf16", 16384
-            self.make = lambda seed: rp.inputs_reduce_mean(seed=seed)
-            self.batch_inputs = [0]
-            self.bytes, self.flops, self.bound = 16384 * 4096 * 2 + 2 * 4096 * 2 + 16384 * 4, None, "hbm"
+            self.user_batch = [0]
+            self.bytes_per_row, self.flops_per_row, self.bound = 4096 * 2 + 4, None, "hbm"
+            self.fixed_bytes = 2 * 4096 * 2
         elif key == "c3":
             self.name = "c3 row softmax forward fp32 [32768,8192]"
-            self.fn, self.dtype, self.samples = rp.softmax_forward, "f32", 32768
+            self.fn, self.dtype, self.rows = rp.softmax_forward, "f32", 32768
             self.make = lambda seed: rp.inputs_softmax(seed=seed)[:1]
-            self.batch_inputs = [0]
-            self.bytes, self.flops, self.bound = 2 * 32768 * 8192 * 4, None, "hbm"
+            self.user_batch = [0]
+            self.bytes_per_row, self.flops_per_row, self.bound = 2 * 8192 * 4, None, "hbm"
+            self.fixed_bytes = 0
         elif key == "c3b":
-            self.name = "c3 row softmax backward fp32 [32768,8192]"
-            self.fn, self.dtype, self.samples = rp.softmax_backward, "f32", 32768
-
-            def make(seed):
-                logits, grad = rp.inputs_softmax(seed=seed)
-                return [grad, torch.softmax(logits, -1)]
-
-            self.make = make
-            self.batch_inputs = [0, 1]
-            self.bytes, self.flops, self.bound = 3 * 32768 * 8192 * 4, None, "hbm"
+            self.name = "c3b row softmax backward fp32 [32768,8192]"
+            self.fn, self.dtype, self.rows = rp.softmax_backward, "f32", 32768
+            self.make = lambda seed: list(reversed(rp.inputs_softmax(seed=seed)))   # [grad, logits]: y is made on the device
+            self.user_batch = [0, 1]
+            self.bytes_per_row, self.flops_per_row, self.bound = 3 * 8192 * 4, None, "hbm"
+            self.fixed_bytes = 0
         elif key == "c4":
             self.name = "c4 MLP Linear(1024,4096)+ReLU+Linear(4096,1024) bf16, x [8192,1024]"
             self.module = rp.make_mlp()
-            self.fn, self.dtype, self.samples = self.module, "bf16", 8192
+            self.fn, self.dtype, self.rows = self.module, "bf16", 8192
             self.make = lambda seed: rp.inputs_mlp(seed=seed)
-            self.batch_inputs = [0]
-            self.bytes, self.flops, self.bound = None, 2 * 2 * 8192 * 1024 * 4096, "tensor"
+            self.user_batch = [0]
+            self.bytes_per_row, self.flops_per_row, self.bound = None, 2 * 2 * 1024 * 4096, "tensor"
+            self.fixed_bytes = 0
         elif key == "c5":
             self.name = "c5 causal SDPA bf16 [8,16,2048,128]"
-            self.fn, self.dtype, self.samples = rp.causal_attention, "bf16", 8
+            self.fn, self.dtype, self.rows = rp.causal_attention, "bf16", 8
             self.make = lambda seed: rp.inputs_attention(seed=seed)
-            self.batch_inputs = [0, 1, 2]
-            self.bytes, self.flops, self.bound = None, 4 * 8 * 16 * 2048 * 2048 * 128 // 2, "tensor"
+            self.user_batch = [0, 1, 2]
+            self.bytes_per_row, self.flops_per_row, self.bound = None, 4 * 16 * 2048 * 2048 * 128 // 2, "tensor"
+            self.fixed_bytes = 0
         else:
             raise SystemExit(f"unknown workload {key}")
+
+    # seeded host inputs of the whole configuration, as the graph's user arguments
+    def host_inputs(self, seed=0):
+        ins = self.make(seed)
+        if self.key == "c3b":
+            grad, logits = ins
+            return [grad, torch.softmax(logits, -1)]
+        return ins
+
+    def device_batch(self, rows: int, dev, gen):
+        """Fresh batch-carrying inputs drawn on the device with the configuration's distributions
+        (pool slots other than the seeded one)."""
+        k = self.key
+        if k == "c1":
+            return [torch.randn(rows, 4096, device=dev, generator=gen) for _ in range(3)]
+        if k == "c2":
+            return [torch.randn(rows, 4096, device=dev, generator=gen).bfloat16()]
+        if k in ("c3", "c3b"):
+            logits = 3 * torch.randn(rows, 8192, device=dev, generator=gen)
+            logits += 40 * torch.rand(rows, 1, device=dev, generator=gen) - 20
+            if k == "c3":
+                return [logits]
+            return [torch.randn(rows, 8192, device=dev, generator=gen), torch.softmax(logits, -1)]
+        if k == "c4":
+            return [torch.randn(rows, 1024, device=dev, generator=gen).bfloat16()]
+        if k == "c5":
+            return [torch.randn(rows, 16, 2048, 128, device=dev, generator=gen).bfloat16() for _ in range(3)]
+        raise AssertionError(k)
 
 
 # ---------------------------------------------------------------- helpers
@@ -120,7 +164,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index = index
-        self.samples: list[list[str]] = []
+        self.samples: list[tuple[float, list[str]]] = []
         self.proc = None
         self.thread = None
 
@@ -137,22 +181,15 @@ class ClockSampler:
             for line in self.proc.stdout:
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) >= 6:
-                    self.samples.append(parts)
+                    self.samples.append((time.monotonic(), parts))
 
         self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
 
-    def stop(self) -> dict:
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except Exception:
-                self.proc.kill()
-        if self.thread is not None:
-            self.thread.join(timeout=5)
+    @staticmethod
+    def _summary(samples) -> dict:
         sm, mx, reasons = [], [], set()
-        for s in self.samples:
+        for _, s in samples:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -161,12 +198,25 @@ class ClockSampler:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        busy = [c for c in sm if c >= 0.5 * max(sm)] if sm else []
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
 
+    def window(self, t0: float, t1: float) -> dict:
+        """Clock summary of the samples taken inside [t0, t1] (monotonic seconds)."""
+        return self._summary([s for s in self.samples if t0 <= s[0] <= t1])
 
-def dist_setup(n_gpus: int):
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=5)
+
+
+def dist_setup():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -197,216 +247,447 @@ def max_over_ranks(value: float, world: int, device) -> float:
     return float(t.item())
 
 
-# ---------------------------------------------------------------- CPU arm
-def time_reference(wl: Workload, steps: int, warmup: int):
-    """The reference's executed path: the graph traced by Dynamo and run as eager ops on CPU
-    tensors with every host thread (conductor/compiler/gcu_backend.py:89)."""
-    from oracle import reference_path as rp
+def nbytes(tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if isinstance(t, torch.Tensor))
 
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    inputs = wl.make(0)
+
+# ---------------------------------------------------------------- CPU arm
+def reference_available() -> bool:
+    return os.path.isfile(os.path.join(REF_DIR, "conductor", "__init__.py"))
+
+
+def _import_reference():
+    """Import the UNMODIFIED reference package installed under baseline/_ref (this process must
+    not have imported the new package of the same name).  Returns the `kind` of the arm."""
+    if not reference_available():
+        return "port"
+    os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
+    os.environ.setdefault("CONDUCTOR_LOG_LEVEL", "ERROR")
+    os.environ.setdefault("CONDUCTOR_DEBUG", "0")
+    sys.path.insert(0, REF_DIR)
+    import logging
+
+    logging.disable(logging.CRITICAL)
+    import conductor  # noqa: F401  -- the reference: registers its 'gcu' backend
+
+    if not os.path.realpath(conductor.__file__).startswith(os.path.realpath(REF_DIR)):
+        raise SystemExit(f"expected the reference under {REF_DIR}, imported {conductor.__file__}")
+    try:
+        from conductor.utils.config import get_config
+
+        get_config().debug.enabled = False          # the shipped configuration dumps tensors
+    except Exception:
+        pass
+    return "reference"
+
+
+def time_reference(wl: Workload, steps: int, warmup: int, kind: str):
+    """The reference's execution of the graph: `torch.compile(fn, backend='gcu')` of the reference
+    package on CPU tensors, every host thread (its compile step fails without the Choreo
+    toolchain and it runs the traced graph as eager ops, conductor/compiler/gcu_backend.py:70-89).
+    Without an installed reference, the port of that path under oracle/ stands in."""
+    inputs = wl.host_inputs(0)
     fn = wl.fn
     if wl.module is not None:
         import copy
 
         fn = copy.deepcopy(wl.module).cpu()
     torch._dynamo.reset()
-    compiled = torch.compile(fn, backend=rp.reference_backend)
+    if kind == "reference":
+        compiled = torch.compile(fn, backend="gcu")
+    else:
+        from oracle import reference_path as rp
+
+        compiled = torch.compile(fn, backend=rp.reference_backend)
     with torch.no_grad():
-        for _ in range(max(warmup, 1)):
-            compiled(*inputs)
         t0 = time.perf_counter()
-        for _ in range(steps):
+        compiled(*inputs)
+        first = time.perf_counter() - t0
+        for _ in range(max(warmup - 1, 1)):
+            t0 = time.perf_counter()
             compiled(*inputs)
-        dt = time.perf_counter() - t0
+            est = time.perf_counter() - t0
+        steps = max(3, min(steps, int(8.0 / max(est, 1e-4))))       # bounded: about 8 s per configuration
+        times = []
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            compiled(*inputs)
+            times.append(time.perf_counter() - t0)
     torch._dynamo.reset()
-    ms = dt / steps * 1e3
-    return wl.samples / (dt / steps), ms, torch.get_num_threads()
+    dt = sum(times) / steps
+    return {"value": wl.rows / dt, "unit": "samples/s", "ms_per_step": dt * 1e3, "median_ms": statistics.median(times) * 1e3,
+            "best_ms": min(times) * 1e3, "steps": steps, "first_call_s": first, "dtype": wl.dtype, "workload": wl.name}
 
 
-def reference_arm(args, wl: Workload):
+def reference_arm(args, keys):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 50))
-    value, ms, threads = time_reference(wl, steps, max(args.warmup, 3))
+    kind = _import_reference()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    per = {}
+    for k in keys:
+        wl = Workload(k)
+        r = time_reference(wl, args.steps, max(args.warmup, 3), kind)
+        r["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": torch.get_num_threads(), "kind": kind,
+                             "sample": f"whole batch, {r['steps']} steps"}
+        r["e2e"] = {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+        per[k] = r
+    head = per[HEADLINE if HEADLINE in per else keys[0]]
     line = {
-        "impl": "reference", "metric": "compiled-graph samples/s", "value": value, "unit": "samples/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "path": "reference backend falls back to PyTorch eager on CPU tensors",
-                   "torch": torch.__version__},
-        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
-                         "sample": f"full batch, {steps} steps"},
-        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "impl": "reference", "metric": METRIC, "value": head["value"], "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": head["steps"], "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic",
+        "config": bench_config(head["workload"], keys),
+        "cpu_baseline": head["cpu_baseline"], "e2e": head["e2e"], "gpu_launches": 0,
+        "path": ("the reference package from baseline/_ref, torch.compile(backend='gcu') on CPU tensors" if kind == "reference"
+                 else "port of the reference's executed path (oracle/reference_path.py): baseline/_ref is not installed"),
+        "torch": torch.__version__, "host_threads": torch.get_num_threads(), "per_config": per,
     }
     print(json.dumps(line), flush=True)
 
 
-# ---------------------------------------------------------------- GPU arm
-def gpu_arm(args, wl: Workload):
-    import conductor  # noqa: F401  -- registers 'gcu'
-    from conductor_b200.compiler.gcu_backend import get_gcu_backend
-    from conductor_b200.compiler.loader import load_library
+def bench_config(workload_name: str, keys) -> dict:
+    """The `config` object: identical in both arms."""
+    return {"workload": workload_name, "configs": list(keys),
+            "inputs": "seeded synthetic tensors of the benchmark shapes (no dataset)"}
 
-    load_library()
-    rank, world, local = dist_setup(args.gpus)
+
+def cpu_baseline_child(keys) -> dict:
+    """Time the reference arm in a child process (the reference package shares this package's
+    import name, so it cannot live in this process) and return its per-configuration results."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "10", "--warmup", "3",
+           "--workload", ",".join(keys)]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "OMP_NUM_THREADS")}
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+        for ln in reversed(res.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)["per_config"]
+        return {"error": (res.stderr or res.stdout)[-400:]}
+    except Exception as exc:        # the baseline is reported, never required
+        return {"error": repr(exc)}
+
+
+# ---------------------------------------------------------------- GPU arm
+class Measurement:
+    """Compiles one configuration and times this rank's block of it."""
+
+    def __init__(self, wl: Workload, rank: int, world: int, dev, peaks, args):
+        self.wl, self.rank, self.world, self.dev, self.peaks, self.args = wl, rank, world, dev, peaks, args
+        import conductor  # noqa: F401  -- registers 'gcu'
+        from conductor_b200.compiler.callable import Callable
+        from conductor_b200.compiler.gcu_backend import get_gcu_backend
+        from conductor_b200.compiler.sharding import batch_inputs
+
+        if wl.module is not None:
+            wl.module.to(dev)
+        # compile for the WHOLE configuration (what a user of the backend does), on tensors of the
+        # full shape whose batch-carrying members hold no data yet
+        self.host_full = wl.host_inputs(0)
+        example = [torch.empty(t.shape, dtype=t.dtype, device=dev) if i in wl.user_batch else t.to(dev)
+                   for i, t in enumerate(self.host_full)]
+        torch._dynamo.reset()
+        backend = get_gcu_backend()
+        backend.clear_cache()                              # the only entry afterwards is this graph's plan
+        self.compiled = torch.compile(wl.fn, backend="gcu")
+        with torch.no_grad():
+            self.compiled(*example)
+        torch.cuda.synchronize()
+        plan = list(backend._compiled_functions.values())[-1]
+        plan.record_inputs = True
+        with torch.no_grad():
+            self.compiled(*example)
+        plan.record_inputs = False
+        self.template = list(plan.last_inputs)            # the graph's placeholders (module parameters lifted in)
+        del example
+        self.full_plan = plan
+        self.batch, self.batch_idx = batch_inputs(plan.dag)
+        if self.batch != wl.rows or len(self.batch_idx) != len(wl.user_batch):
+            raise SystemExit(f"{wl.key}: batch inputs {self.batch_idx} of batch {self.batch} do not match the configuration")
+        self.plan = Callable(plan.artifact, batch_size=self.batch)
+        self.kernels_per_pass = sum(1 for l in plan.launches if l.template)
+
+    def placeholders(self, batch_tensors):
+        ph = list(self.template)
+        for i, t in zip(self.batch_idx, batch_tensors):
+            ph[i] = t
+        return tuple(ph)
+
+    # ------------------------------------------------------------ device-resident timing
+    def run(self, start: int, stop: int, clocks) -> dict:
+        wl, dev, args, world = self.wl, self.dev, self.args, self.world
+        rows = stop - start
+        seeded = [self.host_full[i][start:stop].to(dev) for i in wl.user_batch]
+        with torch.no_grad():
+            out0 = self.plan(*self.placeholders(seeded))
+        slot_bytes = nbytes(seeded) + nbytes(out0)
+        pool_n = int(min(MAX_POOL, max(2, -(-POOL_BYTES_MIN // max(slot_bytes, 1)))))
+        gen = torch.Generator(device=dev).manual_seed(1000 * self.rank + 17)
+        pool = [self.placeholders(seeded)] + [self.placeholders(wl.device_batch(rows, dev, gen)) for _ in range(pool_n - 1)]
+        del out0
+        torch.cuda.synchronize()
+
+        # size the captured sequence from a direct run of a few passes
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.no_grad():
+            self.plan(*pool[0])
+            e0.record()
+            for i in range(4):
+                self.plan(*pool[i % pool_n])
+            e1.record()
+        torch.cuda.synchronize()
+        est_ms = max(e0.elapsed_time(e1) / 4, 1e-3)
+        seq_len = int(min(MAX_SEQ, max(pool_n, 4.0 / est_ms)))
+        seq_len = -(-seq_len // pool_n) * pool_n if seq_len > pool_n else pool_n
+        seq_sets = [pool[i % pool_n] for i in range(seq_len)]
+        if args.no_graphs:
+            class _Direct:
+                def __init__(s, plan, sets):
+                    s.plan, s.sets = plan, sets
+
+                def replay(s):
+                    for inp in s.sets:
+                        s.plan(*inp)
+
+            sequence = _Direct(self.plan, seq_sets)
+        else:
+            sequence = self.plan.capture_sequence(seq_sets, keep_outputs="first")
+        sequence.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        sequence.replay()
+        sequence.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        replay_ms = max(e0.elapsed_time(e1) / 2, 1e-3)
+        region = 0.05 if args.quick else REGION_S
+        replays_per_step = max(1, math.ceil(region * 1e3 / (args.steps * replay_ms)))
+        if world > 1:       # every rank must run the same number of passes
+            replays_per_step = int(max_over_ranks(float(replays_per_step), world, dev))
+        passes_per_step = replays_per_step * seq_len
+
+        for _ in range(max(args.warmup, 3) * replays_per_step if not args.quick else 1):
+            sequence.replay()
+        barrier(world)
+        t_wall0 = time.monotonic()
+        e0.record()
+        for _ in range(args.steps * replays_per_step):
+            sequence.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t_wall1 = time.monotonic()
+        own_ms = e0.elapsed_time(e1)
+        dev_ms = max_over_ranks(own_ms, world, dev)
+        barrier(world)
+
+        passes = args.steps * passes_per_step
+        pass_ms = own_ms / passes
+        kern_ms = pass_ms / max(self.kernels_per_pass, 1)
+        if wl.bound == "hbm":
+            alg = wl.bytes_per_row * rows + wl.fixed_bytes
+            achieved = alg / (kern_ms * 1e-3) / 1e9
+            peak, unit = float(self.peaks["hbm_gbs"]), "GB/s"
+        else:
+            alg = wl.flops_per_row * rows
+            achieved = alg / max(self.kernels_per_pass, 1) / (kern_ms * 1e-3) / 1e12
+            peak, unit = float(self.peaks.get("bf16_tflops_sustained", self.peaks["bf16_tflops"])), "TFLOP/s"
+        traffic = TRAFFIC_BYTES.get(wl.key)
+        roofline = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                    "traffic": traffic * rows / wl.rows if traffic else None,
+                    "algorithmic": alg, "kernel_ms": kern_ms, "kernels_per_pass": self.kernels_per_pass,
+                    "launches_timed": passes * self.kernels_per_pass, "region_ms": own_ms,
+                    "vs_nominal": achieved / 8000.0 if wl.bound == "hbm" else achieved / 2250.0}
+        result = {
+            "rows_per_gpu": rows, "passes_per_step": passes_per_step, "ms_per_step": dev_ms / args.steps,
+            "ms_per_pass": dev_ms / passes, "timed_region_ms": dev_ms, "pool_slots": pool_n,
+            "pool_mib": pool_n * slot_bytes >> 20, "passes_per_graph": seq_len,
+            "gpu_launches": passes * self.kernels_per_pass, "roofline": roofline,
+            "clocks": clocks.window(t_wall0, t_wall1) if clocks is not None else None,
+        }
+        del sequence, pool
+        return result
+
+    # ------------------------------------------------------------ all-gather of the outputs
+    def allgather(self, start: int, stop: int) -> dict:
+        """One NCCL all-gather of this configuration's output blocks (outside every roofline
+        figure), and a check that `ShardedCallable` on the whole input reproduces this rank's block."""
+        import torch.distributed as dist
+
+        from conductor_b200.compiler.sharding import ShardedCallable
+
+        wl, dev = self.wl, self.dev
+        gen = torch.Generator(device=dev).manual_seed(4242)           # the same full input on every rank
+        full = self.placeholders(wl.device_batch(wl.rows, dev, gen))
+        sc = ShardedCallable.for_rank(self.full_plan.artifact, self.rank, self.world, device=dev, gather_outputs=True)
+        with torch.no_grad():
+            gathered = sc(*full)
+            local = self.plan(*self.placeholders([full[i][start:stop] for i in self.batch_idx]))
+        ok = bool(torch.equal(gathered[0][start:stop], local[0])) and gathered[0].shape[0] == wl.rows
+        mine = local[0].contiguous()
+        out = mine.new_empty((wl.rows,) + tuple(mine.shape[1:]))
+        even = mine.shape[0] * self.world == wl.rows
+        ms = None
+        if even:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(3):
+                dist.all_gather_into_tensor(out, mine)
+            barrier(self.world)
+            e0.record()
+            for _ in range(10):
+                dist.all_gather_into_tensor(out, mine)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = max_over_ranks(e0.elapsed_time(e1) / 10, self.world, dev)
+        total = out.numel() * out.element_size()
+        return {"ms": ms, "bytes": total, "algbw_gbs": total / (ms * 1e-3) / 1e9 if ms else None,
+                "sharded_callable_matches_local_block": ok}
+
+    # ------------------------------------------------------------ end to end, host tensors
+    def e2e(self, start: int, stop: int) -> dict:
+        """The public call with HOST tensors: every pass copies its inputs from pinned host memory
+        to the device, runs the plan and copies the result back to the host.  One GPU: the callable
+        `torch.compile(fn, backend='gcu')` returns (a module lives on the host, as in the reference;
+        the callable keeps device copies of its parameters).  Several GPUs: this rank's block through
+        the row-count-polymorphic `Callable` that `ShardedCallable` drives."""
+        wl, dev, world = self.wl, self.dev, self.world
+
+        def pinned_block(pos, shift):
+            t = self.host_full[pos][start:stop]
+            return (t.roll(shift, 0) if shift else t).contiguous().pin_memory()
+
+        slots = []
+        if world == 1:
+            if wl.module is not None:
+                import copy
+
+                torch._dynamo.reset()
+                fn = torch.compile(copy.deepcopy(wl.module).cpu(), backend="gcu")
+            else:
+                fn = self.compiled
+            for shift in (0, 1):
+                slots.append(tuple(pinned_block(pos, shift) if pos in wl.user_batch else t.pin_memory()
+                                   for pos, t in enumerate(self.host_full)))
+        else:
+            fn = self.plan
+            for shift in (0, 1):
+                ph = list(self.template)                   # module parameters stay resident on the device
+                if wl.module is None:
+                    assert len(ph) == len(self.host_full)
+                    ph = [t.pin_memory() if pos not in wl.user_batch else None for pos, t in enumerate(self.host_full)]
+                for pos, idx in enumerate(self.batch_idx):
+                    ph[idx] = pinned_block(wl.user_batch[pos], shift)
+                slots.append(tuple(ph))
+        with torch.no_grad():
+            for i in range(2):
+                out = fn(*slots[i % 2])
+            t0 = time.perf_counter()
+            out = fn(*slots[0])
+            est = time.perf_counter() - t0
+            steps = int(max(5, min(2000, math.ceil(REGION_S / max(est, 1e-5)))))
+            if world > 1:
+                steps = int(max_over_ranks(float(steps), world, dev))
+            barrier(world)
+            t0 = time.perf_counter()
+            for i in range(steps):
+                out = fn(*slots[i % 2])
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        dt = max_over_ranks(dt, world, dev)
+        out0 = out[0] if isinstance(out, (tuple, list)) else out
+        assert out0.device.type == "cpu"
+        h2d = nbytes([t for t in slots[0] if t.device.type == "cpu"])
+        d2h = nbytes([out0])
+        return {"value": wl.rows / (dt / steps), "unit": "samples/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": dt / steps * 1e3,
+                "timed_region_ms": dt * 1e3, "pcie_gbs_per_gpu": (h2d + d2h) / (dt / steps) / 1e9}
+
+
+def h2d_bandwidth(dev, world: int) -> dict:
+    """Pinned host -> device copy rate of this rank while every rank copies at once: the ceiling of
+    the end-to-end figures."""
+    n = 256 << 20
+    host = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    dst = torch.empty(n, dtype=torch.uint8, device=dev)
+    dst.copy_(host, non_blocking=True)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(8):
+        dst.copy_(host, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1) / 8, world, dev)
+    return {"h2d_gbs_per_gpu_all_ranks_copying": n / (ms * 1e-3) / 1e9, "bytes": n}
+
+
+def gpu_arm(args, keys):
+    import conductor  # noqa: F401  -- registers 'gcu'
+    from conductor_b200.compiler.loader import load_library
+    from conductor_b200.compiler.sharding import row_partition
+
+    load_library()          # fails loudly when the CUDA library is missing
+    rank, world, local = dist_setup()
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     peaks, peak_kind = load_peaks()
-
-    # ---- inputs: a rotating pool of distinct batches, larger than L2 in total
-    host0 = wl.make(0)
-    batch_bytes = sum(host0[i].numel() * host0[i].element_size() for i in wl.batch_inputs)
-    pool_n = max(2, -(-POOL_BYTES_MIN // batch_bytes))
-    pool_n = min(pool_n, 8)
-    host_pool = [host0] + [wl.make(1000 * rank + s) for s in range(1, pool_n)]
-    if wl.module is not None:
-        wl.module.to(dev)
-    dev_pool = [[t.to(dev) for t in h] for h in host_pool]
-    pinned_pool = [[t.pin_memory() for t in h] for h in host_pool[:2]]
-
-    torch._dynamo.reset()
-    compiled = torch.compile(wl.fn, backend="gcu")
-    with torch.no_grad():
-        first = compiled(*dev_pool[0])
-    torch.cuda.synchronize()
-    backend = get_gcu_backend()
-    plan = list(backend._compiled_functions.values())[-1]
-    kernels_per_step = sum(1 for l in plan.launches if l.template)
-    # the graph's placeholders include lifted module parameters: run every pool entry once
-    # through the public API and keep the placeholder tuples the plan actually received
-    plan.record_inputs = True
-    placeholder_pool = []
-    with torch.no_grad():
-        for inp in dev_pool:
-            compiled(*inp)
-            placeholder_pool.append(plan.last_inputs)
-    plan.record_inputs = False
-    torch.cuda.synchronize()
-    dev_pool = placeholder_pool
-
-    # One CUDA graph per pool slot (one step each) and one "sequence" graph holding SEQ steps
-    # that walk the pool: K timed steps = K // SEQ sequence replays + K % SEQ single replays.
-    class _Direct:
-        def __init__(self, sets):
-            self.sets, self.runs = sets, len(sets)
-
-        def replay(self):
-            for inp in self.sets:
-                plan(*inp)
-
-    seq_len = pool_n * max(1, 32 // pool_n)
-    seq_sets = [dev_pool[i % pool_n] for i in range(seq_len)]
-    if args.no_graphs:
-        singles = [_Direct([inp]) for inp in dev_pool]
-        sequence = _Direct(seq_sets)
-    else:
-        singles = [plan.capture(*inp) for inp in dev_pool]
-        sequence = plan.capture_sequence(seq_sets)
-
-    def run_steps(k: int):
-        for _ in range(k // seq_len):
-            sequence.replay()
-        for i in range(k % seq_len):
-            singles[i % pool_n].replay()
-
-    clocks = ClockSampler(local)
-    if rank == 0:
+    clocks = ClockSampler(local) if rank == 0 else None
+    if clocks is not None:
         clocks.start()
 
-    # ---- value: K steps, inputs resident
-    run_steps(max(args.warmup, 3))
-    barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    run_steps(args.steps)
-    e1.record()
-    torch.cuda.synchronize()
-    dev_ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
-    barrier(world)
-    ms_per_step = dev_ms / args.steps
-    value = wl.samples * world / (ms_per_step * 1e-3)
-
-    if args.quick:          # profiling runs: the timed steps only
-        if rank == 0:
-            clocks.stop()
-            print(json.dumps({"metric": "compiled-graph samples/s", "value": value, "ms_per_step": ms_per_step,
-                              "quick": True, "config": {"workload": wl.name}}), flush=True)
-        return
-
-    # ---- roofline: the dominant kernel, many launches inside one timed region (about 1.5 s)
-    reps = max(4, min(2000, int(1500 / max(ms_per_step * seq_len, 1e-3))))
-    sequence.replay()
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(reps):
-        sequence.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    reps *= seq_len
-    kern_ms = e0.elapsed_time(e1) / reps / max(kernels_per_step, 1)
-    if wl.bound == "hbm":
-        achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
-        peak, unit = float(peaks["hbm_gbs"]), "GB/s"
-    else:
-        achieved = wl.flops / max(kernels_per_step, 1) / (kern_ms * 1e-3) / 1e12
-        peak, unit = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])), "TFLOP/s"
-    roofline = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                "traffic": TRAFFIC_BYTES.get(wl.key), "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
-                "kernel_ms": kern_ms, "launches_timed": reps * kernels_per_step,
-                "vs_nominal_8TBs": achieved / 8000.0 if wl.bound == "hbm" else None}
-
-    # ---- e2e: public API, host tensors in pinned memory, H2D + kernels + D2H every step
-    e2e_steps = max(3, min(args.steps, 200 if batch_bytes < (1 << 28) else 20))
-    if wl.module is not None:
-        # the reference's convention: model and inputs live on the host; the callable keeps
-        # device copies of the parameters and stages the activations every call
-        import copy
-
-        host_module = copy.deepcopy(wl.module).cpu()
+    per = {}
+    t_begin = time.monotonic()
+    for k in keys:
+        wl = Workload(k)
+        m = Measurement(wl, rank, world, dev, peaks, args)
+        start, stop = row_partition(wl.rows, world)[rank]
+        r = m.run(start, stop, clocks)
+        total_rows = wl.rows                     # strong scaling: the fixed configuration over all ranks
+        r["value"] = total_rows * r["passes_per_step"] * args.steps / (r["timed_region_ms"] * 1e-3)
+        r["unit"], r["dtype"], r["workload"], r["scaling"] = "samples/s", wl.dtype, wl.name, "strong"
+        r["roofline"]["peak_source"] = f"MEASURED_PEAKS.json ({peak_kind})"
+        if not args.quick:
+            r["e2e"] = m.e2e(start, stop)
+            if world > 1:
+                r["allgather"] = m.allgather(start, stop)
+                torch.cuda.empty_cache()
+                w = m.run(0, wl.rows, None)      # replicas: every rank the whole configuration
+                r["weak"] = {"value": wl.rows * world * w["passes_per_step"] * args.steps / (w["timed_region_ms"] * 1e-3),
+                             "unit": "samples/s", "ms_per_pass": w["ms_per_pass"], "roofline_frac": w["roofline"]["frac"],
+                             "timed_region_ms": w["timed_region_ms"]}
+        per[k] = r
+        del m
         torch._dynamo.reset()
-        compiled = torch.compile(host_module, backend="gcu")
-    with torch.no_grad():
-        for i in range(3):
-            out = compiled(*pinned_pool[i % 2])
-        barrier(world)
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            out = compiled(*pinned_pool[i % 2])
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-    dt = max_over_ranks(dt, world, dev)
-    out0 = out[0] if isinstance(out, (tuple, list)) else out
-    assert out0.device.type == "cpu"
-    h2d = sum(t.numel() * t.element_size() for t in pinned_pool[0])
-    d2h = out0.numel() * out0.element_size()
-    e2e = {"value": wl.samples * world / (dt / e2e_steps), "unit": "samples/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": dt / e2e_steps * 1e3}
+        torch.cuda.empty_cache()
 
-    clock_info = clocks.stop() if rank == 0 else None
-
-    cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_steps = 20 if wl.key in ("c1", "c2", "c2g", "c4", "c5") else 8
-        v, ms, threads = time_reference(wl, cpu_steps, 3)
-        cpu_baseline = {"value": v, "unit": "samples/s", "cores": threads, "kind": "port",
-                        "sample": f"full batch, {cpu_steps} steps, {ms:.2f} ms/step"}
+    pcie = None if args.quick else h2d_bandwidth(dev, world)
+    if clocks is not None:
+        clocks.stop()
+        clock_info = clocks.window(t_begin, time.monotonic())
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.quick:
+        base = cpu_baseline_child(keys)
+        for k in keys:
+            b = base.get(k)
+            per[k]["cpu_baseline"] = b["cpu_baseline"] | {"ms_per_step": b["ms_per_step"]} if isinstance(b, dict) else {"error": base.get("error")}
 
     if rank == 0:
+        head = per[HEADLINE if HEADLINE in per else keys[0]]
         line = {
-            "metric": "compiled-graph samples/s", "value": value, "unit": "samples/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.name, "samples_per_step_per_gpu": wl.samples, "sharding": f"rows x{world}",
-                       "l2": f"{pool_n} distinct input batches rotate ({pool_n * batch_bytes >> 20} MiB > 126 MB L2)",
-                       "launch": f"CUDA graph replay of the compiled plan, {seq_len} steps per graph"},
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": args.steps * kernels_per_step, "clocks": clock_info,
+            "metric": METRIC, "value": head["value"], "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic",
+            "config": bench_config(head["workload"], keys),
+            "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
+            "gpu_launches": head["gpu_launches"], "clocks": clock_info,
+            "passes_per_step": head["passes_per_step"],
+            "run": {"sharding": f"fixed configuration, rows partitioned over {world} GPU(s), no data-path collective",
+                    "step": "passes_per_step back-to-back passes of the compiled plan, replayed from CUDA graphs",
+                    "l2": "a rotating pool of distinct batches larger than 4x L2 (pool_mib per configuration)",
+                    "timing": "CUDA events on the launching stream, max over ranks"},
+            "host_link": pcie, "per_config": per,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -415,27 +696,25 @@ def gpu_arm(args, wl: Workload):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (None until a capture exists for the workload)
-TRAFFIC_BYTES: dict = {"c1": 235.0e6, "c2": 137.98e6, "c2g": 138.2e6, "c3": 2097.4e6, "c3b": 3180.9e6, "c4": 81.0e6, "c5": 552.2e6}
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="all", help="all, or a comma-separated subset of " + ",".join(ALL))
     ap.add_argument("--impl", default="conductor_b200", choices=["conductor_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--quick", action="store_true", help="timed steps only (for profiler runs)")
+    ap.add_argument("--quick", action="store_true", help="short device-resident regions only (for profiler runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the plan directly instead of replaying a CUDA graph")
     args = ap.parse_args()
-    wl = Workload(args.workload)
+    keys = ALL if args.workload == "all" else [k.strip() for k in args.workload.split(",") if k.strip()]
+    for k in keys:
+        if k not in ALL:
+            raise SystemExit(f"unknown workload {k}")
     if args.impl == "reference":
-        reference_arm(args, wl)
+        reference_arm(args, keys)
     else:
-        gpu_arm(args, wl)
+        gpu_arm(args, keys)
 
 
 if __name__ == "__main__":

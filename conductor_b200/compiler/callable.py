@@ -115,12 +115,7 @@ class Callable:
                         f"input {i} has shape {tuple(t.shape)}, compiled for {buf.shape}",
                         kernel_name=self.artifact.entry_point)
                 env[buf] = self._stage_in(i, t, device) if t.device.type == "cpu" else t
-            rows = None
-            if self.batch_size is not None:
-                for buf, t in zip(dag.inputs, tensors):
-                    if buf.shape and buf.shape[0] == self.batch_size and t.dim() > 0 and t.shape[0] != self.batch_size:
-                        rows = t.shape[0]
-                        break
+            rows = self._rows_given(tensors)
             outputs = None
             if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
                 from .autograd import LinearChainFunction, SoftmaxFunction, differentiable_kind, linear_chain_layers
@@ -160,6 +155,15 @@ class Callable:
         if t_start is not None:
             tracer.trace_execution(self.artifact.entry_point, tensors, list(outputs), (time.perf_counter() - t_start) * 1e3)
         return tuple(outputs)
+
+    def _rows_given(self, tensors) -> Optional[int]:
+        """Row count of the block this call runs on, or None when it is the whole batch."""
+        if self.batch_size is None:
+            return None
+        for buf, t in zip(self.dag.inputs, tensors):
+            if buf.shape and buf.shape[0] == self.batch_size and t.dim() > 0 and t.shape[0] != self.batch_size:
+                return t.shape[0]
+        return None
 
     def _is_shard(self, t: torch.Tensor, buf) -> bool:
         return (self.batch_size is not None and buf.shape and buf.shape[0] == self.batch_size and t.dim() == len(buf.shape)
@@ -224,10 +228,13 @@ class Callable:
         what keeps microsecond-scale plans from being launch-bound."""
         return GraphedCall(self, [tuple(device_tensors)])
 
-    def capture_sequence(self, input_sets) -> "GraphedCall":
+    def capture_sequence(self, input_sets, keep_outputs: str = "all") -> "GraphedCall":
         """Record one run of the plan per entry of `input_sets` (tuples of device tensors)
-        back to back in a single CUDA graph: one driver call replays the whole sequence."""
-        return GraphedCall(self, [tuple(t) for t in input_sets])
+        back to back in a single CUDA graph: one driver call replays the whole sequence.
+        ``keep_outputs="first"`` keeps only the first run's output tensors; the later runs'
+        outputs are released inside the capture, so the graph's memory pool holds two runs'
+        worth of outputs instead of one per run (long sequences of large graphs)."""
+        return GraphedCall(self, [tuple(t) for t in input_sets], keep_outputs=keep_outputs)
 
     # reference API (callable.py:96-152)
     def get_artifact(self) -> CompiledArtifact:
@@ -248,22 +255,30 @@ class GraphedCall:
     output tuple of the first run, ``all_outputs`` one tuple per run; the tensors are reused by
     every replay."""
 
-    def __init__(self, fn: Callable, input_sets):
+    def __init__(self, fn: Callable, input_sets, keep_outputs: str = "all"):
+        if keep_outputs not in ("all", "first"):
+            raise ValueError("keep_outputs is 'all' or 'first'")
         if not input_sets or any(not ts or any(t.device.type != "cuda" for t in ts) for ts in input_sets):
             raise DeviceError("CUDA graphs capture device-resident inputs only")
         self.fn = fn
         self.input_sets = input_sets
         device = input_sets[0][0].device
         envs = [dict(zip(fn.dag.inputs, ts)) for ts in input_sets]
+        rows = [fn._rows_given(ts) for ts in input_sets]
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.device(device), torch.cuda.stream(side):
-            fn._run_plan(dict(envs[0]), device)        # warm-up: lazy initialisation, constants
+            fn._run_plan(dict(envs[0]), device, rows[0])        # warm-up: lazy initialisation, constants
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.device(device), torch.cuda.graph(self.graph):
-            self.all_outputs = [tuple(fn._run_plan(dict(env), device)) for env in envs]
+            if keep_outputs == "all":
+                self.all_outputs = [tuple(fn._run_plan(dict(env), device, r)) for env, r in zip(envs, rows)]
+            else:
+                self.all_outputs = [tuple(fn._run_plan(dict(envs[0]), device, rows[0]))]
+                for env, r in zip(envs[1:], rows[1:]):
+                    fn._run_plan(dict(env), device, r)        # outputs dropped: their blocks are reused by the next run
         self.outputs = self.all_outputs[0]
         self.runs = len(input_sets)
         self.n_kernels = self.runs * sum(1 for l in fn.launches if l.template)

@@ -67,6 +67,16 @@ def batch_inputs(dag) -> tuple[int, list[int]]:
     return batch, picked
 
 
+def _output_spec(dag):
+    """[(shape, dtype)] of the graph's tensor outputs, or None when any of them is unknown."""
+    spec = []
+    for buf in dag.outputs:
+        if buf.shape is None or buf.dtype is None:
+            return None
+        spec.append((tuple(buf.shape), buf.dtype))
+    return spec or None
+
+
 class ShardedCallable:
     """Runs ``run_shard`` on this rank's (or each device's) block of rows.
 
@@ -76,7 +86,8 @@ class ShardedCallable:
 
     def __init__(self, run_shard: TypingCallable, batch: int, batch_input_idx: Sequence[int], *,
                  devices: Optional[Sequence[int]] = None, rank: Optional[int] = None,
-                 world_size: Optional[int] = None, process_group=None, gather_outputs: bool = True):
+                 world_size: Optional[int] = None, process_group=None, gather_outputs: bool = True,
+                 output_spec: Optional[Sequence[tuple]] = None):
         if (devices is None) == (rank is None):
             raise ValueError("give either `devices` (one process, several GPUs) or `rank`/`world_size`")
         self.run_shard = run_shard
@@ -85,6 +96,9 @@ class ShardedCallable:
         self.devices = list(devices) if devices is not None else None
         self.rank, self.world_size, self.group = rank, world_size, process_group
         self.gather_outputs = gather_outputs
+        # [(shape, dtype)] of the full outputs: lets a rank whose block is empty (batch smaller
+        # than the world) still take part in every all-gather with a zero-row contribution
+        self.output_spec = [(tuple(s), d) for s, d in output_spec] if output_spec is not None else None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -97,9 +111,29 @@ class ShardedCallable:
                  for d in range(n_devices)}
 
         def run_shard(inputs, device_index):
-            return plans[device_index](*inputs)
+            # every device works on its own copy of the block: inputs that live elsewhere
+            # (another GPU, or replicated weights on the first one) are moved to it first
+            dev = plans[device_index].default_device
+            moved = [t.to(dev, non_blocking=True) if t.device.type == "cuda" and t.device != dev else t for t in inputs]
+            return plans[device_index](*moved)
 
-        return cls(run_shard, batch, idx, devices=list(range(n_devices)), **kw)
+        return cls(run_shard, batch, idx, devices=list(range(n_devices)), output_spec=_output_spec(artifact.dag), **kw)
+
+    @classmethod
+    def for_rank(cls, artifact, rank: int, world_size: int, graph_module=None, device=None, **kw):
+        """One rank of a ``torch.distributed`` world (one process per GPU): this rank runs block
+        ``rank`` of ``row_partition(batch, world_size)`` on its own device."""
+        from .callable import Callable
+
+        batch, idx = batch_inputs(artifact.dag)
+        plan = Callable(artifact, graph_module, device=device, batch_size=batch)
+
+        def run_shard(inputs, _rank):
+            return plan(*inputs)
+
+        sc = cls(run_shard, batch, idx, rank=rank, world_size=world_size, output_spec=_output_spec(artifact.dag), **kw)
+        sc.plan = plan
+        return sc
 
     # ------------------------------------------------------------------ helpers
     def _slice(self, inputs, start, stop):
@@ -139,13 +173,29 @@ class ShardedCallable:
         start, stop = parts[self.rank]
         local = self.run_shard(self._slice(tensors, start, stop), self.rank) if stop > start else None
         if not self.gather_outputs:
-            return local
+            return local if local is not None else ()
+        if local is None and self.output_spec is None:
+            # raised on every rank that is in this position BEFORE any collective is entered
+            raise ExecutionError(f"rank {self.rank} has no rows (batch {self.batch} over {self.world_size} ranks) and the "
+                                 "output shapes are unknown: build the ShardedCallable with `output_spec`")
         per = parts[0][1] - parts[0][0]
+        even = per * self.world_size == self.batch
+        n_out = len(local) if local is not None else len(self.output_spec)
+        device = tensors[self.batch_input_idx[0]].device
         outs = []
-        n_out = len(local) if local is not None else 1
         for k in range(n_out):
-            mine = local[k]
-            # equal-sized contributions: pad the (possibly shorter) last block
+            if local is not None:
+                mine = local[k]
+            else:
+                shape, dtype = self.output_spec[k]
+                mine = torch.empty((0,) + tuple(shape[1:]), dtype=dtype, device=device)
+            if even:
+                # equal blocks: gather straight into the full tensor, no padding and no concatenation
+                full = mine.new_empty((self.batch,) + tuple(mine.shape[1:]))
+                dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
+                outs.append(full)
+                continue
+            # equal-sized contributions: pad the (possibly shorter or empty) trailing blocks
             padded = mine.new_zeros((per,) + tuple(mine.shape[1:]))
             padded[: mine.shape[0]] = mine
             chunks = [torch.empty_like(padded) for _ in range(self.world_size)]

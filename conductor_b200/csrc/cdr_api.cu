@@ -68,7 +68,7 @@ int sm_count() {
   return g_sm_count[dev];
 }
 
-namespace {
+void clear_error() { g_error[0] = 0; }
 
 int check_lists(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out) {
   if (n_in < 0 || n_out < 0 || (n_in > 0 && !ins) || (n_out > 0 && !outs)) {
@@ -96,6 +96,8 @@ int check_lists(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_o
   }
   return CDR_OK;
 }
+
+namespace {
 
 int check_params(int template_id, const void* params, size_t bytes) {
   size_t want = 0;

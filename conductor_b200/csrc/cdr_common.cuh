@@ -67,9 +67,14 @@ int launch_elementwise(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
 int launch_row_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                       const cdr_reduce_params* p, cudaStream_t stream);
 int full_reduce_workspace(const cdr_tensor* ins, int n_in, size_t* bytes);
+// allow_runtime_instance = false keeps the call on the kernel compiled into the library (no
+// NVRTC compile, no module load: nothing that allocates).
 int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                        const cdr_reduce_params* p, void* ws, size_t ws_bytes,
-                       cudaStream_t stream);
+                       cudaStream_t stream, bool allow_runtime_instance = true);
+// Shape / dtype / rank sanity of the tensor lists every entry point receives.
+int check_lists(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out);
+void clear_error();
 int launch_softmax_fwd(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                        cudaStream_t stream);
 int launch_softmax_bwd(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,

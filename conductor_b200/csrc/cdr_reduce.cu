@@ -557,7 +557,8 @@ int full_reduce_workspace(const cdr_tensor*, int, size_t* bytes) {
 }
 
 int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
-                       const cdr_reduce_params* p, void* ws, size_t ws_bytes, cudaStream_t stream) {
+                       const cdr_reduce_params* p, void* ws, size_t ws_bytes, cudaStream_t stream,
+                       bool allow_runtime_instance) {
   if (!p) { set_error("full_reduce: params is null"); return CDR_ERR_BAD_ARG; }
   if (int rc = validate_ew_program(&p->chain, n_in, n_out)) return rc;
   if (n_out != 1 || n_in < 1) { set_error("full_reduce: needs >=1 input and exactly one output"); return CDR_ERR_BAD_ARG; }
@@ -590,8 +591,9 @@ int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
   int64_t grid = (n + 255) / 256;
   if (grid > full_reduce_grid()) grid = full_reduce_grid();
   CDR_CUDA_TRY(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned int), stream));
-  // vector-shaped problems get a run-time instance of the streaming skeleton
-  {
+  // vector-shaped problems get a run-time instance of the streaming skeleton (its first use
+  // compiles and loads a module, which allocates: callers that must not allocate skip it)
+  if (allow_runtime_instance) {
     bool any16 = false, ok = true;
     for (int i = 0; i < n_in; ++i) any16 |= dtype_size(ins[i].dtype) == 2;
     const int E = any16 ? 8 : 4;
@@ -634,7 +636,10 @@ int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
 //  * All calls on a device share the array.  The ticket is cleared at the start of every
 //    call; partials are overwritten.  Two calls whose kernels overlap on the GPU (different
 //    streams, no ordering between them) race on it: serialise them.
-//  * No cudaMalloc, cudaFree or allocating library call happens in here.
+//  * No cudaMalloc, cudaFree or allocating library call happens in here.  In particular the
+//    call never takes the run-time-instance path of the ordinary entry point (whose first use
+//    per program compiles with NVRTC and loads a module into device memory): it always runs the
+//    kernel that was compiled into this library.
 // =====================================================================================
 namespace cdr {
 namespace {
@@ -668,10 +673,8 @@ extern "C" CDR_API int cdr_full_reduce_noalloc(const cdr_tensor* inputs, int n_i
                                                int n_outputs, const void* params, size_t params_bytes,
                                                void* cuda_stream) {
   using namespace cdr;
-  if (n_inputs < 0 || n_outputs < 0 || (n_inputs > 0 && !inputs) || (n_outputs > 0 && !outputs)) {
-    set_error("full_reduce_noalloc: tensor list is null or has a negative count");
-    return CDR_ERR_BAD_ARG;
-  }
+  clear_error();
+  if (int rc = check_lists(inputs, n_inputs, outputs, n_outputs)) return rc;
   if (!params || params_bytes != sizeof(cdr_reduce_params)) {
     set_error("full_reduce_noalloc: expects a %zu-byte cdr_reduce_params block", sizeof(cdr_reduce_params));
     return CDR_ERR_BAD_ARG;
@@ -687,5 +690,6 @@ extern "C" CDR_API int cdr_full_reduce_noalloc(const cdr_tensor* inputs, int n_i
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
   return launch_full_reduce(inputs, n_inputs, outputs, n_outputs, static_cast<const cdr_reduce_params*>(params),
-                            scratch, kStaticScratchBytes, static_cast<cudaStream_t>(cuda_stream));
+                            scratch, kStaticScratchBytes, static_cast<cudaStream_t>(cuda_stream),
+                            /*allow_runtime_instance=*/false);
 }

@@ -292,7 +292,10 @@ CDR_API int cdr_release_host_arena(int device);
  * CDR_ERR_UNSUPPORTED and cdr_last_error() names the needed and available sizes.
  *
  * inputs / outputs / params are exactly those of cdr_launch(CDR_T_FULL_REDUCE, ...); the
- * caller still owns them.  The first call on a device resolves the array's device address and
+ * caller still owns them.  The call always runs the kernel compiled into the library: it never
+ * takes the run-time-instance path of cdr_launch (whose first use per program compiles with NVRTC
+ * and loads a module, which allocates device memory), so results may differ from cdr_launch's by
+ * fp32 summation order.  The first call on a device resolves the array's device address and
  * should therefore be made before any stream capture begins.  Every call on a device shares the
  * one array: the ticket is cleared at the start of each call, and calls whose kernels could
  * overlap on the GPU (different streams without ordering) race and must be serialised. */

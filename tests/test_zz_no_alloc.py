@@ -6,7 +6,9 @@ tolerate the device-wide synchronisation of an allocation.  For them the library
 of the full reduction whose scratch lives in a fixed array inside the library instead of in a
 workspace the caller would have to allocate.  This test calls that variant through the C ABI, twice
 in a row (every call shares the one array, so the second call runs on whatever the first left
-behind), and compares each result with the ordinary workspace-taking entry point.
+behind), and compares each result with the ordinary workspace-taking entry point and with a
+double-precision sum computed on the host (the two entry points may run different kernels: the
+allocation-free one never compiles or loads a run-time instance, because that would allocate).
 
 The file name sorts last on purpose: a run that stops at the first failure has already run every
 other test."""
@@ -55,6 +57,7 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
     x2 = (torch.randn(64, 50, generator=gen) * 3).to(DEV)          # different size: fewer CTAs, stale partials
     sum_sq = params(abi.ew_program(1, [(EwOp.MUL, 0, 0, 0, 0, torch.float32)], [1]), ReduceOp.SUM)
     mean = params(abi.ew_program(1, [], [0]), ReduceOp.MEAN)
+    exact = {id(sum_sq): lambda t: (t.double() ** 2).sum().item(), id(mean): lambda t: t.double().mean().item()}
     for x, p in ((x1, sum_sq), (x2, mean), (x1, mean)):
         want = torch.empty((), device=DEV)
         with_workspace([x], want, p)
@@ -64,6 +67,31 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
         torch.cuda.synchronize()
         w, g = want.item(), got.item()
         assert abs(g - w) <= F32_TOL * max(1.0, abs(w)), (g, w)
+        host = exact[id(p)](x.cpu())
+        assert abs(g - host) <= F32_TOL * max(1.0, abs(host)), (g, host)
+
+
+def test_noalloc_leaves_the_device_allocation_untouched():
+    """The call must not allocate: the driver's free-memory figure is the same before and after
+    calls on a program and a shape this process has not run before (the ordinary entry point would
+    compile and load a run-time kernel instance for it)."""
+    x = torch.randn(512, 264, device=DEV)                    # vector-shaped: the ordinary path would specialise it
+    p = params(abi.ew_program(1, [(EwOp.ABS, 0, 0, 0, 0, torch.float32)], [1]), ReduceOp.SUM)
+    got = torch.empty((), device=DEV)
+    rc, msg = noalloc([x], got, p)                            # first call on the device resolves the array's address
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    q = params(abi.ew_program(1, [(EwOp.NEG, 0, 0, 0, 0, torch.float32), (EwOp.ABS, 1, 0, 0, 0, torch.float32)], [2]),
+               ReduceOp.SUM)
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        rc, msg = noalloc([x], got, q)
+        assert rc == 0, msg
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    host = x.cpu().double().abs().sum().item()
+    assert abs(got.item() - host) <= F32_TOL * max(1.0, abs(host))
 
 
 def test_noalloc_reports_bad_arguments():
