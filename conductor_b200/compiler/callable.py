@@ -186,12 +186,19 @@ class Callable:
                     t = env[b] = self._constant_on(b, device)
                 ins.append(t)
             if launch.template == 0:                       # alias: reshape, no kernel
-                env[launch.outputs[0]] = ins[0].reshape(self._shard_shape(launch.out_shapes[0], rows))
+                src = ins[0]
+                if not src.is_contiguous():                # a caller's strided tensor: gather it with the copy template
+                    src = env[launch.inputs[0]] = ex.make_contiguous(src)
+                env[launch.outputs[0]] = src.reshape(self._shard_shape(launch.out_shapes[0], rows))
                 continue
             if launch.view_strides is not None:            # transpose / permute / slice: gather the strided view
                 if rows is not None:
                     raise ExecutionError("a plan with layout changes cannot run on a block of its rows", kernel_name=launch.name)
                 src = ins[0]
+                if not src.is_contiguous():
+                    # the view's strides were derived for a contiguous source (every buffer of a plan
+                    # is): a caller's strided tensor is gathered first, once, and reused by later launches
+                    src = env[launch.inputs[0]] = ex.make_contiguous(src)
                 ins = [torch.as_strided(src, launch.out_shapes[0], launch.view_strides, src.storage_offset() + launch.view_offset)]
             outs = None
             if launch.out_view is not None:                # cat: this launch fills one slice of the result

@@ -171,13 +171,14 @@ class ShardedCallable:
 
         parts = row_partition(self.batch, self.world_size)
         start, stop = parts[self.rank]
+        if self.gather_outputs and self.output_spec is None and any(e == s for s, e in parts):
+            # the partition is the same on every rank, so EVERY rank raises here, before any
+            # collective is entered: nobody is left waiting in an all-gather
+            raise ExecutionError(f"some ranks have no rows (batch {self.batch} over {self.world_size} ranks) and the "
+                                 "output shapes are unknown: build the ShardedCallable with `output_spec`")
         local = self.run_shard(self._slice(tensors, start, stop), self.rank) if stop > start else None
         if not self.gather_outputs:
             return local if local is not None else ()
-        if local is None and self.output_spec is None:
-            # raised on every rank that is in this position BEFORE any collective is entered
-            raise ExecutionError(f"rank {self.rank} has no rows (batch {self.batch} over {self.world_size} ranks) and the "
-                                 "output shapes are unknown: build the ShardedCallable with `output_spec`")
         per = parts[0][1] - parts[0][0]
         even = per * self.world_size == self.batch
         n_out = len(local) if local is not None else len(self.output_spec)

@@ -27,8 +27,17 @@
 //               running max grew by more than 2^8 (exact after the final division)
 // TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511.  MMAs of one CTA execute in
 // issue order, so reusing the S_h columns for S_h(j+1) after P_h(j) needs no extra barrier.
-// Causal work is triangular: tiles are numbered heaviest first and dealt to the CTAs in a snake
-// order.  No load is multicast; every wait is bounded and reports through the device status word.
+// Tiles are handed out dynamically: the producer warp takes the next tile index from a counter in
+// global scratch (one atomic per tile, fetched one tile ahead) and publishes it to the other warps
+// through a small shared-memory ring.  The index order keeps the heads that are in flight at any
+// time few -- groups of about (SMs / query tiles per head) heads, so that the K/V of a head is read
+// from HBM once and then served by L2 to the CTAs working on its other query tiles -- and inside
+// a group runs the triangular causal work heaviest first, which leaves only light tiles for the
+// tail.  No load is multicast; every wait is bounded and reports through the device status word.
+// The softmax warps compute P = exp2(s*c - m_ref) for block j > 0 against the reference maximum
+// they already hold, accumulating the block's own maximum on the side; only when that maximum
+// exceeds the reference by more than 2^8 (rare after the first blocks) is the accumulator rescaled
+// and P recomputed.  This takes the row-max pass off the softmax -> MMA critical chain.
 // Measured alternatives that lost: a polling issuer that lets a half run into the next tile (-8 %), 64-key blocks
 // with P double-buffered beside S (-50 %: the tensor core accepts about one MMA per 90 cycles
 // whatever its N, so halving N halves the rate), 16 softmax warps, two threads per row (-17 %), P handed
@@ -58,13 +67,17 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 struct AttnArgs {
   CUtensorMap tmap_q, tmap_k, tmap_v;  // [BH, S, D] each, box 64 x 128 x 1
   void* out;                            // [BH, S, D]
+  unsigned int* next_tile;              // global scratch: tiles handed out beyond the first one per CTA
   int S, BH, n_qtiles;
+  int group_heads, total_tiles;         // heads per scheduling group; BH * n_qtiles
   float scale_log2;                     // scale * log2(e)
   int causal;
   int* status;
 };
 
 constexpr int KV_STAGES = 4;   // one ring for K and V tiles: K_0 V_0 K_1 V_1 ... (4 measured as fast as 5)
+constexpr int TILE_SLOTS = 4;  // ring of tile indices from the producer warp to the MMA and softmax warps
+constexpr int TILE_READERS = 9;  // the MMA warp and the eight softmax warps release a slot
 
 template <int HD>
 struct AttnSmem {
@@ -77,7 +90,8 @@ struct AttnSmem {
 
 // barrier indices; ring barriers are indexed by stage, the others by half
 enum { B_QFULL = 0, B_QEMPTY = 1, B_FULL = 2, B_EMPTY = B_FULL + KV_STAGES, B_SFULL = B_EMPTY + KV_STAGES, B_PFULL = B_SFULL + 2,
-       B_PVDONE = B_PFULL + 2, B_OFREE = B_PVDONE + 2, B_COUNT = B_OFREE + 2 };
+       B_PVDONE = B_PFULL + 2, B_OFREE = B_PVDONE + 2, B_TFULL = B_OFREE + 2, B_TEMPTY = B_TFULL + TILE_SLOTS,
+       B_COUNT = B_TEMPTY + TILE_SLOTS };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -128,10 +142,12 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
 // P = exp2(s*c - m) for one row's 128 scores, packed to 16-bit pairs and stored over the S columns the
 // row just read (`p_taddr`); row sums accumulate in two fp32 lanes.  EMU of every 8 pairs take the polynomial path,
 // the rest the special-function unit.
-template <bool BF16, int EMU>
-__device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2, float neg_m, float& l0, float& l1, uint32_t p_taddr) {
+// With WITH_MAX the maximum of the raw scores is accumulated alongside (four independent chains) and returned.
+template <bool BF16, int EMU, bool WITH_MAX>
+__device__ __forceinline__ float store_p(uint32_t (&sr)[4][32], float scale_log2, float neg_m, float& l0, float& l1, uint32_t p_taddr) {
   const uint64_t scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
   uint64_t lsum4[4] = {pack2(l0, l1), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};   // independent chains
+  float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t pw[16];
@@ -139,6 +155,7 @@ __device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2,
     for (int i = 0; i < 16; ++i) {
       float p0, p1;
       const uint64_t x = fma2(pack2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2);
+      if (WITH_MAX) mx[i & 1] = max3(mx[i & 1], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
       if ((i & 7) < EMU) {
         poly_exp2_pair(x, p0, p1);
       } else {
@@ -153,6 +170,7 @@ __device__ __forceinline__ void store_p(uint32_t (&sr)[4][32], float scale_log2,
     sm100::tmem_st16(p_taddr + c * 16, pw);
   }
   unpack2(add2(add2(lsum4[0], lsum4[1]), add2(lsum4[2], lsum4[3])), l0, l1);
+  return fmaxf(mx[0], mx[1]);
 }
 
 // One (batch*head, 256-query) tile of this CTA's sequence.
@@ -162,16 +180,17 @@ struct Tile {
   int n_iter;    // key blocks the tile loads (max of the two)
 };
 
-// k-th tile of this CTA.  Tiles are numbered heaviest (last query tile) first; round k hands tiles
-// k*G .. k*G+G-1 to the CTAs in ascending order for even k and descending for odd k, which evens out
-// the triangular causal work (C5: 64 block steps on the busiest SM against a mean of 62.3).
-__device__ __forceinline__ bool tile_at(const AttnArgs& a, int k, Tile& t) {
-  const int G = static_cast<int>(gridDim.x), b = static_cast<int>(blockIdx.x);
-  const int total = a.BH * a.n_qtiles;
-  const int idx = k * G + ((k & 1) ? (G - 1 - b) : b);
-  if (k * G >= total || idx >= total) return false;
-  t.q0 = (a.n_qtiles - 1 - idx / a.BH) * BQ;
-  t.bh = idx % a.BH;
+// Tile `idx` of the hand-out order.  Heads are taken in groups of `group_heads`; inside a group the
+// index runs over the query tiles from the last (most key blocks under a causal mask) to the first,
+// heads innermost.  About one group is in flight at a time, so its K/V (2*S*D elements per head)
+// stays in L2 while the group's other query tiles read it.
+__device__ __forceinline__ void decode_tile(const AttnArgs& a, int idx, Tile& t) {
+  const int per_group = a.group_heads * a.n_qtiles;
+  const int grp = idx / per_group, r = idx - grp * per_group;
+  const int left = a.BH - grp * a.group_heads;
+  const int hg = left < a.group_heads ? left : a.group_heads;
+  t.q0 = (a.n_qtiles - 1 - r / hg) * BQ;
+  t.bh = grp * a.group_heads + r % hg;
   const int kv_total = (a.S + BKV - 1) / BKV;
   t.n_iter = 0;
 #pragma unroll
@@ -184,7 +203,6 @@ __device__ __forceinline__ bool tile_at(const AttnArgs& a, int k, Tile& t) {
     t.nblk[h] = n;
     t.n_iter = n > t.n_iter ? n : t.n_iter;
   }
-  return true;
 }
 
 template <int HD, bool BF16>
@@ -194,6 +212,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(bars + B_COUNT + 1);   // TILE_SLOTS tile indices, -1 = no more
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -203,7 +222,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     sm100::prefetch_tensormap(&a.tmap_v);
     for (int i = 0; i < B_COUNT; ++i) {
       const bool per_warp = (i >= B_PFULL && i < B_PFULL + 2) || (i >= B_OFREE && i < B_OFREE + 2);
-      sm100::mbar_init(&bars[i], per_warp ? 4 : 1);   // P and O-free: one arrival per softmax warp of the half
+      const bool slot_free = i >= B_TEMPTY && i < B_TEMPTY + TILE_SLOTS;
+      // P and O-free: one arrival per softmax warp of the half; a tile slot is free once every reader has it
+      sm100::mbar_init(&bars[i], slot_free ? TILE_READERS : per_warp ? 4 : 1);
     }
     sm100::fence_barrier_init();
   }
@@ -225,9 +246,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     if (lane == 0) {
       int ring = 0;
       bool ok = true;
+      // the first tile of a CTA is its block index; later ones come from the global counter, fetched
+      // one tile ahead so that the atomic's latency hides behind the current tile's loads
+      int idx = static_cast<int>(blockIdx.x);
       for (int k = 0; ok; ++k) {
+        const int slot = k % TILE_SLOTS;
+        if (k >= TILE_SLOTS && !sm100::mbar_wait(&bars[B_TEMPTY + slot], (k / TILE_SLOTS - 1) & 1)) { sm100::report_timeout(a.status, 30); break; }
+        const bool valid = idx < a.total_tiles;
+        tile_ring[slot] = valid ? idx : -1;
+        sm100::mbar_arrive(&bars[B_TFULL + slot]);      // release: the index is visible to whoever sees the phase flip
+        if (!valid) break;
         Tile t;
-        if (!tile_at(a, k, t)) break;
+        decode_tile(a, idx, t);
+        idx = static_cast<int>(gridDim.x + atomicAdd(a.next_tile, 1u));
         if (k > 0 && !sm100::mbar_wait(&bars[B_QEMPTY], (k - 1) & 1)) { sm100::report_timeout(a.status, 21); break; }
         const int active = (t.nblk[0] > 0) + (t.nblk[1] > 0);
         sm100::mbar_arrive_expect_tx(&bars[B_QFULL], active * L::TILE_BYTES);
@@ -280,8 +311,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       bool ok = true;
 
       for (int k = 0; ok; ++k) {
+        const int slot = k % TILE_SLOTS;
+        ok = wait_all(&bars[B_TFULL + slot], (k / TILE_SLOTS) & 1, 31);
+        if (!ok) break;
+        const int idx = tile_ring[slot];
+        __syncwarp();
+        if (leader) sm100::mbar_arrive(&bars[B_TEMPTY + slot]);
+        if (idx < 0) break;
         Tile t;
-        if (!tile_at(a, k, t)) break;
+        decode_tile(a, idx, t);
         const int n_iter = t.n_iter;
         ok = wait_all(&bars[B_QFULL], k & 1, 22);
         if (!ok) break;
@@ -374,8 +412,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
+      const int slot = k % TILE_SLOTS;
+      if (!sm100::mbar_wait(&bars[B_TFULL + slot], (k / TILE_SLOTS) & 1)) { sm100::report_timeout(a.status, 32); break; }
+      const int idx = tile_ring[slot];
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&bars[B_TEMPTY + slot]);
+      if (idx < 0) break;
       Tile t;
-      if (!tile_at(a, k, t)) break;
+      decode_tile(a, idx, t);
       const int n_my = t.nblk[g];
       if (n_my == 0) continue;
       const int row0 = t.q0 + g * BH_ROWS;
@@ -392,53 +436,57 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
 
         const int key0 = j * BKV;
         const bool need_mask = (a.causal && key0 + BKV - 1 > row0) || (key0 + BKV > a.S);
-        float bmax = -INFINITY;
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int key = key0 + c * 32 + i;
-              float v = __uint_as_float(sr[c][i]);
-              if (key >= a.S || (a.causal && key > row)) v = -INFINITY;
-              sr[c][i] = __float_as_uint(v);
-              bmax = fmaxf(bmax, v);
+              if (key >= a.S || (a.causal && key > row)) sr[c][i] = __float_as_uint(-INFINITY);   // exp2(-inf) is exactly 0
             }
-        } else {
+        }
+
+        if (j == 0) {
+          // first block of a tile: the reference maximum is this block's own
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains of 3-input max
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
-          bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        }
-        bmax *= a.scale_log2;  // scale > 0: max commutes with the scaling
-
-        // S_h(j) was issued after P_h(j-1) V_(j-1), and MMAs complete in order: O_h is stable here
-        if (j == 0) {
-          m_ref = bmax;
-        } else if (__any_sync(0xffffffffu, bmax > m_ref + kRescaleThreshold)) {
-          const float m_new = fmaxf(m_ref, bmax);
-          const float alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
-          l0 *= alpha;
-          l1 *= alpha;
-          m_ref = m_new;
+          m_ref = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;  // scale > 0: max commutes with the scaling
+          const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+          store_p<BF16, CDR_ATT_EMU, false>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
+        } else {
+          // later blocks: P against the reference maximum already held, the block's own maximum on the
+          // side.  S_h(j) was issued after P_h(j-1) V_(j-1), and MMAs complete in order: O_h is stable here.
+          float l0s = l0, l1s = l1;
+          const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+          const float bmax = store_p<BF16, CDR_ATT_EMU, true>(sr, a.scale_log2, neg_m, l0s, l1s, s_taddr) * a.scale_log2;
+          if (__any_sync(0xffffffffu, bmax > m_ref + kRescaleThreshold)) {
+            // rare: the block's maximum outgrew the reference; rescale the accumulator and redo P
+            const float m_new = fmaxf(m_ref, bmax);
+            const float alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
+            l0 *= alpha;
+            l1 *= alpha;
+            m_ref = m_new;
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t o[32];
-            sm100::tmem_ld32(o_taddr + c * 32, o);
-            sm100::tmem_ld_wait();
+            for (int c = 0; c < HD / 32; ++c) {
+              uint32_t o[32];
+              sm100::tmem_ld32(o_taddr + c * 32, o);
+              sm100::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            sm100::tmem_st32(o_taddr + c * 32, o);
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              sm100::tmem_st32(o_taddr + c * 32, o);
+            }
+            sm100::tmem_st_wait();      // the first P of this block must be in place before it is overwritten
+            const float neg_m2 = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+            store_p<BF16, CDR_ATT_EMU, false>(sr, a.scale_log2, neg_m2, l0, l1, s_taddr);
+          } else {
+            l0 = l0s;
+            l1 = l1s;
           }
         }
-
-        // masked blocks keep the special-function path: exp2(-inf) must be exactly 0
-        const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-        if (need_mask) store_p<BF16, 0>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
-        else store_p<BF16, CDR_ATT_EMU>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
         sm100::tmem_st_wait();
         sm100::tc_fence_before();
         __syncwarp();
@@ -486,7 +534,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
 }  // namespace
 // ---------------------------------------------------------------- host side
 int attention_workspace(const cdr_tensor*, int, size_t* bytes) {
-  *bytes = 0;  // O, the running max and the running sum never leave TMEM / registers
+  // O, the running max and the running sum never leave TMEM / registers; the scratch is the
+  // counter the CTAs take their next tile from (cleared by every launch)
+  *bytes = 256;
   return CDR_OK;
 }
 
@@ -523,7 +573,7 @@ int launch_attention_cfg(const AttnArgs& a, cudaStream_t stream) {
 }  // namespace
 
 int launch_attention(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, const cdr_attn_params* p,
-                     void*, size_t, cudaStream_t stream) {
+                     void* ws, size_t ws_bytes, cudaStream_t stream) {
   if (!p) { set_error("attention: params is null"); return CDR_ERR_BAD_ARG; }
   if (n_in != 3 || n_out != 1) { set_error("attention: expects (q, k, v) and one output"); return CDR_ERR_BAD_ARG; }
   const cdr_tensor& q = ins[0];
@@ -556,6 +606,12 @@ int launch_attention(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, in
   if (!out.data || !aligned16(out.data)) { set_error("attention: output is null or not 16-byte aligned"); return CDR_ERR_MISALIGNED; }
   if (S > 0x7fffffff || BH > 0x7fffffff) { set_error("attention: extent too large"); return CDR_ERR_UNSUPPORTED; }
 
+  if (!ws || ws_bytes < sizeof(unsigned int)) {
+    set_error("attention: workspace of %zu bytes required, got %zu", (size_t)256, ws ? ws_bytes : (size_t)0);
+    return CDR_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(ws) & 3u) { set_error("attention: workspace must be 4-byte aligned"); return CDR_ERR_MISALIGNED; }
+
   AttnArgs a;
   const int bf16 = q.dtype == CDR_BF16;
   if (int rc = make_tensor_map_3d(&a.tmap_q, ins[0].data, bf16, D, S, BH, 64, 128)) return rc;
@@ -565,6 +621,14 @@ int launch_attention(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, in
   a.S = static_cast<int>(S);
   a.BH = static_cast<int>(BH);
   a.n_qtiles = static_cast<int>((S + BQ - 1) / BQ);
+  if (BH * ((S + BQ - 1) / BQ) > 0x3fffffff) { set_error("attention: too many tiles"); return CDR_ERR_UNSUPPORTED; }
+  a.total_tiles = a.BH * a.n_qtiles;
+  // heads per scheduling group: the CTAs in flight cover about one group's tiles
+  a.group_heads = sm_count() / a.n_qtiles;
+  if (a.group_heads < 1) a.group_heads = 1;
+  if (a.group_heads > a.BH) a.group_heads = a.BH;
+  a.next_tile = static_cast<unsigned int*>(ws);
+  CDR_CUDA_TRY(cudaMemsetAsync(a.next_tile, 0, sizeof(unsigned int), stream));
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.causal = p->causal ? 1 : 0;
   a.status = device_status_ptr();

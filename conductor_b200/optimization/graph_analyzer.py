@@ -228,7 +228,33 @@ class GraphAnalyzer:
         out.producer = cnode
         cnode.add_output(out)
         self._buffer_to_node[out] = cnode
+        self._rebind_mutated_operand(node, op_name, out)
         return cnode
+
+    # in-place updates ------------------------------------------------------------------
+    _INPLACE_OPERATORS = ("iadd", "isub", "imul", "itruediv", "ifloordiv", "ipow", "imod", "iand", "ior", "ixor")
+
+    def _rebind_mutated_operand(self, node: torch.fx.Node, op_name: str, out: Buffer) -> None:
+        """``h.relu_()``, ``h += y`` and ``F.relu(h, inplace=True)`` change ``h`` itself, but FX keeps
+        later readers pointing at the node that produced ``h``.  The plan computes the update out
+        of place, so every later reader of the mutated value is redirected to the update's result.
+        Updating a graph input in place (the caller's tensor would have to change) or a view of
+        another value (the base would have to change too) is refused instead of computed wrongly."""
+        raw = str(node.target) if node.op == "call_method" else getattr(node.target, "__name__", str(node.target))
+        inplace = (raw.endswith("_") and not raw.endswith("__")) or raw.strip("_") in self._INPLACE_OPERATORS \
+            or node.kwargs.get("inplace") is True
+        if not inplace or not node.args or not isinstance(node.args[0], torch.fx.Node):
+            return
+        target = node.args[0]
+        if target.op in ("placeholder", "get_attr"):
+            raise UnsupportedOperationError(op_name, "in-place update of a graph input or constant; write the result to a new tensor")
+        from ..codegen.operator_registry import OpType, get_operator_registry
+
+        producer = self._buffer_to_node.get(self._node_to_buffer[target])
+        info = get_operator_registry().get_operation(producer.op_name) if producer is not None else None
+        if info is not None and info.operation_type == OpType.SHAPE and producer.op_name not in ("cat", "concat", "concatenate", "contiguous"):
+            raise UnsupportedOperationError(op_name, "in-place update through a view of another value")
+        self._node_to_buffer[target] = out
 
     def _bind_operand(self, a: Any, cnode: ConductorNode):
         if isinstance(a, torch.fx.Node):

@@ -609,3 +609,29 @@ def test_bf16_chain_with_cast_is_bit_exact():
     want = rp.run_reference(fn, [x, w, b])
     got = compiled(fn)(x.to(DEV), w.to(DEV), b.to(DEV))
     assert got.dtype == torch.float32 and torch.equal(got.cpu(), want)
+
+
+# ---------------------------------------------------------------- strided graph inputs feeding layout changes
+@pytest.mark.parametrize("make_input", [lambda base: base.t(), lambda base: base[:, ::2], lambda base: base[3:40, 5:61]],
+                         ids=["transposed", "every_other_column", "window"])
+@pytest.mark.parametrize("fn", [
+    lambda x: x.t() + 1.0,
+    lambda x: x.permute(1, 0).contiguous() * 2.0,
+    lambda x: x[1:, 2:] - 3.0,
+    lambda x: x.sum(dim=0),
+    lambda x: torch.softmax(x, dim=0),
+    lambda x: x.reshape(-1) * 0.5,
+], ids=["t", "permute", "slice", "sum_dim0", "softmax_dim0", "reshape"])
+def test_strided_input_followed_by_a_layout_change(fn, make_input):
+    """A plan's layout-change launches describe views of CONTIGUOUS buffers; a caller's strided
+    tensor (a transpose, a column subset, a window of a larger tensor) must be gathered first, not
+    re-interpreted with those strides."""
+    gen = torch.Generator().manual_seed(123)
+    base = torch.randn(48, 64, generator=gen)
+    want = fn(make_input(base))
+    x = make_input(base.to(DEV))
+    assert not x.is_contiguous()
+    with torch.no_grad():
+        got = compiled(fn)(x)
+    assert got.shape == want.shape
+    assert_close(got.cpu(), want, 1e-5, "strided input")

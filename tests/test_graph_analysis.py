@@ -161,3 +161,58 @@ def test_buffer_manager_reuse_and_promotion():
     assert not a.overlaps_with(b) and b.can_reuse_memory_with(a)
     assert bm.optimize_buffer_reuse([a, b]) == {b.name: a.name}
     assert a.get_memory_footprint() == 64
+
+
+# ---------------------------------------------------------------- in-place updates
+def _plan_of(fn, inputs):
+    import conductor  # noqa: F401
+    from conductor_b200.compiler.jit_compiler import ChoreoJITCompiler
+
+    box = {}
+
+    def backend(gm, ex):
+        box["artifact"] = ChoreoJITCompiler().compile_graph(gm, ex)
+        return gm.forward
+
+    torch._dynamo.reset()
+    with torch.no_grad():
+        torch.compile(fn, backend=backend)(*inputs)
+    torch._dynamo.reset()
+    return box["artifact"]
+
+
+def test_later_readers_see_an_in_place_update():
+    """`h.relu_()` changes h; the add after it must read the relu's result, not the product."""
+    def f(x):
+        h = x * 2
+        h.relu_()
+        return h + 1
+
+    art = _plan_of(f, [torch.randn(4, 8)])
+    dag = art.dag
+    add = [n for n in dag.nodes if n.op_name == "add"][0]
+    relu = [n for n in dag.nodes if n.op_name in ("relu", "relu_")][0]
+    assert add.inputs[0] is relu.outputs[0]
+    assert dag.output_spec[0] is add.outputs[0]
+
+    def g(x, y):
+        h = x + y
+        h += y                      # operator.iadd
+        return torch.nn.functional.relu(h, inplace=True), h
+
+    dag = _plan_of(g, [torch.randn(4, 8), torch.randn(4, 8)]).dag
+    last = [n for n in dag.nodes if n.op_name == "relu"][0]
+    # both returned values are the mutated h, i.e. the relu's result
+    assert dag.output_spec[0] is last.outputs[0] and dag.output_spec[1] is last.outputs[0]
+
+
+def test_in_place_update_of_a_graph_input_is_refused():
+    from conductor_b200.utils.exceptions import UnsupportedOperationError
+
+    def f(x):
+        x.mul_(2)
+        return x + 1
+
+    with pytest.raises(Exception) as err:
+        _plan_of(f, [torch.randn(4, 8)])
+    assert "in-place" in str(err.value) or isinstance(err.value, UnsupportedOperationError)

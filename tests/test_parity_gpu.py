@@ -635,7 +635,11 @@ def test_full_size_mlp_through_backend(executor):
 def attention(q, k, v, causal, scale=None):
     out = torch.empty_like(q)
     scale = scale if scale is not None else q.shape[-1] ** -0.5
-    abi.launch(Template.ATTENTION, [q, k, v], [out], CdrAttnParams(scale, 1 if causal else 0))
+    p = CdrAttnParams(scale, 1 if causal else 0)
+    # scratch: the counter the CTAs draw their tiles from.  Filled with garbage on purpose -- every
+    # launch clears it itself
+    ws = torch.full((abi.workspace_bytes(Template.ATTENTION, [q, k, v], [out], p),), 0xAB, dtype=torch.uint8, device=q.device)
+    abi.launch(Template.ATTENTION, [q, k, v], [out], p, workspace=ws)
     return out
 
 
@@ -687,6 +691,24 @@ def test_attention_rejects_unsupported(executor):
     assert abi.launch(Template.ATTENTION, [q, q, q], [torch.empty_like(q)], CdrAttnParams(0.1, 0), check=False) == -2
     qf = torch.randn(1, 1, 64, 64, device=DEV)
     assert abi.launch(Template.ATTENTION, [qf, qf, qf], [torch.empty_like(qf)], CdrAttnParams(0.1, 0), check=False) == -2
+    qb = torch.randn(1, 1, 64, 64, device=DEV).bfloat16()           # supported shape, but no scratch given
+    assert abi.launch(Template.ATTENTION, [qb, qb, qb], [torch.empty_like(qb)], CdrAttnParams(0.1, 0), check=False) == -6
+
+
+def test_attention_rescale_path_after_the_first_block(executor):
+    """Scores that keep growing along the key axis: every later block's maximum exceeds the reference
+    the softmax warps hold by far more than the 2^8 slack, so P is recomputed and the accumulator
+    rescaled block after block (the path ordinary data takes only in a tile's first blocks)."""
+    S, D = 640, 64
+    gen = torch.Generator().manual_seed(77)
+    q = torch.ones(1, 1, S, D).bfloat16()
+    ramp = torch.arange(S, dtype=torch.float32).div(8).unsqueeze(-1)              # key i scores about i/8 * D * scale
+    k = (ramp * torch.ones(1, 1, S, D) / D ** 0.5).bfloat16()
+    v = torch.randn(1, 1, S, D, generator=gen).bfloat16()
+    for causal in (True, False):
+        want = scalar.attention_f32(q.float().numpy(), k.float().numpy(), v.float().numpy(), 1.0, causal=causal)
+        out = attention(*cuda(q, k, v), causal=causal, scale=1.0)
+        assert_close(out.float(), torch.from_numpy(want), BF16_TOL, f"growing scores causal={causal}")
 
 
 def test_full_size_attention_through_backend(executor):

@@ -114,6 +114,56 @@ def test_two_gloo_ranks_shard_and_gather():
     assert results == [(0, 6, True, (6,)), (1, 5, True, (5,))]
 
 
+def _worker_small_batch(rank, world, port, out_q):
+    import torch.distributed as dist
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from conductor_b200.compiler.sharding import ShardedCallable
+        from examples import workloads
+
+        x, w, b = workloads.inputs_reduce_mean(1, 64, seed=8)             # one row over two ranks: rank 1 has none
+        ran = []
+
+        def run_shard(inputs, r):
+            ran.append(inputs[0].shape[0])
+            return (workloads.reduce_mean_fusion(*inputs),)
+
+        sc = ShardedCallable(run_shard, 1, [0], rank=rank, world_size=world, gather_outputs=True,
+                             output_spec=[((1,), torch.float32)])
+        (full,) = sc(x, w, b)
+        even = ShardedCallable(run_shard, 4, [0], rank=rank, world_size=world, gather_outputs=True)
+        x4 = workloads.inputs_reduce_mean(4, 64, seed=9)[0]
+        (full4,) = even(x4, w, b)                                           # equal blocks: gathered in place
+        out_q.put((rank, ran, bool(torch.equal(full, workloads.reduce_mean_fusion(x, w, b))),
+                   bool(torch.equal(full4, workloads.reduce_mean_fusion(x4, w, b)))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_without_rows_still_joins_the_gather():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_small_batch, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results == [(0, [1, 2], True, True), (1, [2], True, True)]
+
+
+def test_rank_without_rows_and_unknown_outputs_is_refused_before_any_collective():
+    for rank in (0, 1):           # the rank that does have rows must refuse too, or it would wait alone
+        sc = ShardedCallable(lambda inputs, r: (inputs[0],), 1, [0], rank=rank, world_size=2, gather_outputs=True)
+        with pytest.raises(Exception, match="no rows"):
+            sc(torch.zeros(1, 4))
+
+
 @pytest.mark.gpu
 def test_shard_polymorphic_plan_on_gpu():
     """A plan compiled for the full batch runs on a block of its rows (what every rank does)."""
