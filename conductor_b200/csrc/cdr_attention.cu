@@ -41,12 +41,36 @@
 // Measured alternatives that lost: a polling issuer that lets a half run into the next tile (-8 %), 64-key blocks
 // with P double-buffered beside S (-50 %: the tensor core accepts about one MMA per 90 cycles
 // whatever its N, so halving N halves the rate), 16 softmax warps, two threads per row (-17 %), P handed
-// over in two parts of 64 keys so that half of P.V starts early (-1.5 %).
+// over in two parts of 64 keys so that half of P.V starts early (-1.5 %); sixteen softmax warps with
+// the key columns of a row split over two threads that agree on the reference maximum only in a
+// tile's first block and on a rescale (equal at S=8192, -14 % at S=2048: four warps per scheduler
+// contend for the special-function unit whenever the two halves' exp passes overlap); bf16 packing
+// by integer add + byte permute instead of cvt (no change: the conversion runs on the half-rate
+// ALU pipe, not on the special-function unit); polynomial exp2 for 2/8 or 4/8 of the pairs with
+// sixteen warps (-1 %, -6 %: with half-rate f32x2 arithmetic the cubic costs more issue cycles than
+// the special-function time it frees).
 #include <cuda.h>
 #include <math.h>
 
 #include "cdr_common.cuh"
 #include "cdr_sm100.cuh"
+
+// Cycle accounting for development (-DCDR_ATT_PROF): one thread per role adds the clock64 time
+// it spends in each wait or phase to a per-CTA table in shared memory, written to the tail of the
+// scratch buffer at exit.  Compiled out by default.
+#ifdef CDR_ATT_PROF
+#define PROF_SLOTS 128
+#define PROF_BEGIN(cond) long long prof_t0_ = (cond) ? clock64() : 0
+#define PROF_MARK(cond) if (cond) prof_t0_ = clock64()
+#define PROF_ADD(cond, idx) do { if (cond) { const long long now_ = clock64(); prof_tab[(idx)] += now_ - prof_t0_; prof_t0_ = now_; } } while (0)
+#define PROF_COUNT(cond, idx) do { if (cond) prof_tab[(idx)] += 1; } while (0)
+#else
+#define PROF_SLOTS 0
+#define PROF_BEGIN(cond)
+#define PROF_MARK(cond)
+#define PROF_ADD(cond, idx)
+#define PROF_COUNT(cond, idx)
+#endif
 
 namespace cdr {
 
@@ -85,7 +109,8 @@ struct AttnSmem {
   static constexpr int Q_OFF = 0;                      // 2 halves
   static constexpr int KV_OFF = 2 * TILE_BYTES;        // KV_STAGES tiles
   static constexpr int BAR_OFF = KV_OFF + KV_STAGES * TILE_BYTES;
-  static constexpr size_t TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int PROF_OFF = BAR_OFF + 256;
+  static constexpr size_t TOTAL = BAR_OFF + 256 + PROF_SLOTS * 8 + 1024;
 };
 
 // barrier indices; ring barriers are indexed by stage, the others by half
@@ -215,6 +240,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
   volatile int* tile_ring = reinterpret_cast<volatile int*>(bars + B_COUNT + 1);   // TILE_SLOTS tile indices, -1 = no more
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef CDR_ATT_PROF
+  volatile long long* prof_tab = reinterpret_cast<volatile long long*>(smem + L::PROF_OFF);
+  for (int i = threadIdx.x; i < PROF_SLOTS; i += ATT_THREADS) prof_tab[i] = 0;
+#endif
 
   if (warp == 0 && lane == 0) {
     sm100::prefetch_tensormap(&a.tmap_q);
@@ -249,9 +278,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       // the first tile of a CTA is its block index; later ones come from the global counter, fetched
       // one tile ahead so that the atomic's latency hides behind the current tile's loads
       int idx = static_cast<int>(blockIdx.x);
+      PROF_BEGIN(true);
       for (int k = 0; ok; ++k) {
         const int slot = k % TILE_SLOTS;
+        PROF_ADD(true, 0);
         if (k >= TILE_SLOTS && !sm100::mbar_wait(&bars[B_TEMPTY + slot], (k / TILE_SLOTS - 1) & 1)) { sm100::report_timeout(a.status, 30); break; }
+        PROF_ADD(true, 30);
         const bool valid = idx < a.total_tiles;
         tile_ring[slot] = valid ? idx : -1;
         sm100::mbar_arrive(&bars[B_TFULL + slot]);      // release: the index is visible to whoever sees the phase flip
@@ -259,7 +291,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         Tile t;
         decode_tile(a, idx, t);
         idx = static_cast<int>(gridDim.x + atomicAdd(a.next_tile, 1u));
+        PROF_ADD(true, 0);
         if (k > 0 && !sm100::mbar_wait(&bars[B_QEMPTY], (k - 1) & 1)) { sm100::report_timeout(a.status, 21); break; }
+        PROF_ADD(true, 21);
+        PROF_COUNT(true, 1);
         const int active = (t.nblk[0] > 0) + (t.nblk[1] > 0);
         sm100::mbar_arrive_expect_tx(&bars[B_QFULL], active * L::TILE_BYTES);
         for (int h = 0; h < 2; ++h)
@@ -271,7 +306,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         // ring tile i of the tile: K_j for i = 2j, V_j for i = 2j + 1
         for (int i = 0; i < 2 * t.n_iter; ++i) {
           const int r = ring + i, st = r % KV_STAGES, use = r / KV_STAGES;
+          PROF_ADD(true, 0);
           if (use > 0 && !sm100::mbar_wait(&bars[B_EMPTY + st], (use - 1) & 1)) { sm100::report_timeout(a.status, 20); ok = false; break; }
+          PROF_ADD(true, 20);
           sm100::mbar_arrive_expect_tx(&bars[B_FULL + st], L::TILE_BYTES);
           const void* tmap = (i & 1) ? static_cast<const void*>(&a.tmap_v) : static_cast<const void*>(&a.tmap_k);
 #pragma unroll
@@ -296,8 +333,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       constexpr uint32_t idesc_s = sm100::umma_idesc_f16(BH_ROWS, BKV, BF16, false, false);
       constexpr uint32_t idesc_o = sm100::umma_idesc_f16(BH_ROWS, HD, BF16, false, true);  // V is MN-major
       // every lane waits; the vote makes the outcome provably uniform
+      PROF_BEGIN(leader);
       auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+        PROF_ADD(leader, 2);                       // issue / bookkeeping time between waits
         const bool done = __all_sync(0xffffffffu, sm100::mbar_wait(bar, parity));
+        PROF_ADD(leader, site);
         if (!done && leader) sm100::report_timeout(a.status, site);
         return done;
       };
@@ -365,7 +405,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
                 ok = wait_all(&bars[B_OFREE + h], (tiles_done[h] - 1) & 1, 28);
                 if (!ok) break;
               }
-              ok = wait_all(&bars[B_PFULL + h], blocks[h] & 1, 26);
+              ok = wait_all(&bars[B_PFULL + h], blocks[h] & 1, 26 + h);     // sites 26 and 27 (timeouts); also cycle-accounting slots
               if (!ok) break;
               ++blocks[h];
               sm100::tc_fence_after();
@@ -410,10 +450,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     const uint32_t o_taddr = tmem_base + TMEM_O + g * 128 + lane_sel;
     int n = 0;                           // key blocks consumed so far over all tiles (barrier phases)
     bool ok = true;
+#ifdef CDR_ATT_PROF
+    const bool pw = q == 0 && lane == 0;   // one accounting thread per half
+    const int pb = 64 + 32 * g;
+#endif
+    PROF_BEGIN(pw);
 
     for (int k = 0; ok; ++k) {
       const int slot = k % TILE_SLOTS;
+      PROF_ADD(pw, pb + 0);
       if (!sm100::mbar_wait(&bars[B_TFULL + slot], (k / TILE_SLOTS) & 1)) { sm100::report_timeout(a.status, 32); break; }
+      PROF_ADD(pw, pb + 1);
       const int idx = tile_ring[slot];
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&bars[B_TEMPTY + slot]);
@@ -427,12 +474,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       float m_ref = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
       for (int j = 0; j < n_my; ++j, ++n) {
-        if (!sm100::mbar_wait(&bars[B_SFULL + g], n & 1)) { sm100::report_timeout(a.status, 27); ok = false; break; }
+        PROF_ADD(pw, pb + 0);
+        if (!sm100::mbar_wait(&bars[B_SFULL + g], n & 1)) { sm100::report_timeout(a.status, 33); ok = false; break; }
+        PROF_ADD(pw, pb + 2);
+        PROF_COUNT(pw, pb + 10);
         sm100::tc_fence_after();
         uint32_t sr[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) sm100::tmem_ld32(s_taddr + c * 32, sr[c]);
         sm100::tmem_ld_wait();
+        PROF_ADD(pw, pb + 3);
 
         const int key0 = j * BKV;
         const bool need_mask = (a.causal && key0 + BKV - 1 > row0) || (key0 + BKV > a.S);
@@ -457,13 +508,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
           m_ref = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;  // scale > 0: max commutes with the scaling
           const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
           store_p<BF16, CDR_ATT_EMU, false>(sr, a.scale_log2, neg_m, l0, l1, s_taddr);
+          PROF_ADD(pw, pb + 4);
         } else {
           // later blocks: P against the reference maximum already held, the block's own maximum on the
           // side.  S_h(j) was issued after P_h(j-1) V_(j-1), and MMAs complete in order: O_h is stable here.
           float l0s = l0, l1s = l1;
           const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
           const float bmax = store_p<BF16, CDR_ATT_EMU, true>(sr, a.scale_log2, neg_m, l0s, l1s, s_taddr) * a.scale_log2;
+          PROF_ADD(pw, pb + 5);
           if (__any_sync(0xffffffffu, bmax > m_ref + kRescaleThreshold)) {
+            PROF_COUNT(pw, pb + 11);
             // rare: the block's maximum outgrew the reference; rescale the accumulator and redo P
             const float m_new = fmaxf(m_ref, bmax);
             const float alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
@@ -482,6 +536,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
             sm100::tmem_st_wait();      // the first P of this block must be in place before it is overwritten
             const float neg_m2 = (m_ref == -INFINITY) ? 0.0f : -m_ref;
             store_p<BF16, CDR_ATT_EMU, false>(sr, a.scale_log2, neg_m2, l0, l1, s_taddr);
+            PROF_ADD(pw, pb + 6);
           } else {
             l0 = l0s;
             l1 = l1s;
@@ -491,11 +546,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
         sm100::tc_fence_before();
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive(&bars[B_PFULL + g]);
+        PROF_ADD(pw, pb + 7);
       }
       if (!ok) break;
+      PROF_ADD(pw, pb + 0);
 
       // ---- epilogue: O / l, rounded to the output type; O_h is handed back after the last read
       if (!sm100::mbar_wait(&bars[B_PVDONE + g], (n - 1) & 1)) { sm100::report_timeout(a.status, 29); ok = false; break; }
+      PROF_ADD(pw, pb + 8);
       sm100::tc_fence_after();
       const float inv = 1.0f / (l0 + l1);
       unsigned char* orow = static_cast<unsigned char*>(a.out) + (static_cast<size_t>(t.bh) * a.S + row) * (HD * 2);
@@ -520,6 +578,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
           }
         }
       }
+      PROF_ADD(pw, pb + 9);
     }
   }
 
@@ -529,6 +588,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     sm100::tc_fence_after();
     sm100::tmem_dealloc(tmem_base, ATT_TMEM_COLS);
   }
+#ifdef CDR_ATT_PROF
+  {
+    long long* dst = reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(a.next_tile) + 256) + static_cast<size_t>(blockIdx.x) * PROF_SLOTS;
+    for (int i = threadIdx.x; i < PROF_SLOTS; i += ATT_THREADS) dst[i] = prof_tab[i];
+  }
+#endif
 }
 
 }  // namespace
@@ -536,7 +601,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
 int attention_workspace(const cdr_tensor*, int, size_t* bytes) {
   // O, the running max and the running sum never leave TMEM / registers; the scratch is the
   // counter the CTAs take their next tile from (cleared by every launch)
-  *bytes = 256;
+  *bytes = 256 + static_cast<size_t>(PROF_SLOTS) * 8 * 1024;   // the accounting table exists in development builds only
   return CDR_OK;
 }
 

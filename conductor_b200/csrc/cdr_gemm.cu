@@ -16,6 +16,8 @@
 // share the same weight tile in L2.  No load is multicast; every mbarrier wait is bounded.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "cdr_common.cuh"
 #include "cdr_sm100.cuh"
 
@@ -180,6 +182,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
   __syncthreads();
   sm100::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch)
+  // may run while the previous kernel in the stream drains; nothing below touches global memory
+  // before that kernel has completed and flushed.  No-ops without the launch attribute.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int num_tiles = a.tiles_m * a.tiles_n;
   const int kblocks = (a.K + BK - 1) / BK;
@@ -335,6 +342,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_pair_kernel(cons
   sm100::cluster_sync_all();   // both CTAs' barriers exist before anything signals them remotely
   sm100::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch (see the 1-CTA kernel): set-up above overlaps the previous
+  // kernel's tail, global memory is touched only after it has completed.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int num_tiles = a.tiles_m * a.tiles_n;       // 256 x 256 tiles
   const int kblocks = (a.K + BK - 1) / BK;
@@ -568,6 +579,7 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
     configured = true;
   }
 
+  static const bool pdl = getenv("CDR_DISABLE_PDL") == nullptr;
   if (M >= P_BM && N >= P_BN) {
     // CTA-pair kernel: 256 x 256 tiles, clusters of two CTAs, at most one cluster per TPC.
     // Each CTA stages only 128 of the tile's 256 weight rows: the W box is 64 x 128 here.
@@ -583,13 +595,15 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = P_SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     if (dt == CDR_BF16) CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_pair_kernel<true>, a));
     else CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_pair_kernel<false>, a));
     return CDR_OK;
@@ -600,9 +614,18 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
   int grid = sm_count();
   if (grid > tiles) grid = static_cast<int>(tiles);
-  if (dt == CDR_BF16) gemm_epilogue_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a);
-  else gemm_epilogue_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a);
-  CDR_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (dt == CDR_BF16) CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<true>, a));
+  else CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<false>, a));
   return CDR_OK;
 }
 
