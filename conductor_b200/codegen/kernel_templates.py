@@ -93,7 +93,7 @@ class KernelLaunch:
         ins = ", ".join(b.name for b in self.inputs)
         outs = ", ".join(f"{b.name}:{b.scope.value}" for b in self.outputs)
         tname = {0: "alias", 1: "elementwise", 2: "row_reduce", 3: "softmax_fwd", 4: "softmax_bwd",
-                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce", 8: "layer_norm", 9: "copy"}[self.template]
+                 5: "gemm_epilogue", 6: "attention", 7: "full_reduce", 8: "layer_norm", 9: "copy", 10: "col_sum"}[self.template]
         return f"{outs} = {tname}<{self.name}>({ins})"
 
 

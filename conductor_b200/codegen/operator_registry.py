@@ -51,7 +51,7 @@ class ReduceOp:
 class Template:
     """cdr_template ids."""
 
-    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE, LAYER_NORM, COPY = range(1, 10)
+    ELEMENTWISE, ROW_REDUCE, SOFTMAX_FWD, SOFTMAX_BWD, GEMM_EPILOGUE, ATTENTION, FULL_REDUCE, LAYER_NORM, COPY, COL_SUM = range(1, 11)
 
 
 @dataclass(frozen=True)

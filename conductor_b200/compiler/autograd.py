@@ -11,6 +11,8 @@ Other plans stay forward-only and say so.
 """
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from ..codegen.kernel_templates import KernelLaunch
@@ -18,6 +20,9 @@ from ..codegen.operator_registry import Template
 from ..utils.exceptions import UnsupportedOperationError
 
 
+# Backward launches are built once per (shape, dtype, layout) and reused: the executor keeps the
+# marshalled descriptors on the launch object, so a training step pays for them only the first time.
+@functools.lru_cache(maxsize=256)
 def _softmax_bwd_launch(shape, dtype) -> KernelLaunch:
     return KernelLaunch(Template.SOFTMAX_BWD, "softmax_bwd[autograd]", [], [], None, [tuple(shape)], [dtype])
 
@@ -38,7 +43,7 @@ class SoftmaxFunction(torch.autograd.Function):
         g = grad.contiguous()
         if g.dtype != y.dtype:
             g = g.to(y.dtype)
-        (dx,) = ctx.executor.execute(_softmax_bwd_launch(y.shape, y.dtype), [g, y])
+        (dx,) = ctx.executor.execute(_softmax_bwd_launch(tuple(y.shape), y.dtype), [g, y])
         return dx, None, None
 
 
@@ -67,8 +72,10 @@ def require_differentiable(launches) -> None:
 # as the transposed operands the three products need, so no tensor is ever transposed in memory.
 #   dX = dY @ W              x = dY [M, N],            W [N, K] read as [K'=N, N'=K]   (weight_layout KN)
 #   dW = dY^T @ x            x = dY read as [K'=M, M'=N] (x_layout KM), W = x [M, K] read as [K'=M, N'=K]
-#   db = 1^T @ dY            x = ones [1, M],          W = dY read as [K'=M, N'=N]
+#   db = sum over rows of dY  the column-sum template (HBM-bound: dY is read once; as a product with a row
+#                             of ones the GEMM template ran it on N/256 CTAs and took as long as a full GEMM)
 # and the ReLU mask dZ = dH * (H > 0) is one elementwise launch.
+@functools.lru_cache(maxsize=256)
 def _gemm_launch(name, out_shape, dtype, weight_layout=0, x_layout=0) -> KernelLaunch:
     from ..codegen.kernel_templates import CdrGemmParams
 
@@ -76,6 +83,7 @@ def _gemm_launch(name, out_shape, dtype, weight_layout=0, x_layout=0) -> KernelL
                         [tuple(out_shape)], [dtype])
 
 
+@functools.lru_cache(maxsize=256)
 def _relu_mask_launch(shape, dtype) -> KernelLaunch:
     from ..codegen.kernel_templates import CdrEwInstr, CdrEwParams
     from ..codegen.operator_registry import EwOp
@@ -114,6 +122,11 @@ def linear_chain_layers(launches, dag_inputs):
     return layers
 
 
+@functools.lru_cache(maxsize=256)
+def _col_sum_launch(n: int, dtype) -> KernelLaunch:
+    return KernelLaunch(Template.COL_SUM, "bias_grad[autograd]", [], [], None, [(n,)], [dtype], needs_workspace=True)
+
+
 class LinearChainFunction(torch.autograd.Function):
     """Forward: the plan's GEMM launches.  Backward: GEMM launches with transposed-operand layouts."""
 
@@ -149,14 +162,15 @@ class LinearChainFunction(torch.autograd.Function):
             x2 = x.reshape(-1, K)
             M = g2.shape[0]
             if launch.params.activation == 1:
-                (g2,) = ex.execute(_relu_mask_launch(g2.shape, dt), [g2, h.reshape(-1, N)])
+                (g2,) = ex.execute(_relu_mask_launch(tuple(g2.shape), dt), [g2, h.reshape(-1, N)])
             db = None
             if has_bias:
-                ones = torch.ones(1, M, dtype=dt, device=g2.device)
-                (db,) = ex.execute(_gemm_launch("bias_grad[autograd]", (1, N), dt, weight_layout=1), [ones, g2])
-                db = db.reshape(N)
+                (db,) = ex.execute(_col_sum_launch(N, dt), [g2])
             (dw,) = ex.execute(_gemm_launch("weight_grad[autograd]", (N, K), dt, weight_layout=1, x_layout=1), [g2, x2])
-            (dx,) = ex.execute(_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w])
             param_grads = [dw] + ([db] if has_bias else []) + param_grads
+            if i == 0 and not ctx.needs_input_grad[2]:
+                g = None                     # nobody asked for d/dx of the chain's input: skip that product
+                break
+            (dx,) = ex.execute(_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w])
             g = dx.reshape(x.shape)
         return (None, None, g, *param_grads)

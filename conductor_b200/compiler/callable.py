@@ -6,6 +6,10 @@ Contract kept from the reference: called with the graph's placeholders positiona
 * CUDA tensors: the plan runs on their device and stream, asynchronously; outputs are CUDA tensors.
 * CPU tensors (the reference's only mode, ``host_wrapper.py:374-396``): inputs are staged to the
   GPU through pinned buffers, the plan runs, outputs are copied back; the call is synchronous.
+  A graph whose rows are independent (the same test that batch sharding uses) is run in row
+  chunks on three streams, so that the copy in of chunk i+1, the kernels of chunk i and the copy
+  out of chunk i-1 overlap inside the one call; PCIe is full duplex, so a graph with as much output
+  as input finishes in about half the time of copy-in + kernels + copy-out.
 
 There is no eager fallback: everything in the plan is a hand-written kernel template.
 """
@@ -38,11 +42,15 @@ class Callable:
         # of the batch); outputs with that leading extent are sized to the rows actually given
         self.batch_size = batch_size
         self._executor = None
-        self._const_cache: dict[tuple, torch.Tensor] = {}
+        self._const_cache: dict[tuple, tuple] = {}
         self._pinned: dict[int, torch.Tensor] = {}
         self._param_cache: dict[tuple, tuple] = {}
         self.calls = 0
-        self._warned_no_grad = False
+        self._grad_kind: Optional[str] = None
+        self._grad_layers = None
+        self.chunked_calls = 0                # host calls that ran in overlapped row chunks
+        self._chunk_plan = None               # (batch, batch input indices) or False, decided on first host call
+        self._copy_streams: dict = {}
         # when set, every call stores the placeholder tensors it ran on (graph capture needs the
         # full list, including module parameters Dynamo lifted into placeholders)
         self.record_inputs = False
@@ -65,12 +73,18 @@ class Callable:
         return torch.device("cuda", torch.cuda.current_device())
 
     def _constant_on(self, buf, device) -> torch.Tensor:
+        """Device copy of a constant the plan captured (a module parameter, a ``get_attr`` tensor),
+        refreshed when the source was modified in place since the copy was made."""
         key = (id(buf), device)
-        t = self._const_cache.get(key)
         src = buf.constant_value
-        if t is None:
+        hit = self._const_cache.get(key)
+        if hit is not None and hit[0] == src._version:
+            return hit[1]
+        if src.device == device and src.is_contiguous():
+            t = src.detach()                  # already where it is needed: no copy, always current
+        else:
             t = src.detach().to(device).contiguous()
-            self._const_cache[key] = t
+        self._const_cache[key] = (src._version, t)
         return t
 
     def _stage_in(self, idx: int, t: torch.Tensor, device) -> torch.Tensor:
@@ -107,6 +121,15 @@ class Callable:
                                  kernel_name=self.artifact.entry_point)
         device = self._pick_device(tensors)
         host_mode = any(t.device.type == "cpu" for t in tensors)
+        if host_mode and not (torch.is_grad_enabled() and any(t.requires_grad for t in tensors)):
+            chunks = self._host_chunks(tensors)
+            if chunks is not None:
+                outputs = self._call_host_chunked(tensors, device, chunks)
+                self.calls += 1
+                self.chunked_calls += 1
+                if t_start is not None:
+                    tracer.trace_execution(self.artifact.entry_point, tensors, list(outputs), (time.perf_counter() - t_start) * 1e3)
+                return tuple(outputs)
         env: dict = {}
         with torch.cuda.device(device):
             for i, (buf, t) in enumerate(zip(dag.inputs, tensors)):
@@ -120,20 +143,26 @@ class Callable:
             if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
                 from .autograd import LinearChainFunction, SoftmaxFunction, differentiable_kind, linear_chain_layers
 
-                kind = differentiable_kind(self.launches, dag.inputs) if not host_mode and rows is None else ""
+                if self._grad_kind is None:           # decided once per plan
+                    self._grad_kind = differentiable_kind(self.launches, dag.inputs)
+                    self._grad_layers = linear_chain_layers(self.launches, dag.inputs) if self._grad_kind == "linear_chain" else None
+                kind = self._grad_kind if not host_mode and rows is None else ""
                 if kind == "softmax":
                     # forward through an autograd.Function whose backward is the softmax-backward template
                     outputs = [SoftmaxFunction.apply(env[dag.inputs[0]], self._exec(), self.launches[0])]
                 elif kind == "linear_chain" and len(dag.output_spec) == 1 and dag.output_spec[0] is self.launches[-1].outputs[0]:
-                    layers = linear_chain_layers(self.launches, dag.inputs)
+                    layers = self._grad_layers
                     operands = [env[self.launches[0].inputs[0]]]
                     for l, _ in layers:
                         operands += [env[b] for b in l.inputs[1:]]
                     outputs = [LinearChainFunction.apply(self._exec(), layers, *operands)]
-                elif not self._warned_no_grad:
-                    self._warned_no_grad = True
-                    logger.warning("%s: inputs require grad but this plan has no backward; outputs are detached",
-                                   self.artifact.entry_point)
+                else:
+                    # the reference would run such a graph eagerly and keep autograd working; there is
+                    # no eager path here, and detaching silently would lose the caller's gradients
+                    raise ExecutionError(
+                        "inputs require grad but this compiled graph has no backward (differentiable plans: a row "
+                        "softmax, a chain of linear(+relu) layers); call it under torch.no_grad() or detach the inputs",
+                        kernel_name=self.artifact.entry_point)
             if outputs is None:
                 outputs = self._run_plan(env, device, rows)
             if host_mode:
@@ -170,9 +199,101 @@ class Callable:
                 and tuple(t.shape[1:]) == buf.shape[1:] and 0 < t.shape[0] <= self.batch_size)
 
     def _shard_shape(self, shape, rows):
-        if rows is None or not shape or shape[0] != self.batch_size:
+        batch = self._batch_override if self._batch_override is not None else self.batch_size
+        if rows is None or not shape or shape[0] != batch:
             return tuple(shape)
         return (rows,) + tuple(shape[1:])
+
+    _batch_override: Optional[int] = None     # set while a host call runs in row chunks
+
+    # ------------------------------------------------------------------ chunked host calls
+    def _host_chunks(self, tensors) -> Optional[list]:
+        """Row ranges to run a host-tensor call in, or None when the call runs in one piece: the
+        graph must be row-parallel with every batch input on the host, free of layout-change
+        launches (their views are tied to the full shapes), and large enough to be worth it."""
+        from ..utils.config import get_config
+
+        cfg = get_config().runtime
+        if cfg.host_chunk_bytes <= 0 or self.batch_size is not None:
+            return None
+        if self._chunk_plan is None:
+            from .sharding import batch_inputs
+
+            from ..codegen.operator_registry import Template
+
+            batch, idx = batch_inputs(self.dag)
+            carried = {self.dag.inputs[i] for i in idx}
+            row_local = (0, Template.ELEMENTWISE, Template.ROW_REDUCE, Template.SOFTMAX_FWD, Template.SOFTMAX_BWD,
+                         Template.LAYER_NORM, Template.GEMM_EPILOGUE, Template.ATTENTION)
+            ok = bool(idx) and batch > 1 and all(l.view_strides is None and l.out_view is None and l.template in row_local
+                                                 for l in self.launches)
+            # a product's weight must be whole on every chunk
+            ok = ok and not any(l.template == Template.GEMM_EPILOGUE and any(b in carried for b in l.inputs[1:])
+                                for l in self.launches)
+            ok = ok and all(hasattr(o, "shape") and o.shape and o.shape[0] == batch for o in self.dag.output_spec)
+            self._chunk_plan = (batch, idx) if ok else False
+        if not self._chunk_plan:
+            return None
+        batch, idx = self._chunk_plan
+        if any(tensors[i].device.type != "cpu" or tensors[i].shape[0] != batch for i in idx):
+            return None
+        in_bytes = sum(tensors[i].numel() * tensors[i].element_size() for i in idx)
+        n = min(cfg.host_max_chunks, in_bytes // cfg.host_chunk_bytes, batch)
+        if n < 2:
+            return None
+        per = -(-batch // n)
+        return [(s, min(s + per, batch)) for s in range(0, batch, per)]
+
+    def _streams_for(self, device):
+        st = self._copy_streams.get(device)
+        if st is None:
+            st = self._copy_streams[device] = (torch.cuda.Stream(device=device), torch.cuda.Stream(device=device))
+        return st
+
+    def _call_host_chunked(self, tensors, device, chunks) -> list:
+        batch, idx = self._chunk_plan
+        dag = self.dag
+        with torch.cuda.device(device):
+            compute = torch.cuda.current_stream(device)
+            h2d, d2h = self._streams_for(device)
+            h2d.wait_stream(compute)
+            d2h.wait_stream(compute)
+            shared = {}
+            for i, (buf, t) in enumerate(zip(dag.inputs, tensors)):
+                if i not in idx:                       # weights, row vectors, scalars: staged once
+                    shared[buf] = self._stage_in(i, t, device) if t.device.type == "cpu" else t
+            sources = {}
+            for i in idx:                              # pageable inputs go through a pinned copy, chunk by chunk
+                t = tensors[i].contiguous()
+                sources[i] = t
+            host_out = None
+            self._batch_override = batch
+            try:
+                for (s, e) in chunks:
+                    env = dict(shared)
+                    with torch.cuda.stream(h2d):
+                        for i in idx:
+                            src = sources[i][s:e]
+                            if not src.is_pinned():
+                                pin = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
+                                pin.copy_(src)
+                                src = pin
+                            d = src.to(device, non_blocking=True)
+                            d.record_stream(compute)
+                            env[dag.inputs[i]] = d
+                    compute.wait_stream(h2d)
+                    outs = self._run_plan(env, device, e - s)
+                    if host_out is None:
+                        host_out = [torch.empty((batch,) + tuple(o.shape[1:]), dtype=o.dtype, pin_memory=True) for o in outs]
+                    d2h.wait_stream(compute)
+                    with torch.cuda.stream(d2h):
+                        for h, o in zip(host_out, outs):
+                            o.record_stream(d2h)
+                            h[s:e].copy_(o, non_blocking=True)
+            finally:
+                self._batch_override = None
+            d2h.synchronize()
+        return host_out
 
     def _run_plan(self, env: dict, device, rows: Optional[int] = None) -> list:
         ex = self._exec()

@@ -17,7 +17,7 @@ from ..utils.config import get_config
 from ..utils.logging import get_logger
 from .backend_registry import register_backend
 from .callable import Callable as GCUCallable
-from .jit_compiler import ChoreoJITCompiler
+from .jit_compiler import ChoreoJITCompiler, constants_fingerprint
 
 logger = get_logger(__name__)
 
@@ -49,6 +49,8 @@ class GCUBackend:
         for t in example_inputs or []:
             if isinstance(t, torch.Tensor):
                 text += f"|{tuple(t.shape)}:{t.dtype}:{t.stride()}:{t.device.type}"
+        # the plan holds module parameters and constant tensors by reference: their identity is part of the key
+        text += "|" + constants_fingerprint(graph_module)
         return hashlib.md5(text.encode()).hexdigest()
 
     def clear_cache(self) -> None:

@@ -45,6 +45,30 @@ class CompiledArtifact:
         return bool(self.launches) or bool(self.dag and not self.dag.nodes)
 
 
+def constants_fingerprint(graph_module: torch.fx.GraphModule) -> str:
+    """Identity of every tensor the plan would capture by reference: ``get_attr`` tensors and the
+    parameters of leaf modules reached by ``call_module``.  Two graphs with the same text but
+    different modules (or the same module after a parameter was replaced) must not share a cached
+    plan, because the plan holds these tensors.  The cached plan keeps the tensors alive, so an
+    ``id`` cannot be recycled for another tensor while its entry exists."""
+    parts = []
+    for node in graph_module.graph.nodes:
+        try:
+            if node.op == "get_attr":
+                obj = graph_module
+                for part in str(node.target).split("."):
+                    obj = getattr(obj, part)
+                if isinstance(obj, torch.Tensor):
+                    parts.append(f"{node.target}:{id(obj)}:{tuple(obj.shape)}:{obj.dtype}")
+            elif node.op == "call_module":
+                mod = graph_module.get_submodule(node.target)
+                for name, t in list(mod.named_parameters(recurse=True)) + list(mod.named_buffers(recurse=True)):
+                    parts.append(f"{node.target}.{name}:{id(t)}:{tuple(t.shape)}:{t.dtype}")
+        except AttributeError:
+            parts.append(f"{node.target}:?")
+    return "|".join(parts)
+
+
 class ChoreoJITCompiler:
     """Pipeline driver.  The class keeps the reference's name because ``GCUBackend.jit_compiler``
     is part of the plugin surface; nothing Choreo-related remains inside."""
@@ -70,6 +94,7 @@ class ChoreoJITCompiler:
                 h.update(f"{tuple(t.shape)}:{t.dtype}:{t.stride()}:{t.device.type};".encode())
             else:
                 h.update(f"{t!r};".encode())
+        h.update(constants_fingerprint(graph_module).encode())
         return h.hexdigest()[:16]
 
     # ------------------------------------------------------------------ pipeline

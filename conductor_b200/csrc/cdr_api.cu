@@ -107,6 +107,7 @@ int check_params(int template_id, const void* params, size_t bytes) {
     case CDR_T_FULL_REDUCE: want = sizeof(cdr_reduce_params); break;
     case CDR_T_SOFTMAX_FWD:
     case CDR_T_SOFTMAX_BWD:
+    case CDR_T_COL_SUM:
     case CDR_T_COPY: return CDR_OK;
     case CDR_T_GEMM_EPILOGUE: want = sizeof(cdr_gemm_params); break;
     case CDR_T_ATTENTION: want = sizeof(cdr_attn_params); break;
@@ -236,6 +237,7 @@ int cdr_workspace_bytes(int template_id, const cdr_tensor* inputs, int n_inputs,
   switch (template_id) {
     case CDR_T_FULL_REDUCE: return full_reduce_workspace(inputs, n_inputs, bytes_out);
     case CDR_T_ATTENTION: return attention_workspace(inputs, n_inputs, bytes_out);
+    case CDR_T_COL_SUM: return col_sum_workspace(inputs, n_inputs, outputs, n_outputs, bytes_out);
     default: return CDR_OK;
   }
 }
@@ -262,6 +264,7 @@ int cdr_launch(int template_id, const cdr_tensor* inputs, int n_inputs, const cd
       return launch_attention(inputs, n_inputs, outputs, n_outputs, static_cast<const cdr_attn_params*>(params),
                               workspace, workspace_bytes, s);
     case CDR_T_COPY: return launch_strided_copy(inputs, n_inputs, outputs, n_outputs, s);
+    case CDR_T_COL_SUM: return launch_col_sum(inputs, n_inputs, outputs, n_outputs, workspace, workspace_bytes, s);
     case CDR_T_LAYER_NORM:
       return launch_layer_norm(inputs, n_inputs, outputs, n_outputs, static_cast<const cdr_norm_params*>(params), s);
     default:

@@ -75,6 +75,9 @@ int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
 // Shape / dtype / rank sanity of the tensor lists every entry point receives.
 int check_lists(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out);
 void clear_error();
+int col_sum_workspace(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, size_t* bytes);
+int launch_col_sum(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, void* ws, size_t ws_bytes,
+                   cudaStream_t stream);
 int launch_softmax_fwd(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                        cudaStream_t stream);
 int launch_softmax_bwd(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,

@@ -615,6 +615,166 @@ int launch_full_reduce(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, 
   return CDR_OK;
 }
 
+
+// ---------------------------------------------------------------- column sums: out[n] = sum_m x[m, n]
+// HBM-bound (every element read once).  The [M, N] matrix is cut into strips of 256 columns (a
+// warp reads 32 x 16 bytes of a row: whole 512-byte lines) and chunks of rows; a CTA of 8 warps
+// sums its chunk of its strip in fp32 registers, folds the warps through shared memory and
+// writes one partial row to scratch.  The last CTA of a strip to finish (a ticket per strip) adds
+// the chunk partials in chunk order -- a fixed order, so the result is the same on every run --
+// and rounds to the output type.  Columns past the last whole vector take a scalar path.
+namespace {
+
+constexpr int CS_STRIP = 256, CS_WARPS = 8;
+
+struct ColSumArgs {
+  const void* x;
+  void* out;
+  float* partials;         // [chunks][N]
+  unsigned int* tickets;   // [strips]
+  int64_t M, N;
+  int chunks, rows_per_chunk;
+  int dtype;
+};
+
+template <typename T>
+__device__ __forceinline__ float cs_load(const T* p) { return static_cast<float>(*p); }
+template <>
+__device__ __forceinline__ float cs_load<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <>
+__device__ __forceinline__ float cs_load<__half>(const __half* p) { return __half2float(*p); }
+
+template <typename T>
+__global__ void __launch_bounds__(CS_WARPS * 32) col_sum_kernel(const ColSumArgs a) {
+  constexpr int V = 16 / sizeof(T);                 // elements per 16-byte vector
+  constexpr int PER_LANE = CS_STRIP / 32;            // 8 columns per lane
+  constexpr int VECS = PER_LANE / V;                 // 1 vector (16-bit types) or 2 (fp32)
+  __shared__ float fold[CS_WARPS][CS_STRIP];
+  __shared__ unsigned int last_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int strip = blockIdx.x, chunk = blockIdx.y;
+  const int64_t col0 = static_cast<int64_t>(strip) * CS_STRIP + lane * PER_LANE;
+  const int64_t r0 = static_cast<int64_t>(chunk) * a.rows_per_chunk;
+  int64_t r1 = r0 + a.rows_per_chunk;
+  if (r1 > a.M) r1 = a.M;
+  const T* x = static_cast<const T*>(a.x);
+  float acc[PER_LANE];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) acc[i] = 0.0f;
+  const bool vec = (a.N % V) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && col0 + PER_LANE <= a.N;
+  if (vec) {
+#pragma unroll 4
+    for (int64_t r = r0 + warp; r < r1; r += CS_WARPS) {
+      const uint4* p = reinterpret_cast<const uint4*>(x + r * a.N + col0);
+#pragma unroll
+      for (int v = 0; v < VECS; ++v) {
+        const uint4 q = __ldcs(p + v);
+        const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[v * V + i] += cs_load<T>(e + i);
+      }
+    }
+  } else {
+    for (int64_t r = r0 + warp; r < r1; r += CS_WARPS)
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i)
+        if (col0 + i < a.N) acc[i] += cs_load<T>(x + r * a.N + col0 + i);
+  }
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) fold[warp][lane * PER_LANE + i] = acc[i];
+  __syncthreads();
+  // one thread per column of the strip: the CTA's partial, warps added in index order
+  const int c = threadIdx.x;
+  const int64_t col = static_cast<int64_t>(strip) * CS_STRIP + c;
+  if (col < a.N) {
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < CS_WARPS; ++w) s += fold[w][c];
+    a.partials[static_cast<int64_t>(chunk) * a.N + col] = s;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_flag = atomicAdd(&a.tickets[strip], 1u) == static_cast<unsigned int>(a.chunks - 1);
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  if (col < a.N) {
+    float s = 0.0f;
+    for (int k = 0; k < a.chunks; ++k) s += __ldcg(&a.partials[static_cast<int64_t>(k) * a.N + col]);
+    if (a.dtype == CDR_F32) static_cast<float*>(a.out)[col] = s;
+    else if (a.dtype == CDR_BF16) static_cast<__nv_bfloat16*>(a.out)[col] = __float2bfloat16_rn(s);
+    else static_cast<__half*>(a.out)[col] = __float2half_rn(s);
+  }
+}
+
+// strips x chunks CTAs: enough chunks to fill the device about four times over, at least 32 rows each
+void col_sum_geometry(int64_t M, int64_t N, int* strips, int* chunks, int* rows_per_chunk) {
+  *strips = static_cast<int>((N + CS_STRIP - 1) / CS_STRIP);
+  int64_t want = (static_cast<int64_t>(sm_count()) * 4 + *strips - 1) / *strips;
+  const int64_t most = (M + 31) / 32;
+  if (want > most) want = most;
+  if (want < 1) want = 1;
+  if (want > 1024) want = 1024;
+  *rows_per_chunk = static_cast<int>((M + want - 1) / want);
+  *chunks = static_cast<int>((M + *rows_per_chunk - 1) / *rows_per_chunk);
+}
+
+int col_sum_shape(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, int64_t* M, int64_t* N) {
+  if (n_in != 1 || n_out != 1) { set_error("col_sum: expects one input and one output"); return CDR_ERR_BAD_ARG; }
+  *N = numel(outs[0]);
+  const int64_t n = numel(ins[0]);
+  if (*N <= 0 || n % *N != 0) { set_error("col_sum: the input's element count must be a multiple of the output's"); return CDR_ERR_BAD_ARG; }
+  *M = n / *N;
+  return CDR_OK;
+}
+
+}  // namespace
+
+int col_sum_workspace(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, size_t* bytes) {
+  int64_t M = 0, N = 0;
+  if (int rc = col_sum_shape(ins, n_in, outs, n_out, &M, &N)) return rc;
+  int strips, chunks, rpc;
+  col_sum_geometry(M > 0 ? M : 1, N, &strips, &chunks, &rpc);
+  // [tickets: strips words, rounded up to 256 bytes][partials: chunks x N floats]
+  *bytes = ((static_cast<size_t>(strips) * 4 + 255) & ~static_cast<size_t>(255)) + static_cast<size_t>(chunks) * N * sizeof(float);
+  return CDR_OK;
+}
+
+int launch_col_sum(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, void* ws, size_t ws_bytes,
+                   cudaStream_t stream) {
+  int64_t M = 0, N = 0;
+  if (int rc = col_sum_shape(ins, n_in, outs, n_out, &M, &N)) return rc;
+  const cdr_tensor &x = ins[0], &out = outs[0];
+  if (!is_contiguous(x) || !is_contiguous(out)) { set_error("col_sum: tensors must be contiguous"); return CDR_ERR_BAD_ARG; }
+  if (x.dtype != out.dtype || (x.dtype != CDR_F32 && x.dtype != CDR_BF16 && x.dtype != CDR_F16)) {
+    set_error("col_sum: input and output must share one floating dtype");
+    return CDR_ERR_UNSUPPORTED;
+  }
+  if (!out.data || (M > 0 && !x.data)) { set_error("col_sum: null pointer"); return CDR_ERR_BAD_ARG; }
+  size_t need = 0;
+  col_sum_workspace(ins, n_in, outs, n_out, &need);
+  if (!ws || ws_bytes < need) { set_error("col_sum: workspace of %zu bytes required, got %zu", need, ws ? ws_bytes : (size_t)0); return CDR_ERR_WORKSPACE; }
+  if (reinterpret_cast<uintptr_t>(ws) & 255u) { set_error("col_sum: workspace must be 256-byte aligned"); return CDR_ERR_MISALIGNED; }
+  if (M == 0) {   // an empty sum is zero
+    CDR_CUDA_TRY(cudaMemsetAsync(out.data, 0, static_cast<size_t>(N) * dtype_size(out.dtype), stream));
+    return CDR_OK;
+  }
+  ColSumArgs a{};
+  int strips;
+  col_sum_geometry(M, N, &strips, &a.chunks, &a.rows_per_chunk);
+  const size_t ticket_bytes = (static_cast<size_t>(strips) * 4 + 255) & ~static_cast<size_t>(255);
+  a.x = x.data; a.out = out.data; a.M = M; a.N = N; a.dtype = x.dtype;
+  a.tickets = static_cast<unsigned int*>(ws);
+  a.partials = reinterpret_cast<float*>(static_cast<char*>(ws) + ticket_bytes);
+  CDR_CUDA_TRY(cudaMemsetAsync(a.tickets, 0, static_cast<size_t>(strips) * 4, stream));
+  const dim3 grid(static_cast<unsigned>(strips), static_cast<unsigned>(a.chunks));
+  if (x.dtype == CDR_F32) col_sum_kernel<float><<<grid, CS_WARPS * 32, 0, stream>>>(a);
+  else if (x.dtype == CDR_BF16) col_sum_kernel<__nv_bfloat16><<<grid, CS_WARPS * 32, 0, stream>>>(a);
+  else col_sum_kernel<__half><<<grid, CS_WARPS * 32, 0, stream>>>(a);
+  CDR_CUDA_TRY(cudaGetLastError());
+  return CDR_OK;
+}
+
 }  // namespace cdr
 
 // =====================================================================================

@@ -94,10 +94,14 @@ enum cdr_template {
                              params = cdr_reduce_params; needs workspace                 */
   CDR_T_LAYER_NORM = 8,   /* layer normalisation over the last dim, inputs (x[, weight][, bias]),
                              params = cdr_norm_params                                    */
-  CDR_T_COPY = 9          /* copy a strided view (the input descriptor's strides are honoured; stride 0
+  CDR_T_COPY = 9,         /* copy a strided view (the input descriptor's strides are honoured; stride 0
                              broadcasts) into an output of the same shape: transpose / permute / slice /
                              expand / contiguous().  The output's strides are honoured too (positive,
                              non-overlapping), which writes one part of a concatenation; no params */
+  CDR_T_COL_SUM = 10      /* out[n] = sum over m of x[m, n] for a contiguous x viewed as [M, N] (N = the
+                             output's element count): the bias gradient of a linear layer, `sum(dim=0)`.
+                             fp32 accumulation in a fixed order (deterministic); no params; needs workspace.
+                             The reference has no counterpart: it compiles no backward graphs */
 };
 
 /* ---- elementwise programs -------------------------------------------------

@@ -635,3 +635,121 @@ def test_strided_input_followed_by_a_layout_change(fn, make_input):
         got = compiled(fn)(x)
     assert got.shape == want.shape
     assert_close(got.cpu(), want, 1e-5, "strided input")
+
+
+# ---------------------------------------------------------------- compile cache and debug dump on the GPU
+def test_compile_cache_hit_and_misses_on_gpu():
+    """A second compile of the same graph returns the cached plan and the identical result; a change
+    of dtype or of input strides is a different key (reference: utils/cache.py, jit_compiler.py:443-470,
+    whose hash covers names and shapes only)."""
+    from conductor_b200.compiler.gcu_backend import get_gcu_backend
+
+    backend = get_gcu_backend()
+    backend.clear_cache()
+    a, b, c = (t.to(DEV) for t in wl.inputs_mul_add(128, 256, seed=71))
+    first = compiled(wl.mul_add)(a, b, c)
+    assert len(backend._compiled_functions) == 1
+    plan = next(iter(backend._compiled_functions.values()))
+    calls = plan.calls
+    again = compiled(wl.mul_add)(a, b, c)                       # Dynamo retraces; the backend must not recompile
+    assert len(backend._compiled_functions) == 1 and next(iter(backend._compiled_functions.values())) is plan
+    assert plan.calls == calls + 1 and torch.equal(first, again)
+    half = compiled(wl.mul_add)(a.bfloat16(), b.bfloat16(), c.bfloat16())
+    assert len(backend._compiled_functions) == 2 and half.dtype == torch.bfloat16
+    at = a.t().contiguous().t()                                  # same shape and dtype, other strides
+    strided = compiled(wl.mul_add)(at, b, c)
+    assert len(backend._compiled_functions) == 3 and torch.equal(strided, first)
+    backend.clear_cache()
+
+
+def test_debug_dump_of_a_gpu_compiled_graph_holds_the_source_that_ran(tmp_path):
+    """With a dump directory set, compiling and running a graph whose cluster has no ahead-of-time
+    kernel instance leaves the CUDA source of its run-time instance beside the plan -- the same
+    text the library hands out for that launch -- and the result matches eager
+    (reference: utils/artifacts.py:18-237 keeps the generated DSL and the compiled objects)."""
+    import ctypes
+
+    from conductor_b200.compiler.executor import make_descriptors
+    from conductor_b200.compiler.gcu_backend import get_gcu_backend
+    from conductor_b200.compiler.loader import load_library
+    from conductor_b200.utils.artifacts import get_debug_manager
+    from conductor_b200.utils.config import ConductorConfig, reset_config, set_config
+    from conductor_b200.utils.tracer import reset_tracer
+
+    def chain(x, y):
+        return torch.tanh(x - y) * y
+
+    cfg = ConductorConfig.load()
+    cfg.debug.enabled = True
+    cfg.debug.dump_dir = str(tmp_path / "dump")
+    set_config(cfg)
+    reset_tracer()
+    backend = get_gcu_backend()
+    backend.clear_cache()
+    backend.jit_compiler.clear_cache()
+    try:
+        gen = torch.Generator().manual_seed(72)
+        x, y = torch.randn(256, 512, generator=gen), torch.randn(256, 512, generator=gen)
+        got = compiled(chain)(x.to(DEV), y.to(DEV))
+        assert_close(got.cpu(), chain(x, y), 1e-5, "dumped graph")
+        plan = next(iter(backend._compiled_functions.values()))
+        name = plan.artifact.entry_point
+        mgr = get_debug_manager()
+        names = {p.name for p in mgr.list_artifacts(name)}
+        assert {f"{name}.fx.txt", f"{name}.dag.txt", f"{name}.clusters.json", f"{name}.plan.txt", f"{name}.source0.cu"} <= names, names
+        dumped = mgr.get_instance_source_path(name, 0).read_text()
+        assert "tanh" in dumped and "__global__" in dumped
+        # the library's own answer for the launch that ran
+        launch = plan.launches[0]
+        lib = load_library()
+        ins = make_descriptors([torch.empty(b.shape, dtype=b.dtype) for b in launch.inputs])
+        outs = make_descriptors([torch.empty(s, dtype=d) for s, d in zip(launch.out_shapes, launch.out_dtypes)])
+        buf = ctypes.create_string_buffer(1 << 17)
+        rc = lib.cdr_template_source(launch.template, ins, len(launch.inputs), outs, len(launch.outputs),
+                                     ctypes.cast(ctypes.byref(launch.params), ctypes.c_void_p), ctypes.sizeof(launch.params),
+                                     buf, len(buf), 0)
+        assert rc == 0 and buf.value.decode() == dumped
+    finally:
+        reset_config()
+        reset_tracer()
+        backend.clear_cache()
+        backend.jit_compiler.clear_cache()
+
+
+# ---------------------------------------------------------------- host calls in overlapped row chunks
+@pytest.mark.parametrize("case", ["mul_add", "reduce_mean", "softmax", "mlp", "attention"])
+def test_host_call_in_row_chunks_matches_one_piece(case):
+    """A host-tensor call of a row-parallel graph runs in row chunks on three streams (copy in,
+    kernels, copy out overlapped); the result must be the one-piece result bit for bit, for
+    pinned and for pageable inputs, with a ragged last chunk."""
+    from conductor_b200.utils.config import get_config
+
+    if case == "mul_add":
+        fn, inputs = wl.mul_add, wl.inputs_mul_add(1000, 512, seed=81)
+    elif case == "reduce_mean":
+        fn, inputs = wl.reduce_mean_fusion, wl.inputs_reduce_mean(1000, 1024, seed=82)
+    elif case == "softmax":
+        fn, inputs = wl.softmax_forward, wl.inputs_softmax(777, 2048, seed=83)[:1]
+    elif case == "mlp":
+        fn, inputs = wl.make_mlp(256, 512, 256, seed=84), wl.inputs_mlp(1000, 256, seed=84)
+    else:
+        fn, inputs = wl.causal_attention, wl.inputs_attention(6, 2, 256, 64, seed=85)
+    cfg = get_config().runtime
+    old = cfg.host_chunk_bytes
+    try:
+        cfg.host_chunk_bytes = 0
+        with torch.no_grad():
+            whole = compiled(fn)(*inputs)
+        nbytes = inputs[0].numel() * inputs[0].element_size()
+        cfg.host_chunk_bytes = max(1, nbytes // 5)                  # five chunks, the last one shorter
+        with torch.no_grad():
+            f = compiled(fn)
+            chunked = f(*inputs)
+            pinned = f(*[t.pin_memory() for t in inputs])
+        assert chunked.device.type == "cpu" and torch.equal(chunked, whole) and torch.equal(pinned, whole)
+        from conductor_b200.compiler.gcu_backend import get_gcu_backend
+
+        plan = list(get_gcu_backend()._compiled_functions.values())[-1]
+        assert plan.chunked_calls == 2, (case, plan.chunked_calls)
+    finally:
+        cfg.host_chunk_bytes = old

@@ -329,6 +329,33 @@ def test_full_reduce_with_workspace(executor):
         assert_close(out, (x.double() * x.double()).sum().float(), F32_TOL, "sum of squares")
 
 
+@pytest.mark.parametrize("M,N,dtype", [(8192, 4096, torch.bfloat16), (777, 1031, torch.float32), (5, 8, torch.float16),
+                                       (1, 300, torch.bfloat16), (4096, 256, torch.float32), (33, 7, torch.bfloat16),
+                                       (0, 64, torch.float32)])
+def test_col_sum_against_fp64_host_sum(executor, M, N, dtype):
+    """out[n] = sum_m x[m, n] (the bias gradient of a linear layer): fp32 accumulation in a fixed
+    order, compared with a double-precision sum on the host; two runs are bit-identical."""
+    gen = torch.Generator().manual_seed(M * 131 + N)
+    x = torch.randn(M, N, generator=gen).to(dtype)
+    want = x.double().sum(0)
+    xd = x.to(DEV)
+    outs = []
+    for _ in range(2):
+        out = torch.full((N,), float("nan"), dtype=dtype, device=DEV)
+        ws = torch.full((abi.workspace_bytes(Template.COL_SUM, [xd], [out]),), 0xCD, dtype=torch.uint8, device=DEV)
+        abi.launch(Template.COL_SUM, [xd], [out], workspace=ws)
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1])
+    tol = 1e-5 if dtype == torch.float32 else BF16_TOL
+    scale = max(1.0, float(want.abs().max())) if M else 1.0
+    assert float((outs[0].double() - want).abs().max()) <= tol * scale
+    # shape checks: an output whose size does not divide the input, a missing workspace
+    bad = torch.empty(N + 1, dtype=dtype, device=DEV)
+    if M:
+        assert abi.launch(Template.COL_SUM, [xd], [bad], workspace=ws, check=False) == -1
+    assert abi.launch(Template.COL_SUM, [xd], [out], check=False) == -6
+
+
 # ---------------------------------------------------------------- K3 softmax
 def test_softmax_golden(executor):
     g = load_golden("c3_softmax")

@@ -124,3 +124,33 @@ def test_validation_failure_is_a_compilation_error():
     comp = ChoreoJITCompiler()
     with pytest.raises((CompilationError, ValueError)):
         comp.compile_graph(traced(), [torch.randn(4, 4)])            # wrong number of example inputs
+
+
+def test_cache_key_covers_the_constants_a_plan_captures():
+    """Two structurally identical modules (same graph text, same target names) hold different
+    weights: the plan captures the weights by reference, so they must not share a cache entry."""
+    import torch.nn as nn
+
+    from conductor.compiler.gcu_backend import GCUBackend
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = nn.Linear(16, 16)
+
+        def forward(self, x):
+            return self.fc(x)
+
+    g1, g2 = fx.symbolic_trace(Net()), fx.symbolic_trace(Net())
+    assert str(g1.graph) == str(g2.graph)
+    x = [torch.randn(4, 16)]
+    comp = ChoreoJITCompiler()
+    assert comp._generate_graph_hash(g1, x) != comp._generate_graph_hash(g2, x)
+    assert comp._generate_graph_hash(g1, x) == comp._generate_graph_hash(g1, x)
+    be = GCUBackend()
+    assert be._compute_graph_hash(g1, x) != be._compute_graph_hash(g2, x)
+    a1, a2 = comp.compile_graph(g1, x), comp.compile_graph(g2, x)
+    assert a1 is not a2
+    w1 = [b.constant_value for b in a1.dag.buffers if getattr(b, "constant_value", None) is not None]
+    w2 = [b.constant_value for b in a2.dag.buffers if getattr(b, "constant_value", None) is not None]
+    assert w1 and w2 and w1[0] is not w2[0]
