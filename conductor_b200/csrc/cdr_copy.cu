@@ -10,8 +10,11 @@
 // `cat` writes each part into its slice of the result that way.
 // HBM-bound.  When the view's innermost dimension is contiguous in memory and a whole number of
 // 16-byte vectors (the head-dimension case: [B, S, H, D] -> [B, H, S, D]), every thread moves one
-// 16-byte vector with streaming accesses; otherwise elements are gathered one by one (reads
-// uncoalesced when the innermost stride is not 1).
+// 16-byte vector with streaming accesses.  When the view's unit-stride dimension is NOT its
+// innermost one (a transpose: x.t(), permute(0, 2, 1), [B, S, H, D] -> [B, H, D, S]) a tile of
+// (that dimension) x (innermost dimension) goes through shared memory, so that both the reads
+// and the writes run along memory; every other dimension is a batch index.  Anything else is
+// gathered element by element (reads uncoalesced when no dimension of the view has stride 1).
 #include "cdr_common.cuh"
 
 namespace cdr {
@@ -60,6 +63,56 @@ __global__ void __launch_bounds__(256) strided_copy_kernel(const __grid_constant
   }
 }
 
+// ---- transpose through shared memory --------------------------------------------------------
+struct TransposeArgs {
+  const unsigned char* in;
+  unsigned char* out;
+  int32_t rank, pdim;            // pdim: the view dimension whose input stride is one element
+  int64_t shape[CDR_MAX_RANK];
+  int64_t stride[CDR_MAX_RANK];  // input strides in bytes
+  int64_t ostride[CDR_MAX_RANK]; // output strides in bytes
+  int64_t tiles_p, tiles_l;      // tiles along pdim and along the innermost dimension
+};
+
+// T: an unsigned integer of the element's size.  TILE x TILE elements per CTA of 256 threads; the
+// shared tile is padded by one 32-bit word per row, so column reads hit distinct banks.
+template <typename T, int TILE>
+__global__ void __launch_bounds__(256) transpose_tile_kernel(const __grid_constant__ TransposeArgs a) {
+  constexpr int PAD = sizeof(T) >= 4 ? 1 : 4 / sizeof(T);
+  constexpr int ROWS = 256 / TILE;          // tile rows handled per pass
+  __shared__ T tile[TILE][TILE + PAD];
+  const int last = a.rank - 1;
+  int64_t b = blockIdx.x;
+  const int64_t tl = b % a.tiles_l; b /= a.tiles_l;
+  const int64_t tp = b % a.tiles_p; b /= a.tiles_p;
+  int64_t in_base = 0, out_base = 0;       // the batch dimensions: every one but pdim and the innermost
+#pragma unroll 1
+  for (int d = last - 1; d >= 0; --d) {
+    if (d == a.pdim) continue;
+    const int64_t q = b / a.shape[d], r = b - q * a.shape[d];
+    in_base += r * a.stride[d];
+    out_base += r * a.ostride[d];
+    b = q;
+  }
+  const int64_t p0 = tp * TILE, l0 = tl * TILE;
+  const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
+  // read: consecutive threads along pdim (unit stride in memory), rows of the tile along the innermost dimension
+#pragma unroll
+  for (int y = ty; y < TILE; y += ROWS) {
+    const int64_t pi = p0 + tx, li = l0 + y;
+    if (pi < a.shape[a.pdim] && li < a.shape[last])
+      tile[y][tx] = *reinterpret_cast<const T*>(a.in + in_base + pi * a.stride[a.pdim] + li * a.stride[last]);
+  }
+  __syncthreads();
+  // write: consecutive threads along the innermost dimension (unit stride in the output)
+#pragma unroll
+  for (int y = ty; y < TILE; y += ROWS) {
+    const int64_t pi = p0 + y, li = l0 + tx;
+    if (pi < a.shape[a.pdim] && li < a.shape[last])
+      *reinterpret_cast<T*>(a.out + out_base + pi * a.ostride[a.pdim] + li * a.ostride[last]) = tile[tx][y];
+  }
+}
+
 }  // namespace
 
 int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, cudaStream_t stream) {
@@ -96,6 +149,35 @@ int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs,
   bool vec = x.rank > 0 && x.stride[last] == 1 && out.stride[last] == 1 && x.shape[last] % per_vec == 0 &&
              aligned16(x.data) && aligned16(out.data);
   for (int d = 0; d < last; ++d) vec &= a.shape[d] == 1 || ((a.stride[d] % 16) == 0 && (a.ostride[d] % 16) == 0);
+  if (!vec && x.rank >= 2 && out.stride[last] == 1 && x.stride[last] != 1 && x.shape[last] > 1) {
+    // a transpose: some other dimension of the view runs along memory in the input
+    int pdim = -1;
+    for (int d = last - 1; d >= 0; --d)
+      if (x.stride[d] == 1 && x.shape[d] > 1) { pdim = d; break; }
+    if (pdim >= 0) {
+      TransposeArgs t{};
+      t.in = a.in; t.out = a.out; t.rank = a.rank; t.pdim = pdim;
+      for (int d = 0; d < a.rank; ++d) { t.shape[d] = a.shape[d]; t.stride[d] = a.stride[d]; t.ostride[d] = a.ostride[d]; }
+      const int tile = 64;   // 64 x 64 elements per CTA: 8-32 KB in flight, enough CTAs per SM to cover the HBM latency
+      t.tiles_p = (x.shape[pdim] + tile - 1) / tile;
+      t.tiles_l = (x.shape[last] + tile - 1) / tile;
+      int64_t batch = 1;
+      for (int d = 0; d < last; ++d)
+        if (d != pdim) batch *= x.shape[d];
+      const int64_t blocks = batch * t.tiles_p * t.tiles_l;
+      if (blocks > 0 && blocks < (int64_t{1} << 31)) {
+        const unsigned g = static_cast<unsigned>(blocks);
+        switch (esz) {
+          case 1: transpose_tile_kernel<uint8_t, 64><<<g, 256, 0, stream>>>(t); break;
+          case 2: transpose_tile_kernel<uint16_t, 64><<<g, 256, 0, stream>>>(t); break;
+          case 4: transpose_tile_kernel<uint32_t, 64><<<g, 256, 0, stream>>>(t); break;
+          default: transpose_tile_kernel<uint64_t, 64><<<g, 256, 0, stream>>>(t); break;
+        }
+        CDR_CUDA_TRY(cudaGetLastError());
+        return CDR_OK;
+      }
+    }
+  }
   if (vec) {
     a.unit_bytes = 16;
     a.shape[last] = x.shape[last] / per_vec;

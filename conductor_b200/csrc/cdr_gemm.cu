@@ -14,6 +14,12 @@
 // The accumulator is double buffered in TMEM (2 x 256 columns), so the epilogue of tile i runs
 // under the MMAs of tile i+1.  Tiles are walked M-fastest so that concurrently running CTAs
 // share the same weight tile in L2.  No load is multicast; every mbarrier wait is bounded.
+// Measured and dropped: stream-K scheduling of the CTA-pair kernel for shapes whose last wave of
+// tiles is badly filled (C4's second layer: 128 tiles on 74 pairs) -- equal shares of the
+// (tile, k-block) sequence per pair, split tiles completed through fp32 partial tiles in scratch.
+// It made the two-layer step 8 % slower (130 against 120 us): the pairs no longer walk the
+// k-blocks of a shared weight tile in step, and the partial tiles add an L2 round trip to the
+// epilogue.  Programmatic dependent launch between the two layers is in place and is neutral.
 #include <cuda.h>
 
 #include <cstdlib>

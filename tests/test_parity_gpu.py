@@ -2,6 +2,7 @@
 vectors, the C oracle and the reference's executed path (eager on CPU) on identical seeded
 inputs.  Tolerances are the benchmark's: bit-exact for integer work and for the fp32/bf16
 +,-,*,/ chains, max-abs/rel <= 1e-5 for fp32 transcendental/reduction results, <= 2e-2 bf16."""
+import ctypes
 import math
 
 import numpy as np
@@ -13,6 +14,7 @@ from abi_util import COL, FULL, ROW, SCALAR
 from conftest import assert_close, bf16_bits_to_tensor, load_golden, tensor_to_bf16_bits
 from conductor_b200.codegen.kernel_templates import CdrReduceParams
 from conductor_b200.codegen.operator_registry import EwOp, ReduceOp, Template
+from conductor_b200.compiler.loader import load_library
 from oracle import reference_path as rp
 from oracle import scalar
 
