@@ -70,6 +70,15 @@ class CdrAttnParams(ctypes.Structure):
     _fields_ = [("scale", ctypes.c_float), ("causal", ctypes.c_int32)]
 
 
+class CdrLaunchItem(ctypes.Structure):
+    """``cdr_launch_item``: the arguments of one ``cdr_launch`` call, for ``cdr_launch_many``."""
+
+    _fields_ = [("template_id", ctypes.c_int32), ("n_inputs", ctypes.c_int32), ("n_outputs", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("inputs", ctypes.c_void_p), ("outputs", ctypes.c_void_p),
+                ("params", ctypes.c_void_p), ("params_bytes", ctypes.c_size_t), ("workspace", ctypes.c_void_p),
+                ("workspace_bytes", ctypes.c_size_t)]
+
+
 # ---------------------------------------------------------------- launch description
 @dataclass
 class KernelLaunch:

@@ -135,13 +135,15 @@ class LinearChainFunction(torch.autograd.Function):
         ctx.executor, ctx.layers = executor, layers
         acts = [x.detach()]
         it = iter(params)
-        weights = []
+        weights, steps = [], []
         for launch, has_bias in layers:
             w = next(it).detach()
             ins = [acts[-1], w] + ([next(it).detach()] if has_bias else [])
-            (h,) = executor.execute(launch, ins)
+            h = torch.empty(launch.out_shapes[0], dtype=launch.out_dtypes[0], device=x.device)
+            steps.append((launch, ins, [h]))
             acts.append(h)
             weights.append(w)
+        executor.execute_many(steps)          # the whole chain in one call into the library
         ctx.save_for_backward(*acts, *weights)
         ctx.n_layers = len(layers)
         return acts[-1]
@@ -152,8 +154,14 @@ class LinearChainFunction(torch.autograd.Function):
         saved = ctx.saved_tensors
         acts, weights = saved[:n + 1], saved[n + 1:]
         dt = acts[0].dtype
-        g = grad.contiguous().to(dt)
+        dev = acts[0].device
+        g = grad if grad.dtype == dt and grad.is_contiguous() else grad.contiguous().to(dt)
         param_grads = []
+        steps = []
+
+        def out(shape):
+            return torch.empty(shape, dtype=dt, device=dev)
+
         for i in range(n - 1, -1, -1):
             launch, has_bias = layers[i]
             w, x, h = weights[i], acts[i], acts[i + 1]
@@ -162,15 +170,21 @@ class LinearChainFunction(torch.autograd.Function):
             x2 = x.reshape(-1, K)
             M = g2.shape[0]
             if launch.params.activation == 1:
-                (g2,) = ex.execute(_relu_mask_launch(tuple(g2.shape), dt), [g2, h.reshape(-1, N)])
+                masked = out((M, N))
+                steps.append((_relu_mask_launch((M, N), dt), [g2, h.reshape(-1, N)], [masked]))
+                g2 = masked
             db = None
             if has_bias:
-                (db,) = ex.execute(_col_sum_launch(N, dt), [g2])
-            (dw,) = ex.execute(_gemm_launch("weight_grad[autograd]", (N, K), dt, weight_layout=1, x_layout=1), [g2, x2])
+                db = out((N,))
+                steps.append((_col_sum_launch(N, dt), [g2], [db]))
+            dw = out((N, K))
+            steps.append((_gemm_launch("weight_grad[autograd]", (N, K), dt, weight_layout=1, x_layout=1), [g2, x2], [dw]))
             param_grads = [dw] + ([db] if has_bias else []) + param_grads
             if i == 0 and not ctx.needs_input_grad[2]:
                 g = None                     # nobody asked for d/dx of the chain's input: skip that product
                 break
-            (dx,) = ex.execute(_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w])
+            dx = out((M, K))
+            steps.append((_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w], [dx]))
             g = dx.reshape(x.shape)
+        ex.execute_many(steps)                # every gradient launch of the chain in one call into the library
         return (None, None, g, *param_grads)

@@ -296,7 +296,10 @@ class Callable:
         return host_out
 
     def _run_plan(self, env: dict, device, rows: Optional[int] = None) -> list:
+        """Bind every launch's tensors (outputs are allocated here, views and aliases resolved),
+        then hand the whole list to the library in one call."""
         ex = self._exec()
+        steps = []
         for launch in self.launches:
             ins = []
             for b in launch.inputs:
@@ -321,7 +324,6 @@ class Callable:
                     # is): a caller's strided tensor is gathered first, once, and reused by later launches
                     src = env[launch.inputs[0]] = ex.make_contiguous(src)
                 ins = [torch.as_strided(src, launch.out_shapes[0], launch.view_strides, src.storage_offset() + launch.view_offset)]
-            outs = None
             if launch.out_view is not None:                # cat: this launch fills one slice of the result
                 if rows is not None:
                     raise ExecutionError("a plan with a concatenation cannot run on a block of its rows", kernel_name=launch.name)
@@ -329,14 +331,17 @@ class Callable:
                 if whole is None:
                     whole = env[launch.outputs[0]] = torch.empty(launch.out_shapes[0], dtype=launch.out_dtypes[0], device=device)
                 shape, strides, offset = launch.out_view
-                ex.execute(launch, ins, [torch.as_strided(whole, shape, strides, whole.storage_offset() + offset)])
+                steps.append((launch, ins, [torch.as_strided(whole, shape, strides, whole.storage_offset() + offset)]))
                 continue
-            if rows is not None:
-                outs = [torch.empty(self._shard_shape(sh, rows), dtype=dt, device=device)
-                        for sh, dt in zip(launch.out_shapes, launch.out_dtypes)]
-            outs = ex.execute(launch, ins, outs)
+            outs = [torch.empty(self._shard_shape(sh, rows), dtype=dt, device=device)
+                    for sh, dt in zip(launch.out_shapes, launch.out_dtypes)]
+            steps.append((launch, ins, outs))
             for b, t in zip(launch.outputs, outs):
                 env[b] = t
+        if len(steps) == 1:
+            ex.execute(*steps[0])
+        elif steps:
+            ex.execute_many(steps)
         result = []
         for item in self.dag.output_spec:
             if hasattr(item, "name") and item in env:

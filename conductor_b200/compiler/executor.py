@@ -16,7 +16,7 @@ from typing import Optional, Sequence
 import torch
 
 from ..codegen.operator_registry import Template
-from ..codegen.kernel_templates import CdrTensor, KernelLaunch
+from ..codegen.kernel_templates import CdrLaunchItem, CdrTensor, KernelLaunch
 from ..utils.exceptions import DeviceError, ExecutionError, UnsupportedOperationError
 from ..utils.type_mapping import to_cdr_dtype
 from .loader import load_library
@@ -88,15 +88,9 @@ class GCUKernelExecutor:
         self._workspaces[key] = (sig, ws)
         return ws
 
-    def execute(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor],
-                outputs: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
-        """Run `launch`; allocates the outputs when none are passed.  Asynchronous.  Inputs that are
-        not contiguous are first gathered with the strided-copy template (never by torch).
-
-        The descriptor arrays of a launch are built once and kept on the launch object: a repeat
-        call with the same shapes, strides and dtypes only refreshes the data pointers, which
-        keeps the host cost of one launch to a few microseconds (plans that are not replayed from
-        a CUDA graph -- autograd steps, whole transformer blocks -- are otherwise bound by it)."""
+    def _prepare(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor], outputs):
+        """Marshal one launch: contiguous inputs, allocated outputs, descriptor arrays (built once
+        per launch and shape signature, data pointers refreshed per call), parameter block, scratch."""
         if not inputs:
             raise ExecutionError("kernel launch without inputs", kernel_name=launch.name)
         device = inputs[0].device
@@ -129,6 +123,18 @@ class GCUKernelExecutor:
         ws = None
         if launch.needs_workspace:
             ws = self.workspace_for(launch, ins, outputs, in_desc, out_desc, params_ptr, params_size)
+        return device, ins, outputs, in_desc, out_desc, params_ptr, params_size, ws
+
+    def execute(self, launch: KernelLaunch, inputs: Sequence[torch.Tensor],
+                outputs: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
+        """Run `launch`; allocates the outputs when none are passed.  Asynchronous.  Inputs that are
+        not contiguous are first gathered with the strided-copy template (never by torch).
+
+        The descriptor arrays of a launch are built once and kept on the launch object: a repeat
+        call with the same shapes, strides and dtypes only refreshes the data pointers, which
+        keeps the host cost of one launch to a few microseconds.  A launch object is therefore
+        driven by one thread at a time."""
+        device, ins, outputs, in_desc, out_desc, params_ptr, params_size, ws = self._prepare(launch, inputs, outputs)
         stream = torch.cuda.current_stream(device).cuda_stream
         args = (launch.template, in_desc, len(ins), out_desc, len(outputs), params_ptr, params_size,
                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
@@ -140,6 +146,56 @@ class GCUKernelExecutor:
         if rc != 0:
             raise_for_status(self.lib, rc, launch.name)
         return list(outputs)
+
+    def execute_many(self, steps) -> list[list[torch.Tensor]]:
+        """Run several launches with ONE call into the library (``cdr_launch_many``): the whole
+        plan crosses the FFI once, as a compiled graph does in the reference
+        (``host_wrapper.py:360-403``).  `steps` is a list of ``(launch, inputs, outputs or None)``;
+        later steps may read tensors earlier steps write (stream order).  Returns the outputs of
+        every step."""
+        results: list = []
+        batch: list = []          # (launch, prepared)
+        seen: set = set()
+        device = None
+
+        def flush():
+            nonlocal batch, seen
+            if not batch:
+                return
+            items = (CdrLaunchItem * len(batch))()
+            for it, (launch, (dev, ins, outs, in_desc, out_desc, pp, ps, ws)) in zip(items, batch):
+                it.template_id, it.n_inputs, it.n_outputs = launch.template, len(ins), len(outs)
+                it.inputs, it.outputs = ctypes.addressof(in_desc), ctypes.addressof(out_desc)
+                it.params = pp.value if pp is not None else None
+                it.params_bytes = ps
+                it.workspace = ws.data_ptr() if ws is not None else None
+                it.workspace_bytes = ws.numel() if ws is not None else 0
+            stream = torch.cuda.current_stream(device).cuda_stream
+            failed = ctypes.c_int(-1)
+            if torch.cuda.current_device() == device.index:
+                rc = self.lib.cdr_launch_many(items, len(batch), stream, ctypes.byref(failed))
+            else:
+                with torch.cuda.device(device):
+                    rc = self.lib.cdr_launch_many(items, len(batch), stream, ctypes.byref(failed))
+            if rc != 0:
+                name = batch[failed.value][0].name if 0 <= failed.value < len(batch) else "plan"
+                raise_for_status(self.lib, rc, name)
+            batch, seen = [], set()
+
+        for launch, inputs, outputs in steps:
+            # a launch object's descriptors are shared state: the same object twice in one call
+            # (two layers of equal shape) would overwrite them, so the first part goes out first
+            if id(launch) in seen:
+                flush()
+            prepared = self._prepare(launch, inputs, outputs)
+            if device is not None and prepared[0] != device:
+                flush()
+            device = prepared[0]
+            batch.append((launch, prepared))
+            seen.add(id(launch))
+            results.append(list(prepared[2]))
+        flush()
+        return results
 
     def make_contiguous(self, t: torch.Tensor) -> torch.Tensor:
         """Contiguous copy of a strided view through the strided-copy template."""

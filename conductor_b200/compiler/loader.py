@@ -35,6 +35,7 @@ SYMBOLS = {
                                        _c.POINTER(_c.c_size_t)]),
     "cdr_launch": (_c.c_int, [_c.c_int, _TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,
                               _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "cdr_launch_many": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.POINTER(_c.c_int)]),
     "cdr_execute_host": (_c.c_int, [_c.c_int, _TENSORS, _c.c_int, _TENSORS, _c.c_int, _c.c_void_p, _c.c_size_t,
                                     _c.c_int]),
     "cdr_release_host_arena": (_c.c_int, [_c.c_int]),

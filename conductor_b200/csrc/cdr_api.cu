@@ -273,6 +273,22 @@ int cdr_launch(int template_id, const cdr_tensor* inputs, int n_inputs, const cd
   }
 }
 
+int cdr_launch_many(const cdr_launch_item* items, int n_items, void* cuda_stream, int* failed_item) {
+  g_error[0] = 0;
+  if (failed_item) *failed_item = -1;
+  if (n_items < 0 || (n_items > 0 && !items)) { set_error("launch list is null or has a negative count"); return CDR_ERR_BAD_ARG; }
+  for (int i = 0; i < n_items; ++i) {
+    const cdr_launch_item& it = items[i];
+    const int rc = cdr_launch(it.template_id, it.inputs, it.n_inputs, it.outputs, it.n_outputs, it.params, it.params_bytes,
+                              it.workspace, it.workspace_bytes, cuda_stream);
+    if (rc != CDR_OK) {
+      if (failed_item) *failed_item = i;
+      return rc;
+    }
+  }
+  return CDR_OK;
+}
+
 int cdr_execute_host(int template_id, const cdr_tensor* host_inputs, int n_inputs, const cdr_tensor* host_outputs,
                      int n_outputs, const void* params, size_t params_bytes, int device) {
   g_error[0] = 0;

@@ -113,6 +113,55 @@ __global__ void __launch_bounds__(256) transpose_tile_kernel(const __grid_consta
   }
 }
 
+// Vector form of the tile transpose: every thread moves 16 bytes on both sides (V elements along the
+// input's unit-stride dimension on the way in, V elements along the output's on the way out), so a
+// warp request covers whole 128-byte lines for 2-byte types too.  Needs every extent, stride and
+// base involved to be a multiple of 16 bytes; the scalar form above takes the rest.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_tile_vec_kernel(const __grid_constant__ TransposeArgs a) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int TILE = 16 * V;
+  constexpr int PAD = sizeof(T) >= 4 ? 1 : 4 / sizeof(T);
+  __shared__ T tile[TILE][TILE + PAD];
+  const int last = a.rank - 1;
+  int64_t b = blockIdx.x;
+  const int64_t tl = b % a.tiles_l; b /= a.tiles_l;
+  const int64_t tp = b % a.tiles_p; b /= a.tiles_p;
+  int64_t in_base = 0, out_base = 0;
+#pragma unroll 1
+  for (int d = last - 1; d >= 0; --d) {
+    if (d == a.pdim) continue;
+    const int64_t q = b / a.shape[d], r = b - q * a.shape[d];
+    in_base += r * a.stride[d];
+    out_base += r * a.ostride[d];
+    b = q;
+  }
+  const int64_t p0 = tp * TILE, l0 = tl * TILE;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll 4
+  for (int y = ty; y < TILE; y += 16) {
+    const int64_t pi = p0 + tx * V, li = l0 + y;
+    if (pi < a.shape[a.pdim] && li < a.shape[last]) {
+      const uint4 q = ld_stream16(a.in + in_base + pi * a.stride[a.pdim] + li * a.stride[last]);
+      const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int i = 0; i < V; ++i) tile[y][tx * V + i] = e[i];
+    }
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int y = ty; y < TILE; y += 16) {
+    const int64_t pi = p0 + y, li = l0 + tx * V;
+    if (pi < a.shape[a.pdim] && li < a.shape[last]) {
+      uint4 q;
+      T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+      for (int i = 0; i < V; ++i) e[i] = tile[tx * V + i][y];
+      st_stream16(a.out + out_base + pi * a.ostride[a.pdim] + li * a.ostride[last], q);
+    }
+  }
+}
+
 }  // namespace
 
 int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out, cudaStream_t stream) {
@@ -158,7 +207,14 @@ int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs,
       TransposeArgs t{};
       t.in = a.in; t.out = a.out; t.rank = a.rank; t.pdim = pdim;
       for (int d = 0; d < a.rank; ++d) { t.shape[d] = a.shape[d]; t.stride[d] = a.stride[d]; t.ostride[d] = a.ostride[d]; }
-      const int tile = 64;   // 64 x 64 elements per CTA: 8-32 KB in flight, enough CTAs per SM to cover the HBM latency
+      // 16-byte accesses on both sides when every extent, stride and base allows it
+      bool tvec = (esz == 2 || esz == 4 || esz == 8) && aligned16(x.data) && aligned16(out.data) &&
+                  x.shape[pdim] % per_vec == 0 && x.shape[last] % per_vec == 0;
+      for (int d = 0; d < a.rank && tvec; ++d) {
+        if (d != pdim && a.shape[d] > 1) tvec &= (a.stride[d] % 16) == 0;
+        if (d != last && a.shape[d] > 1) tvec &= (a.ostride[d] % 16) == 0;
+      }
+      const int tile = tvec ? 16 * per_vec : 64;   // scalar form: 64 x 64 elements per CTA
       t.tiles_p = (x.shape[pdim] + tile - 1) / tile;
       t.tiles_l = (x.shape[last] + tile - 1) / tile;
       int64_t batch = 1;
@@ -167,6 +223,13 @@ int launch_strided_copy(const cdr_tensor* ins, int n_in, const cdr_tensor* outs,
       const int64_t blocks = batch * t.tiles_p * t.tiles_l;
       if (blocks > 0 && blocks < (int64_t{1} << 31)) {
         const unsigned g = static_cast<unsigned>(blocks);
+        if (tvec) {
+          if (esz == 2) transpose_tile_vec_kernel<uint16_t><<<g, 256, 0, stream>>>(t);
+          else if (esz == 4) transpose_tile_vec_kernel<uint32_t><<<g, 256, 0, stream>>>(t);
+          else transpose_tile_vec_kernel<uint64_t><<<g, 256, 0, stream>>>(t);
+          CDR_CUDA_TRY(cudaGetLastError());
+          return CDR_OK;
+        }
         switch (esz) {
           case 1: transpose_tile_kernel<uint8_t, 64><<<g, 256, 0, stream>>>(t); break;
           case 2: transpose_tile_kernel<uint16_t, 64><<<g, 256, 0, stream>>>(t); break;

@@ -272,6 +272,29 @@ CDR_API int cdr_launch(int template_id, const cdr_tensor* inputs, int n_inputs,
                size_t params_bytes, void* workspace, size_t workspace_bytes,
                void* cuda_stream);
 
+/* One step of a plan for cdr_launch_many(): the arguments of one cdr_launch() call. */
+typedef struct cdr_launch_item {
+  int32_t template_id;
+  int32_t n_inputs;
+  int32_t n_outputs;
+  int32_t reserved;            /* 0 */
+  const cdr_tensor* inputs;
+  const cdr_tensor* outputs;
+  const void* params;
+  size_t params_bytes;
+  void* workspace;
+  size_t workspace_bytes;
+} cdr_launch_item;
+
+/* Run the steps of a compiled plan in order on one stream with a single call.  The reference's
+ * generated execute_kernel() runs a whole compiled graph per call (host_wrapper.py:132-196); a
+ * plan here may hold several clusters, and crossing the FFI once per plan instead of once per
+ * cluster keeps short plans from being bound by host time.  Equivalent to calling cdr_launch()
+ * per item: stops at the first failing item, returns its status and stores its index in
+ * *failed_item (when not NULL).  Buffers that one item writes and a later item reads are ordered
+ * by the stream. */
+CDR_API int cdr_launch_many(const cdr_launch_item* items, int n_items, void* cuda_stream, int* failed_item);
+
 /* Same cluster, reference calling convention: HOST pointers in, HOST pointers out,
  * synchronous.  Copies inputs to `device`, launches, copies outputs back and waits
  * (host_wrapper.py:169-182).  Staging memory is a per-device arena owned by the

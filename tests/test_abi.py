@@ -142,10 +142,11 @@ def test_struct_layouts_match_the_c_compiler(tmp_path):
     src = tmp_path / "sizes.c"
     src.write_text(
         '#include <stdio.h>\n#include <stddef.h>\n#include "conductor_b200.h"\n'
-        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(cdr_tensor), sizeof(cdr_ew_instr),"
+        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(cdr_tensor), sizeof(cdr_ew_instr),"
         " sizeof(cdr_ew_params), sizeof(cdr_reduce_params), sizeof(cdr_gemm_params), sizeof(cdr_attn_params),"
         " offsetof(cdr_tensor, shape), offsetof(cdr_ew_params, instr), offsetof(cdr_reduce_params, reduce_op),"
-        " sizeof(cdr_norm_params), offsetof(cdr_gemm_params, x_layout));"
+        " sizeof(cdr_norm_params), offsetof(cdr_gemm_params, x_layout), sizeof(cdr_launch_item),"
+        " offsetof(cdr_launch_item, inputs), offsetof(cdr_launch_item, workspace_bytes));"
         "return 0;}\n")
     exe = tmp_path / "sizes"
     subprocess.run(["gcc", "-std=c99", "-I", str(HEADER.parent), str(src), "-o", str(exe)], check=True)
@@ -153,7 +154,8 @@ def test_struct_layouts_match_the_c_compiler(tmp_path):
     want = [ctypes.sizeof(kt.CdrTensor), ctypes.sizeof(kt.CdrEwInstr), ctypes.sizeof(kt.CdrEwParams),
             ctypes.sizeof(kt.CdrReduceParams), ctypes.sizeof(kt.CdrGemmParams), ctypes.sizeof(kt.CdrAttnParams),
             kt.CdrTensor.shape.offset, kt.CdrEwParams.instr.offset, kt.CdrReduceParams.reduce_op.offset,
-            ctypes.sizeof(kt.CdrNormParams), kt.CdrGemmParams.x_layout.offset]
+            ctypes.sizeof(kt.CdrNormParams), kt.CdrGemmParams.x_layout.offset, ctypes.sizeof(kt.CdrLaunchItem),
+            kt.CdrLaunchItem.inputs.offset, kt.CdrLaunchItem.workspace_bytes.offset]
     assert got == want
 
 

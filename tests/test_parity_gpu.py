@@ -521,6 +521,36 @@ def test_strided_copy_template(executor):
     assert abi.launch(Template.COPY, [y], [torch.zeros(37, 1, device=DEV).expand(37, 53)], check=False) != 0   # stride-0 output
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.int64, torch.bool])
+def test_transposing_copies_take_the_tiled_paths(executor, dtype):
+    """Views whose unit-stride dimension is not the innermost one go through a shared-memory tile:
+    the 16-byte form when every extent and stride allows it, the element form otherwise (ragged
+    extents, odd strides, 1-byte types), with batch dimensions around the transposed pair and with
+    a strided output.  All bit-exact."""
+    gen = torch.Generator().manual_seed(93)
+
+    def rnd(*shape):
+        t = torch.randn(*shape, generator=gen) * 50
+        return (t > 0).to(DEV) if dtype == torch.bool else t.to(dtype).to(DEV)
+
+    big = rnd(320, 448)
+    views = [big.t(),                                     # whole-vector extents: 16-byte form
+             rnd(3, 136, 264).transpose(1, 2),            # batched
+             rnd(2, 72, 3, 40).permute(0, 2, 3, 1),       # [B, S, H, D] -> [B, H, D, S]
+             rnd(129, 67).t(),                            # ragged: element form
+             rnd(5, 33, 130).transpose(0, 2),             # unit-stride dimension lands first
+             big[8:, 16:].t(),                            # offset base, still aligned for 2-byte and wider
+             big[1:, 3:].t()]                             # misaligned base: element form
+    for v in views:
+        out = torch.empty(v.shape, dtype=v.dtype, device=DEV)
+        abi.launch(Template.COPY, [v], [out])
+        assert torch.equal(out, v), (tuple(v.shape), v.stride(), v.dtype)
+    # transposed read into a slice of a wider result
+    wide = torch.zeros(448, 400, dtype=dtype, device=DEV)
+    abi.launch(Template.COPY, [big.t()], [wide[:, 40:360]])
+    assert torch.equal(wide[:, 40:360], big.t()) and bool((wide[:, :40] == 0).all()) and bool((wide[:, 360:] == 0).all())
+
+
 def test_layer_norm_template(executor):
     """CDR_T_LAYER_NORM through the C ABI against a float64 evaluation: row lengths from one vector
     to the 1024-thread variant, with and without scale / shift, bf16, and the refusals."""
