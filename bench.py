@@ -644,6 +644,8 @@ def gpu_arm(args, keys):
         wl = Workload(k)
         m = Measurement(wl, rank, world, dev, peaks, args)
         start, stop = row_partition(wl.rows, world)[rank]
+        if args.shard_of > 1 and world == 1:       # one GPU standing in for rank 0 of a larger world
+            start, stop = row_partition(wl.rows, args.shard_of)[0]
         r = m.run(start, stop, clocks)
         total_rows = wl.rows                     # strong scaling: the fixed configuration over all ranks
         r["value"] = total_rows * r["passes_per_step"] * args.steps / (r["timed_region_ms"] * 1e-3)
@@ -706,6 +708,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="short device-resident regions only (for profiler runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the plan directly instead of replaying a CUDA graph")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="with one GPU: time the row block rank 0 of a world of this size would run (value then counts "
+                         "the whole configuration per pass, i.e. what that world would reach if every rank kept this pace)")
     args = ap.parse_args()
     keys = ALL if args.workload == "all" else [k.strip() for k in args.workload.split(",") if k.strip()]
     for k in keys:

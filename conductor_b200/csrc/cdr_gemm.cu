@@ -31,16 +31,25 @@ namespace cdr {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = ACC_STAGES * BN;  // 512: all of tensor memory
 constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps
-constexpr int EPI_WARPS = 8;              // two per TMEM lane quadrant, 128 accumulator columns each
-constexpr int EPI_CHUNKS = BN / 32 / 2;   // 32-column chunks per epilogue warp
-constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_WARPS = 8;              // two per TMEM lane quadrant, half of the accumulator columns each
+constexpr int EPI_CHUNKS = BN / 32 / 2;   // 32-column chunks per epilogue warp (256-column tiles)
+
+// Geometry of the 1-CTA kernel for a tile of 128 x TN outputs.  TN = 256 is the default; TN = 128
+// serves problems with so few 256-wide tiles that most SMs would idle (a 1024 x 1024 output is 16
+// CTA-pair tiles on 74 pairs, but 64 tiles of 128 x 128).
+template <int TN>
+struct Tile1 {
+  static constexpr int B_BYTES = TN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = TN == 256 ? 4 : 6;
+  static constexpr int TMEM = ACC_STAGES * TN;
+  static constexpr int CHUNKS = TN / 32 / 2;
+  static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 struct GemmArgs {
   CUtensorMap tmap_a;  // x  [M, K], box 64 x 128 -- or, with x_km, x [K, M], box 64 (M) x 64 (K)
@@ -87,14 +96,14 @@ __device__ __forceinline__ void store_elem(void* p, size_t i, float v) {
 // 32-column chunks (the load of chunk c+1 is in flight while chunk c is processed), + bias,
 // round to the output type, ReLU on the packed pairs (NaN-propagating max), 16-byte stores.
 // Bias values are fetched with warp-uniform 128-bit loads issued before the TMEM wait.
-template <bool BF16>
+template <bool BF16, int CHUNKS = EPI_CHUNKS>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base, int row, int n0, bool vec_ok,
                                               int c_begin) {
   uint32_t r[2][32];
   sm100::tmem_ld32(t_base + c_begin * 32, r[0]);
   const bool bias_vec = a.bias != nullptr && vec_ok && (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0;
 #pragma unroll
-  for (int cc = 0; cc < EPI_CHUNKS; ++cc) {
+  for (int cc = 0; cc < CHUNKS; ++cc) {
     const int c = c_begin + cc;
     const int col0 = n0 + c * 32;
     const bool full_chunk = vec_ok && col0 + 32 <= a.N;
@@ -105,7 +114,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base
       for (int g = 0; g < 4; ++g) bq[g] = __ldg(bp + g);
     }
     sm100::tmem_ld_wait();
-    if (cc + 1 < EPI_CHUNKS) sm100::tmem_ld32(t_base + (c + 1) * 32, r[(cc + 1) & 1]);
+    if (cc + 1 < CHUNKS) sm100::tmem_ld32(t_base + (c + 1) * 32, r[(cc + 1) & 1]);
     const uint32_t* rc = r[cc & 1];
     if (row < a.M && col0 < a.N) {
       const size_t off = static_cast<size_t>(row) * a.N + col0;
@@ -156,8 +165,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base
   }
 }
 
-template <bool BF16>
+template <bool BF16, int TN>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __grid_constant__ GemmArgs a) {
+  using G = Tile1<TN>;
+  constexpr int STAGES = G::STAGES, STAGE_BYTES = G::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -181,7 +192,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     sm100::fence_barrier_init();
   }
   if (warp == 1) {
-    sm100::tmem_alloc(tmem_slot, TMEM_COLS);
+    sm100::tmem_alloc(tmem_slot, G::TMEM);
     sm100::tmem_relinquish();
   }
   sm100::tc_fence_before();
@@ -203,7 +214,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % a.tiles_m) * BM, n0 = (tile / a.tiles_m) * BN;
+        const int m0 = (tile % a.tiles_m) * BM, n0 = (tile / a.tiles_m) * TN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!sm100::mbar_wait(&empty[s], ph ^ 1)) { sm100::report_timeout(a.status, 10); ok = false; break; }
@@ -220,7 +231,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
             sm100::tma_load_2d(st + A_BYTES, &a.tmap_b, kb * BK, n0, &full[s]);
           } else {   // [K, N]: one box of 64 k-rows per 64 columns of N
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
+            for (int c = 0; c < TN / 64; ++c)
               sm100::tma_load_2d(st + A_BYTES + c * (BK * 128), &a.tmap_b, n0 + c * 64, kb * BK, &full[s]);
           }
         }
@@ -232,7 +243,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     // instructions, so the operand descriptors stay in uniform registers.
     {
       const bool leader = sm100::elect_one();
-      const uint32_t idesc = sm100::umma_idesc_f16(BM, BN, BF16, a.x_km != 0, a.w_kn != 0);
+      const uint32_t idesc = sm100::umma_idesc_f16(BM, TN, BF16, a.x_km != 0, a.w_kn != 0);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
@@ -242,7 +253,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
           break;
         }
         sm100::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * BN;
+        const uint32_t d_tmem = tmem_base + as * TN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!__all_sync(0xffffffffu, sm100::mbar_wait(&full[s], ph))) {
@@ -278,13 +289,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
     uint32_t tile_iter = 0;
     const bool vec_ok = (a.N % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
-      const int m0 = (tile % a.tiles_m) * BM, n0 = (tile / a.tiles_m) * BN;
+      const int m0 = (tile % a.tiles_m) * BM, n0 = (tile / a.tiles_m) * TN;
       const uint32_t as = tile_iter % ACC_STAGES, aph = (tile_iter / ACC_STAGES) & 1;
       if (!sm100::mbar_wait(&acc_full[as], aph)) { sm100::report_timeout(a.status, 13); break; }
       sm100::tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      const uint32_t t_base = tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16);
-      epilogue_tile<BF16>(a, t_base, row, n0, vec_ok, ((warp - 2) >> 2) * EPI_CHUNKS);
+      const uint32_t t_base = tmem_base + as * TN + (static_cast<uint32_t>(q * 32) << 16);
+      epilogue_tile<BF16, G::CHUNKS>(a, t_base, row, n0, vec_ok, ((warp - 2) >> 2) * G::CHUNKS);
       sm100::tc_fence_before();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&acc_empty[as]);
@@ -295,7 +306,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_epilogue_kernel(const __g
   __syncthreads();
   if (warp == 1) {
     sm100::tc_fence_after();
-    sm100::tmem_dealloc(tmem_base, TMEM_COLS);
+    sm100::tmem_dealloc(tmem_base, G::TMEM);
   }
 }
 
@@ -574,10 +585,14 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   static bool configured_dev[64] = {false};
   bool& configured = configured_dev[dev & 63];
   if (!configured) {
-    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(SMEM_BYTES)));
-    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(SMEM_BYTES)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Tile1<256>::SMEM)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Tile1<256>::SMEM)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Tile1<128>::SMEM)));
+    CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Tile1<128>::SMEM)));
     CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(P_SMEM_BYTES)));
     CDR_CUDA_TRY(cudaFuncSetAttribute(gemm_epilogue_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -586,7 +601,13 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
   }
 
   static const bool pdl = getenv("CDR_DISABLE_PDL") == nullptr;
-  if (M >= P_BM && N >= P_BN) {
+  // Few large tiles leave most SMs idle: when the 256 x 256 pair tiles fill less than half of the
+  // CTA pairs and 128 x 128 tiles would still fit in one wave, run the 1-CTA kernel on 128 x 128
+  // tiles instead (a 1024 x 1024 x 4096 product: 16 pair tiles on 74 pairs, or 64 tiles on 148 SMs).
+  const int64_t pair_tiles = ((M + P_BM - 1) / P_BM) * ((N + P_BN - 1) / P_BN);
+  const int64_t small_tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
+  const bool narrow = N >= 128 && 2 * pair_tiles < sm_count() / 2 && small_tiles <= sm_count() && small_tiles > 2 * pair_tiles;
+  if (M >= P_BM && N >= P_BN && !narrow) {
     // CTA-pair kernel: 256 x 256 tiles, clusters of two CTAs, at most one cluster per TPC.
     // Each CTA stages only 128 of the tile's 256 weight rows: the W box is 64 x 128 here.
     if (!w_kn)
@@ -615,23 +636,31 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
     return CDR_OK;
   }
 
+  const int tn = narrow ? 128 : BN;
+  if (narrow && !w_kn)     // the weight box follows the tile: 128 rows of W per k-block
+    if (int rc = make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, 128, BK)) return rc;
   a.tiles_m = static_cast<int>((M + BM - 1) / BM);
-  a.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  a.tiles_n = static_cast<int>((N + tn - 1) / tn);
   const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
   int grid = sm_count();
   if (grid > tiles) grid = static_cast<int>(tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.dynamicSmemBytes = narrow ? Tile1<128>::SMEM : Tile1<256>::SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (dt == CDR_BF16) CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<true>, a));
-  else CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<false>, a));
+  if (narrow) {
+    if (dt == CDR_BF16) CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<true, 128>, a));
+    else CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<false, 128>, a));
+    return CDR_OK;
+  }
+  if (dt == CDR_BF16) CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<true, 256>, a));
+  else CDR_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_epilogue_kernel<false, 256>, a));
   return CDR_OK;
 }
 
