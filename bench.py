@@ -48,7 +48,7 @@ import torch  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 POOL_BYTES_MIN = 4 * L2_BYTES          # rotating pool (inputs + outputs) is at least this large
 MAX_POOL = 64
-MAX_SEQ = 256                          # passes captured in one CUDA graph
+MAX_SEQ = 1024                         # passes captured in one CUDA graph
 REGION_S = 0.6                         # every timed region lasts at least this long
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 ALL = ["c1", "c2", "c3", "c3b", "c4", "c5"]
@@ -254,6 +254,16 @@ def max_over_ranks(value: float, world: int, device) -> float:
     return float(t.item())
 
 
+def sum_over_ranks(value: float, world: int, device) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
 def nbytes(tensors) -> int:
     return sum(t.numel() * t.element_size() for t in tensors if isinstance(t, torch.Tensor))
 
@@ -448,32 +458,40 @@ class Measurement:
         est_ms = max(e0.elapsed_time(e1) / 4, 1e-3)
         seq_len = int(min(MAX_SEQ, max(pool_n, 4.0 / est_ms)))
         seq_len = -(-seq_len // pool_n) * pool_n if seq_len > pool_n else pool_n
-        seq_sets = [pool[i % pool_n] for i in range(seq_len)]
-        if args.no_graphs:
-            class _Direct:
-                def __init__(s, plan, sets):
-                    s.plan, s.sets = plan, sets
+        class _Direct:
+            def __init__(s, plan, sets):
+                s.plan, s.sets = plan, sets
 
-                def replay(s):
-                    for inp in s.sets:
-                        s.plan(*inp)
+            def replay(s):
+                for inp in s.sets:
+                    s.plan(*inp)
 
-            sequence = _Direct(self.plan, seq_sets)
-        else:
-            sequence = self.plan.capture_sequence(seq_sets, keep_outputs="first")
-        sequence.replay()
-        torch.cuda.synchronize()
-        e0.record()
-        sequence.replay()
-        sequence.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        replay_ms = max(e0.elapsed_time(e1) / 2, 1e-3)
+        def build(n):
+            sets = [pool[i % pool_n] for i in range(n)]
+            seq = _Direct(self.plan, sets) if args.no_graphs else self.plan.capture_sequence(sets, keep_outputs="first")
+            seq.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            seq.replay()
+            seq.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return seq, max(e0.elapsed_time(e1) / 2, 1e-3)
+
+        sequence, replay_ms = build(seq_len)
+        # the first estimate came from direct launches, which are launch-bound for microsecond kernels:
+        # one graph replay should last a few milliseconds, so that the host's replay calls stay far ahead
+        grown = seq_len
+        if not args.no_graphs and replay_ms < 3.0 and seq_len < MAX_SEQ:
+            grown = int(min(MAX_SEQ, seq_len * math.ceil(4.0 / replay_ms)))
+            grown = max(pool_n, grown // pool_n * pool_n)
+        if grown > seq_len:
+            del sequence
+            seq_len = grown
+            sequence, replay_ms = build(seq_len)
         region = 0.05 if args.quick else REGION_S
         replays_per_step = max(1, math.ceil(region * 1e3 / (args.steps * replay_ms)))
-        if world > 1:       # every rank must run the same number of passes
-            replays_per_step = int(max_over_ranks(float(replays_per_step), world, dev))
-        passes_per_step = replays_per_step * seq_len
+        passes_per_step = replays_per_step * seq_len    # per rank: the aggregate counts every rank's own rows x passes
 
         for _ in range(max(args.warmup, 3) * replays_per_step if not args.quick else 1):
             sequence.replay()
@@ -487,6 +505,7 @@ class Measurement:
         t_wall1 = time.monotonic()
         own_ms = e0.elapsed_time(e1)
         dev_ms = max_over_ranks(own_ms, world, dev)
+        rows_done = sum_over_ranks(float(rows) * args.steps * passes_per_step, world, dev)   # samples of all ranks
         barrier(world)
 
         passes = args.steps * passes_per_step
@@ -507,7 +526,7 @@ class Measurement:
                     "launches_timed": passes * self.kernels_per_pass, "region_ms": own_ms,
                     "vs_nominal": achieved / 8000.0 if wl.bound == "hbm" else achieved / 2250.0}
         result = {
-            "rows_per_gpu": rows, "passes_per_step": passes_per_step, "ms_per_step": dev_ms / args.steps,
+            "rows_per_gpu": rows, "rows_done_all_ranks": rows_done, "passes_per_step": passes_per_step, "ms_per_step": dev_ms / args.steps,
             "ms_per_pass": dev_ms / passes, "timed_region_ms": dev_ms, "pool_slots": pool_n,
             "pool_mib": pool_n * slot_bytes >> 20, "passes_per_graph": seq_len,
             "gpu_launches": passes * self.kernels_per_pass, "roofline": roofline,
@@ -654,8 +673,8 @@ def gpu_arm(args, keys):
         if args.shard_of > 1 and world == 1:       # one GPU standing in for rank 0 of a larger world
             start, stop = row_partition(wl.rows, args.shard_of)[0]
         r = m.run(start, stop, clocks)
-        total_rows = wl.rows                     # strong scaling: the fixed configuration over all ranks
-        r["value"] = total_rows * r["passes_per_step"] * args.steps / (r["timed_region_ms"] * 1e-3)
+        # strong scaling: the fixed configuration over all ranks; every rank's rows x passes, over the slowest rank's time
+        r["value"] = r["rows_done_all_ranks"] / (r["timed_region_ms"] * 1e-3)
         r["unit"], r["dtype"], r["workload"], r["scaling"] = "samples/s", wl.dtype, wl.name, "strong"
         r["roofline"]["peak_source"] = f"MEASURED_PEAKS.json ({peak_kind})"
         if not args.quick:
@@ -664,7 +683,7 @@ def gpu_arm(args, keys):
                 r["allgather"] = m.allgather(start, stop)
                 torch.cuda.empty_cache()
                 w = m.run(0, wl.rows, None)      # replicas: every rank the whole configuration
-                r["weak"] = {"value": wl.rows * world * w["passes_per_step"] * args.steps / (w["timed_region_ms"] * 1e-3),
+                r["weak"] = {"value": w["rows_done_all_ranks"] / (w["timed_region_ms"] * 1e-3),
                              "unit": "samples/s", "ms_per_pass": w["ms_per_pass"], "roofline_frac": w["roofline"]["frac"],
                              "timed_region_ms": w["timed_region_ms"]}
         per[k] = r
