@@ -97,6 +97,9 @@ class KernelLaunch:
     view_strides: Optional[tuple] = None  # COPY launches: element strides of the view of inputs[0] that is gathered
     view_offset: int = 0                  # COPY launches: first element of that view, relative to inputs[0]'s own
     out_view: Optional[tuple] = None      # COPY launches that fill one part of outputs[0] (cat): (shape, strides, offset)
+    # the executor's marshalled form of this launch (shape signature, descriptor arrays, parameter pointer):
+    # built on first use, reused while shapes, strides and dtypes stay the same
+    _marshal: Any = field(default=None, repr=False, compare=False)
 
     def describe(self) -> str:
         ins = ", ".join(b.name for b in self.inputs)

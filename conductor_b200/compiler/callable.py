@@ -50,6 +50,9 @@ class Callable:
         self._grad_layers = None
         self.chunked_calls = 0                # host calls that ran in overlapped row chunks
         self._chunk_plan = None               # (batch, batch input indices) or False, decided on first host call
+        self._batch_override: Optional[int] = None   # the batch size while a host call runs in row chunks
+        # (a Callable is driven by one thread at a time: the override and the launches' marshalled
+        # descriptors are per-object state)
         self._copy_streams: dict = {}
         # when set, every call stores the placeholder tensors it ran on (graph capture needs the
         # full list, including module parameters Dynamo lifted into placeholders)
@@ -203,8 +206,6 @@ class Callable:
         if rows is None or not shape or shape[0] != batch:
             return tuple(shape)
         return (rows,) + tuple(shape[1:])
-
-    _batch_override: Optional[int] = None     # set while a host call runs in row chunks
 
     # ------------------------------------------------------------------ chunked host calls
     def _host_chunks(self, tensors) -> Optional[list]:

@@ -72,7 +72,7 @@ class GCUKernelExecutor:
         at once needs one Callable per stream."""
         key = (ins[0].device, id(launch))
         hit = self._workspaces.get(key)
-        sig = launch._marshal[0] if getattr(launch, "_marshal", None) is not None else None
+        sig = launch._marshal[0] if launch._marshal is not None else None
         if hit is not None and hit[0] == sig and sig is not None:
             return hit[1]
         need = ctypes.c_size_t(0)
@@ -104,7 +104,7 @@ class GCUKernelExecutor:
             outputs = [torch.empty(shape, dtype=dt, device=device)
                        for shape, dt in zip(launch.out_shapes, launch.out_dtypes)]
         sig = tuple((t.shape, t.stride(), t.dtype) for t in ins) + tuple((t.shape, t.stride(), t.dtype) for t in outputs)
-        m = getattr(launch, "_marshal", None)
+        m = launch._marshal
         if m is None or m[0] != sig:
             in_desc, out_desc = make_descriptors(ins), make_descriptors(outputs)
             if launch.params is not None:
