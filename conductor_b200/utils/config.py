@@ -57,7 +57,7 @@ class RuntimeConfig:
     use_cuda_graphs: bool = False
     # host-tensor calls of a batch-parallel graph are cut into row chunks of about this many input
     # bytes so that copies in, kernels and copies out overlap inside one call (0 = never chunk)
-    host_chunk_bytes: int = 4 << 20
+    host_chunk_bytes: int = 8 << 20
     host_max_chunks: int = 8
 
 
