@@ -157,6 +157,13 @@ __device__ __forceinline__ void poly_exp2_pair(uint64_t x, float& p0, float& p1)
   p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
 }
 
+// 256-bit global store (sm_100): p must be 32-byte aligned
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
   if (BF16) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
@@ -557,6 +564,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       sm100::tc_fence_after();
       const float inv = 1.0f / (l0 + l1);
       unsigned char* orow = static_cast<unsigned char*>(a.out) + (static_cast<size_t>(t.bh) * a.S + row) * (HD * 2);
+      const bool wide_store = (reinterpret_cast<uintptr_t>(a.out) & 31u) == 0;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -568,13 +576,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
           if (lane == 0) sm100::mbar_arrive(&bars[B_OFREE + g]);
         }
         if (row < a.S) {
+          // 32 output columns = 64 bytes of this thread's row: two 256-bit stores, each a whole 32-byte sector
+          // (rows are 2*HD bytes apart and the output is 16-byte aligned, so row starts are 32-byte aligned
+          // whenever the base is; otherwise four 128-bit stores)
+          uint32_t w[16];
 #pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            uint32_t w[4];
+          for (int tt = 0; tt < 16; ++tt)
+            w[tt] = pack_pair<BF16>(__uint_as_float(o[tt * 2]) * inv, __uint_as_float(o[tt * 2 + 1]) * inv);
+          if (wide_store) {
+            st_global_v8(orow + c * 64, w);
+            st_global_v8(orow + c * 64 + 32, w + 8);
+          } else {
 #pragma unroll
-            for (int tt = 0; tt < 4; ++tt)
-              w[tt] = pack_pair<BF16>(__uint_as_float(o[gq * 8 + tt * 2]) * inv, __uint_as_float(o[gq * 8 + tt * 2 + 1]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 64 + gq * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int gq = 0; gq < 4; ++gq)
+              *reinterpret_cast<uint4*>(orow + c * 64 + gq * 16) = make_uint4(w[gq * 4], w[gq * 4 + 1], w[gq * 4 + 2], w[gq * 4 + 3]);
           }
         }
       }
