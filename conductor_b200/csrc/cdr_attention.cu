@@ -48,7 +48,10 @@
 // by integer add + byte permute instead of cvt (no change: the conversion runs on the half-rate
 // ALU pipe, not on the special-function unit); polynomial exp2 for 2/8 or 4/8 of the pairs with
 // sixteen warps (-1 %, -6 %: with half-rate f32x2 arithmetic the cubic costs more issue cycles than
-// the special-function time it frees).
+// the special-function time it frees); Q buffers and barriers per half with the first scores of
+// the next tile issued for half A as soon as it finishes its last block of the current one, so that
+// under a causal mask its softmax runs beside half B's last block (-3 % on every shape, the
+// non-causal ones included: the longer issue loop of the MMA warp costs more than the overlap gains).
 #include <cuda.h>
 #include <math.h>
 
