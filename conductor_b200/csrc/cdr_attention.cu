@@ -51,7 +51,9 @@
 // the special-function time it frees); Q buffers and barriers per half with the first scores of
 // the next tile issued for half A as soon as it finishes its last block of the current one, so that
 // under a causal mask its softmax runs beside half B's last block (-3 % on every shape, the
-// non-causal ones included: the longer issue loop of the MMA warp costs more than the overlap gains).
+// non-causal ones included: the longer issue loop of the MMA warp costs more than the overlap gains);
+// an epilogue that keeps the next chunk's tcgen05.ld in flight while the current one is stored (-2 %).
+// What did pay in the epilogue: 256-bit stores (two per 32 columns instead of four 128-bit ones), +4 %.
 #include <cuda.h>
 #include <math.h>
 
