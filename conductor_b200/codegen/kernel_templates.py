@@ -58,7 +58,7 @@ class CdrReduceParams(ctypes.Structure):
 
 class CdrGemmParams(ctypes.Structure):
     _fields_ = [("activation", ctypes.c_int32), ("has_bias", ctypes.c_int32), ("weight_layout", ctypes.c_int32),
-                ("x_layout", ctypes.c_int32)]
+                ("x_layout", ctypes.c_int32), ("gate_input", ctypes.c_int32)]
 
 
 class CdrNormParams(ctypes.Structure):

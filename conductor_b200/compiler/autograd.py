@@ -72,14 +72,16 @@ def require_differentiable(launches) -> None:
 # as the transposed operands the three products need, so no tensor is ever transposed in memory.
 #   dX = dY @ W              x = dY [M, N],            W [N, K] read as [K'=N, N'=K]   (weight_layout KN)
 #   dW = dY^T @ x            x = dY read as [K'=M, M'=N] (x_layout KM), W = x [M, K] read as [K'=M, N'=K]
+#   dZ = dX * (H > 0)         the ReLU in front of a layer gates that layer's input gradient inside the epilogue of the
+#                             product that makes it (gate_input), so the gradient never makes a trip through memory
 #   db = sum over rows of dY  the column-sum template (HBM-bound: dY is read once; as a product with a row
 #                             of ones the GEMM template ran it on N/256 CTAs and took as long as a full GEMM)
-# and the ReLU mask dZ = dH * (H > 0) is one elementwise launch.
+# Only a ReLU on the chain's OUTPUT needs its own launch (dZ = grad * (H > 0), one elementwise kernel).
 @functools.lru_cache(maxsize=256)
-def _gemm_launch(name, out_shape, dtype, weight_layout=0, x_layout=0) -> KernelLaunch:
+def _gemm_launch(name, out_shape, dtype, weight_layout=0, x_layout=0, gate=0) -> KernelLaunch:
     from ..codegen.kernel_templates import CdrGemmParams
 
-    return KernelLaunch(Template.GEMM_EPILOGUE, name, [], [], CdrGemmParams(0, 0, weight_layout, x_layout),
+    return KernelLaunch(Template.GEMM_EPILOGUE, name, [], [], CdrGemmParams(0, 0, weight_layout, x_layout, gate),
                         [tuple(out_shape)], [dtype])
 
 
@@ -169,7 +171,8 @@ class LinearChainFunction(torch.autograd.Function):
             g2 = g.reshape(-1, N)
             x2 = x.reshape(-1, K)
             M = g2.shape[0]
-            if launch.params.activation == 1:
+            if launch.params.activation == 1 and i == n - 1:
+                # a ReLU on the chain's output gates the incoming gradient itself
                 masked = out((M, N))
                 steps.append((_relu_mask_launch((M, N), dt), [g2, h.reshape(-1, N)], [masked]))
                 g2 = masked
@@ -184,7 +187,11 @@ class LinearChainFunction(torch.autograd.Function):
                 g = None                     # nobody asked for d/dx of the chain's input: skip that product
                 break
             dx = out((M, K))
-            steps.append((_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w], [dx]))
+            if i > 0 and layers[i - 1][0].params.activation == 1:
+                # x is the previous layer's ReLU output: gate this gradient by (x > 0) in the epilogue
+                steps.append((_gemm_launch("input_grad_relu[autograd]", (M, K), dt, weight_layout=1, gate=1), [g2, w, x2], [dx]))
+            else:
+                steps.append((_gemm_launch("input_grad[autograd]", (M, K), dt, weight_layout=1), [g2, w], [dx]))
             g = dx.reshape(x.shape)
         ex.execute_many(steps)                # every gradient launch of the chain in one call into the library
         return (None, None, g, *param_grads)

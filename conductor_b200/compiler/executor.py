@@ -65,6 +65,7 @@ class GCUKernelExecutor:
     def __init__(self):
         self.lib = load_library()
         self._workspaces: dict[tuple, tuple] = {}
+        self._item_cache: dict[tuple, tuple] = {}
 
     def workspace_for(self, launch: KernelLaunch, ins, outs, in_desc, out_desc, params_ptr, params_size):
         """Scratch of the size the library asks for, one buffer per (device, launch).  Launches that
@@ -162,14 +163,27 @@ class GCUKernelExecutor:
             nonlocal batch, seen
             if not batch:
                 return
-            items = (CdrLaunchItem * len(batch))()
-            for it, (launch, (dev, ins, outs, in_desc, out_desc, pp, ps, ws)) in zip(items, batch):
-                it.template_id, it.n_inputs, it.n_outputs = launch.template, len(ins), len(outs)
-                it.inputs, it.outputs = ctypes.addressof(in_desc), ctypes.addressof(out_desc)
-                it.params = pp.value if pp is not None else None
-                it.params_bytes = ps
-                it.workspace = ws.data_ptr() if ws is not None else None
-                it.workspace_bytes = ws.numel() if ws is not None else 0
+            # The item array only holds addresses of per-launch state (descriptor arrays, parameter
+            # block, scratch) that is refreshed in place, so it is built once per sequence of launch
+            # objects and reused while none of them was re-marshalled.
+            key = tuple(id(launch) for launch, _ in batch)
+            stamp = tuple((id(p[3]), launch.template, len(p[1]), len(p[2]), p[6], p[7].data_ptr() if p[7] is not None else 0)
+                          for launch, p in batch)
+            cached = self._item_cache.get(key)
+            if cached is not None and cached[0] == stamp:
+                items = cached[1]
+            else:
+                items = (CdrLaunchItem * len(batch))()
+                for it, (launch, (dev, ins, outs, in_desc, out_desc, pp, ps, ws)) in zip(items, batch):
+                    it.template_id, it.n_inputs, it.n_outputs = launch.template, len(ins), len(outs)
+                    it.inputs, it.outputs = ctypes.addressof(in_desc), ctypes.addressof(out_desc)
+                    it.params = pp.value if pp is not None else None
+                    it.params_bytes = ps
+                    it.workspace = ws.data_ptr() if ws is not None else None
+                    it.workspace_bytes = ws.numel() if ws is not None else 0
+                if len(self._item_cache) > 256:
+                    self._item_cache.clear()
+                self._item_cache[key] = (stamp, items)
             stream = torch.cuda.current_stream(device).cuda_stream
             failed = ctypes.c_int(-1)
             if torch.cuda.current_device() == device.index:

@@ -55,6 +55,7 @@ struct GemmArgs {
   CUtensorMap tmap_a;  // x  [M, K], box 64 x 128 -- or, with x_km, x [K, M], box 64 (M) x 64 (K)
   CUtensorMap tmap_b;  // W  [N, K], box 64 x 256 -- or, with w_kn, W [K, N], box 64 (N) x 64 (K)
   const void* bias;    // [N] or nullptr
+  const void* gate;    // [M, N] or nullptr: entries <= 0 (or NaN) zero the result at their position
   void* out;           // [M, N]
   int M, N, K;
   int relu;
@@ -102,12 +103,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base
   uint32_t r[2][32];
   sm100::tmem_ld32(t_base + c_begin * 32, r[0]);
   const bool bias_vec = a.bias != nullptr && vec_ok && (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0;
+  if (a.gate != nullptr && (reinterpret_cast<uintptr_t>(a.gate) & 15u) != 0) vec_ok = false;   // the scalar path reads the gate element-wise
 #pragma unroll
   for (int cc = 0; cc < CHUNKS; ++cc) {
     const int c = c_begin + cc;
     const int col0 = n0 + c * 32;
     const bool full_chunk = vec_ok && col0 + 32 <= a.N;
     uint4 bq[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    uint4 gq[4];
+    const bool gated = a.gate != nullptr;
+    if (gated && full_chunk && row < a.M) {      // 64 bytes of this thread's row of the gate tensor
+      const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.gate) +
+                                                       (static_cast<size_t>(row) * a.N + col0) * 2);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) gq[g] = __ldg(gp + g);
+    }
     if (bias_vec && full_chunk) {
       const uint4* bp = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.bias) + static_cast<size_t>(col0) * 2);
 #pragma unroll
@@ -142,6 +152,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base
                 v = *reinterpret_cast<uint32_t*>(&t);
               }
             }
+            if (gated) {
+              // both 16-bit floats are sign + magnitude: positive means sign clear and magnitude non-zero (NaN counts
+              // as not positive, as in `H > 0`)
+              const uint32_t gw = (&gq[g].x)[h];
+              const uint32_t lo = (gw & 0x8000u) == 0 && (gw & 0x7fffu) != 0 && (gw & 0x7fffu) <= (BF16 ? 0x7f80u : 0x7c00u) ? 0x0000ffffu : 0u;
+              const uint32_t hw = gw >> 16;
+              const uint32_t hi = (hw & 0x8000u) == 0 && (hw & 0x7fffu) != 0 && (hw & 0x7fffu) <= (BF16 ? 0x7f80u : 0x7c00u) ? 0xffff0000u : 0u;
+              v &= lo | hi;
+            }
             w[g * 4 + h] = v;
           }
         }
@@ -158,6 +177,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, uint32_t t_base
           float x = __uint_as_float(rc[j]);
           if (a.bias != nullptr) x += load_elem<BF16>(a.bias, col0 + j);
           if (a.relu) x = x > 0.0f ? x : (x != x ? x : 0.0f);
+          if (gated) {
+            const float gv = BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.gate)[off + j])
+                                  : __half2float(static_cast<const __half*>(a.gate)[off + j]);
+            if (!(gv > 0.0f)) x = 0.0f;
+          }
           store_elem<BF16>(a.out, off + j, x);
         }
       }
@@ -522,7 +546,7 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t 
 int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                          const cdr_gemm_params* p, cudaStream_t stream) {
   if (!p) { set_error("gemm_epilogue: params is null"); return CDR_ERR_BAD_ARG; }
-  const int want_in = p->has_bias ? 3 : 2;
+  const int want_in = 2 + (p->has_bias ? 1 : 0) + (p->gate_input ? 1 : 0);
   if (n_in != want_in || n_out != 1) {
     set_error("gemm_epilogue: expects %d inputs and 1 output, got %d and %d", want_in, n_in, n_out);
     return CDR_ERR_BAD_ARG;
@@ -575,6 +599,15 @@ int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs
                     : make_tensor_map_2d(&a.tmap_b, w.data, dt == CDR_BF16, N, K, BN, BK)) return rc;
   a.w_kn = w_kn ? 1 : 0;
   a.bias = p->has_bias ? ins[2].data : nullptr;
+  a.gate = nullptr;
+  if (p->gate_input) {
+    const cdr_tensor& gt = ins[want_in - 1];
+    if (gt.dtype != dt || numel(gt) != M * N || !is_contiguous(gt) || !gt.data) {
+      set_error("gemm_epilogue: the gate tensor must be contiguous, of the output's dtype and element count");
+      return CDR_ERR_BAD_ARG;
+    }
+    a.gate = gt.data;
+  }
   a.out = out.data;
   a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
   a.relu = p->activation == CDR_ACT_RELU;

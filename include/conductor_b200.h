@@ -205,6 +205,10 @@ typedef struct cdr_gemm_params {
   int32_t has_bias;      /* 1: inputs are (x, W, bias); 0: (x, W)     */
   int32_t weight_layout; /* enum cdr_weight_layout                    */
   int32_t x_layout;      /* enum cdr_x_layout                         */
+  int32_t gate_input;    /* 1: the LAST input is a tensor shaped like the output whose positive entries let the
+                            result through and whose other entries zero it: out = (gate > 0) ? result : 0.
+                            The backward of a ReLU fused into the product that makes its incoming gradient
+                            (dZ = (dY @ W) * (H > 0)).  The reference has no counterpart (no backward graphs) */
 } cdr_gemm_params;
 
 typedef struct cdr_norm_params {

@@ -615,6 +615,29 @@ def test_gemm_shapes_against_oracle(executor, M, N, K, relu):
     assert_close(out.float(), want, BF16_TOL, f"gemm {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("M,N,K,dtype", [(512, 768, 256, torch.bfloat16), (300, 520, 136, torch.bfloat16), (130, 257, 64, torch.float16),
+                                         (1024, 1024, 512, torch.bfloat16)])
+def test_gemm_with_gated_output(executor, M, N, K, dtype):
+    """`gate_input`: out = (gate > 0) ? x @ W^T : 0 -- the backward of a ReLU fused into the product that
+    makes its incoming gradient.  Vector path (whole 16-byte rows), scalar path (ragged N) and the special
+    gate values: -0.0, +inf (positive), -inf, NaN (not positive)."""
+    gen = torch.Generator().manual_seed(M + 3 * N + K)
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    w = (torch.randn(N, K, generator=gen) / K ** 0.5).to(dtype)
+    gate = torch.relu(torch.randn(M, N, generator=gen)).to(dtype)           # about half zeros, like a ReLU output
+    gate[0, :6] = torch.tensor([-0.0, float("inf"), float("-inf"), float("nan"), 1e-30, -1.0]).to(dtype)
+    want = torch.nn.functional.linear(x.float(), w.float()) * (gate.float() > 0)
+    xd, wd, gd = cuda(x, w, gate)
+    out = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
+    abi.launch(Template.GEMM_EPILOGUE, [xd, wd, gd], [out], CdrGemmParams(0, 0, 0, 0, 1))
+    assert_close(out.float(), want, BF16_TOL, f"gated gemm {M}x{N}x{K}")
+    zeros_expected = ~(gate.float() > 0)
+    assert bool((out.cpu()[zeros_expected] == 0).all())                      # exact zeros where the gate is closed
+    # the gate must match the output's shape and dtype
+    bad = torch.zeros(M, N + 1, dtype=dtype, device=DEV)
+    assert abi.launch(Template.GEMM_EPILOGUE, [xd, wd, bad], [out], CdrGemmParams(0, 0, 0, 0, 1), check=False) == -1
+
+
 def test_gemm_without_bias_fp16_and_3d_input(executor):
     gen = torch.Generator().manual_seed(77)
     x = torch.randn(4, 50, 96, generator=gen).half()
