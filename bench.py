@@ -463,8 +463,9 @@ class Measurement:
                 s.plan, s.sets = plan, sets
 
             def replay(s):
-                for inp in s.sets:
-                    s.plan(*inp)
+                with torch.no_grad():
+                    for inp in s.sets:
+                        s.plan(*inp)
 
         def build(n):
             sets = [pool[i % pool_n] for i in range(n)]
