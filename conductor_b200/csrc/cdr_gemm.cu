@@ -20,6 +20,10 @@
 // It made the two-layer step 8 % slower (130 against 120 us): the pairs no longer walk the
 // k-blocks of a shared weight tile in step, and the partial tiles add an L2 round trip to the
 // epilogue.  Programmatic dependent launch between the two layers is in place and is neutral.
+// Sixteen epilogue warps (four per TMEM lane quadrant) instead of eight: the K=1024 layer, whose
+// epilogue per tile (8.4k cycles by clock64) is as long as its 16 k-blocks of MMAs and stalls the
+// MMA warp for 12 % of the time, went 55-61 -> 63-64 us (96 registers per thread at 576 threads
+// spill the double-buffered accumulator chunks).
 #include <cuda.h>
 
 #include <cstdlib>
