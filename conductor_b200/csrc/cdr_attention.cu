@@ -19,7 +19,8 @@
 //               per MMA, more than the 64 cycles a 128x128x16 MMA executes in)
 //   warps 2-3   idle: they complete the control warp group so that setmaxnreg can hand its
 //               registers (80 per thread kept) to the softmax groups (208 per thread, no spills)
-//   warps 4-7   softmax of half A, warps 8-11 of half B: one query row per thread; tcgen05.ld
+//   warps 4-7   softmax of half A, warps 8-11 of half B (and the tile's epilogue: O / l packed into a
+//               2 KB shared-memory stage per warp and written by tiled TMA stores): one query row per thread; tcgen05.ld
 //               the S row, running max (3-input max) / sum in the log2 domain, P = exp2(..) with
 //               two-lane fp32 instructions (a cubic on the FMA pipes can take pairs off the
 //               special-function unit, CDR_ATT_EMU, but no share of it paid off), stored back to TMEM with tcgen05.st; the O
@@ -53,7 +54,8 @@
 // under a causal mask its softmax runs beside half B's last block (-3 % on every shape, the
 // non-causal ones included: the longer issue loop of the MMA warp costs more than the overlap gains);
 // an epilogue that keeps the next chunk's tcgen05.ld in flight while the current one is stored (-2 %).
-// What did pay in the epilogue: 256-bit stores (two per 32 columns instead of four 128-bit ones), +4 %.
+// What did pay in the epilogue: 256-bit stores (two per 32 columns instead of four 128-bit ones), +4 %,
+// and then handing the stores to the TMA unit from per-warp shared-memory stages, +1.5 % more.
 #include <cuda.h>
 #include <math.h>
 
@@ -81,6 +83,8 @@ namespace cdr {
 
 int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t d0, int64_t d1, int64_t d2,
                        int box0, int box1);
+int make_tensor_map_3d_plain(CUtensorMap* map, const void* base, int is_bf16, int64_t d0, int64_t d1, int64_t d2,
+                             int box0, int box1);
 
 namespace {
 
@@ -95,6 +99,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnArgs {
   CUtensorMap tmap_q, tmap_k, tmap_v;  // [BH, S, D] each, box 64 x 128 x 1
+  CUtensorMap tmap_o;                  // the output, [BH, S, D], box 32 x 32 x 1, no swizzle (epilogue stores)
   void* out;                            // [BH, S, D]
   unsigned int* next_tile;              // global scratch: tiles handed out beyond the first one per CTA
   int S, BH, n_qtiles;
@@ -114,8 +119,10 @@ struct AttnSmem {
   static constexpr int Q_OFF = 0;                      // 2 halves
   static constexpr int KV_OFF = 2 * TILE_BYTES;        // KV_STAGES tiles
   static constexpr int BAR_OFF = KV_OFF + KV_STAGES * TILE_BYTES;
-  static constexpr int PROF_OFF = BAR_OFF + 256;
-  static constexpr size_t TOTAL = BAR_OFF + 256 + PROF_SLOTS * 8 + 1024;
+  static constexpr int STAGE_OFF = BAR_OFF + 256;            // 8 softmax warps x (32 rows x 64 bytes): epilogue store stages
+  static constexpr int STAGE_BYTES = 8 * 32 * 64;
+  static constexpr int PROF_OFF = STAGE_OFF + STAGE_BYTES;
+  static constexpr size_t TOTAL = PROF_OFF + PROF_SLOTS * 8 + 1024;
 };
 
 // barrier indices; ring barriers are indexed by stage, the others by half
@@ -160,13 +167,6 @@ __device__ __forceinline__ void poly_exp2_pair(uint64_t x, float& p0, float& p1)
   unpack2(r, r0, r1);
   p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
   p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
-}
-
-// 256-bit global store (sm_100): p must be 32-byte aligned
-__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
-               : "memory");
 }
 
 template <bool BF16>
@@ -261,6 +261,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
     sm100::prefetch_tensormap(&a.tmap_q);
     sm100::prefetch_tensormap(&a.tmap_k);
     sm100::prefetch_tensormap(&a.tmap_v);
+    sm100::prefetch_tensormap(&a.tmap_o);
     for (int i = 0; i < B_COUNT; ++i) {
       const bool per_warp = (i >= B_PFULL && i < B_PFULL + 2) || (i >= B_OFREE && i < B_OFREE + 2);
       const bool slot_free = i >= B_TEMPTY && i < B_TEMPTY + TILE_SLOTS;
@@ -568,8 +569,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
       PROF_ADD(pw, pb + 8);
       sm100::tc_fence_after();
       const float inv = 1.0f / (l0 + l1);
-      unsigned char* orow = static_cast<unsigned char*>(a.out) + (static_cast<size_t>(t.bh) * a.S + row) * (HD * 2);
-      const bool wide_store = (reinterpret_cast<uintptr_t>(a.out) & 31u) == 0;
+      // Each warp packs 32 columns of its 32 rows into its shared-memory stage and hands them to the TMA
+      // unit (one tiled store per chunk, issued by lane 0): the global stores leave the softmax warps'
+      // path, and rows beyond S are clipped by the tensor map.
+      unsigned char* stage = smem + L::STAGE_OFF + (warp - SOFTMAX_WARP0) * (32 * 64);
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -580,26 +583,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_kernel(const __grid_
           __syncwarp();
           if (lane == 0) sm100::mbar_arrive(&bars[B_OFREE + g]);
         }
-        if (row < a.S) {
-          // 32 output columns = 64 bytes of this thread's row: two 256-bit stores, each a whole 32-byte sector
-          // (rows are 2*HD bytes apart and the output is 16-byte aligned, so row starts are 32-byte aligned
-          // whenever the base is; otherwise four 128-bit stores)
-          uint32_t w[16];
+        uint32_t w[16];
 #pragma unroll
-          for (int tt = 0; tt < 16; ++tt)
-            w[tt] = pack_pair<BF16>(__uint_as_float(o[tt * 2]) * inv, __uint_as_float(o[tt * 2 + 1]) * inv);
-          if (wide_store) {
-            st_global_v8(orow + c * 64, w);
-            st_global_v8(orow + c * 64 + 32, w + 8);
-          } else {
+        for (int tt = 0; tt < 16; ++tt)
+          w[tt] = pack_pair<BF16>(__uint_as_float(o[tt * 2]) * inv, __uint_as_float(o[tt * 2 + 1]) * inv);
+        if (lane == 0) sm100::bulk_wait_read<0>();      // the previous store has read the stage
+        __syncwarp();
 #pragma unroll
-            for (int gq = 0; gq < 4; ++gq)
-              *reinterpret_cast<uint4*>(orow + c * 64 + gq * 16) = make_uint4(w[gq * 4], w[gq * 4 + 1], w[gq * 4 + 2], w[gq * 4 + 3]);
-          }
+        for (int gq = 0; gq < 4; ++gq)
+          *reinterpret_cast<uint4*>(stage + lane * 64 + gq * 16) = make_uint4(w[gq * 4], w[gq * 4 + 1], w[gq * 4 + 2], w[gq * 4 + 3]);
+        sm100::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          sm100::tma_store_3d(&a.tmap_o, stage, c * 32, row0 + q * 32, t.bh);
+          sm100::bulk_commit();
         }
       }
       PROF_ADD(pw, pb + 9);
     }
+    if (lane == 0) sm100::bulk_wait<0>();     // every output store of this warp has completed
   }
 
   sm100::tc_fence_before();
@@ -702,6 +704,7 @@ int launch_attention(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, in
   if (int rc = make_tensor_map_3d(&a.tmap_q, ins[0].data, bf16, D, S, BH, 64, 128)) return rc;
   if (int rc = make_tensor_map_3d(&a.tmap_k, ins[1].data, bf16, D, S, BH, 64, 128)) return rc;
   if (int rc = make_tensor_map_3d(&a.tmap_v, ins[2].data, bf16, D, S, BH, 64, 128)) return rc;
+  if (int rc = make_tensor_map_3d_plain(&a.tmap_o, out.data, bf16, D, S, BH, 32, 32)) return rc;
   a.out = out.data;
   a.S = static_cast<int>(S);
   a.BH = static_cast<int>(BH);

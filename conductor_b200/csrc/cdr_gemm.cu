@@ -549,6 +549,22 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int is_bf16, int64_t 
   return CDR_OK;
 }
 
+// Same tensor without swizzle: the layout a TMA store reads from a plain row-major shared-memory box.
+int make_tensor_map_3d_plain(CUtensorMap* map, const void* base, int is_bf16, int64_t d0, int64_t d1, int64_t d2,
+                             int box0, int box1) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return CDR_ERR_CUDA; }
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d0), static_cast<cuuint64_t>(d1), static_cast<cuuint64_t>(d2)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(d0) * 2, static_cast<cuuint64_t>(d0) * d1 * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(box0), static_cast<cuuint32_t>(box1), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (3-D, plain) failed with %d", static_cast<int>(r)); return CDR_ERR_CUDA; }
+  return CDR_OK;
+}
+
 int launch_gemm_epilogue(const cdr_tensor* ins, int n_in, const cdr_tensor* outs, int n_out,
                          const cdr_gemm_params* p, cudaStream_t stream) {
   if (!p) { set_error("gemm_epilogue: params is null"); return CDR_ERR_BAD_ARG; }
