@@ -182,3 +182,56 @@ def test_shard_polymorphic_plan_on_gpu():
     sc = ShardedCallable.from_artifact(plan.artifact, n_devices=1)
     (again,) = sc(x.cuda(), w.cuda(), b.cuda())
     assert torch.equal(again, full)
+
+
+# ---------------------------------------------------------------- row chunks of host-tensor calls (decision logic, CPU)
+def _callable_for(fn, inputs):
+    import conductor  # noqa: F401
+    from conductor_b200.compiler.callable import Callable
+    from conductor_b200.compiler.jit_compiler import ChoreoJITCompiler
+
+    box = {}
+
+    def backend(gm, ex):
+        box["plan"] = Callable(ChoreoJITCompiler().compile_graph(gm, ex), gm)
+        return gm.forward
+
+    torch._dynamo.reset()
+    with torch.no_grad():
+        torch.compile(fn, backend=backend)(*inputs)
+    torch._dynamo.reset()
+    return box["plan"]
+
+
+def test_host_calls_are_cut_into_row_chunks_only_for_row_parallel_plans():
+    from conductor_b200.utils.config import get_config
+
+    cfg = get_config().runtime
+    old = (cfg.host_chunk_bytes, cfg.host_max_chunks)
+    try:
+        cfg.host_chunk_bytes, cfg.host_max_chunks = 1 << 20, 8
+        a, b, c = wl.inputs_mul_add(1000, 512, seed=1)                     # 3 x 2,048,000 bytes of batch inputs: five chunks of at least 1 MiB
+        plan = _callable_for(wl.mul_add, [a, b, c])
+        chunks = plan._host_chunks([a, b, c])
+        assert chunks is not None and chunks[0][0] == 0 and chunks[-1][1] == 1000 and len(chunks) == 5
+        assert all(e0 == s1 for (_, e0), (s1, _) in zip(chunks, chunks[1:]))   # contiguous, no gaps
+        assert plan._host_chunks([t[:4].contiguous() for t in (a, b, c)]) is None   # another batch size: one piece
+        cfg.host_chunk_bytes = 0
+        assert plan._host_chunks([a, b, c]) is None                           # switched off
+        cfg.host_chunk_bytes = 1 << 20
+        small = wl.inputs_mul_add(16, 64, seed=2)
+        assert _callable_for(wl.mul_add, small)._host_chunks(small) is None     # too small to be worth it
+        # a layout change ties the plan to the full shapes
+        x = torch.randn(1024, 512)
+        assert _callable_for(lambda t: t.t().contiguous() + 1.0, [x])._host_chunks([x]) is None
+        # a reduction over the rows is not row-parallel
+        assert _callable_for(lambda t: t.sum(), [x])._host_chunks([x]) is None
+        # a product whose right operand has as many rows as the batch: the weight must stay whole
+        y = torch.randn(1024, 512)
+        p2 = _callable_for(lambda u, v: torch.nn.functional.linear(u, v), [x.bfloat16(), y.bfloat16()])
+        assert p2._host_chunks([x.bfloat16(), y.bfloat16()]) is None or p2._chunk_plan[1] == [0]
+        # row softmax and the mean-fusion graph are
+        lg = wl.inputs_softmax(2048, 512, seed=3)[:1]
+        assert _callable_for(wl.softmax_forward, lg)._host_chunks(lg) is not None
+    finally:
+        cfg.host_chunk_bytes, cfg.host_max_chunks = old
