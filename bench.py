@@ -533,8 +533,54 @@ class Measurement:
             "gpu_launches": passes * self.kernels_per_pass, "roofline": roofline,
             "clocks": clocks.window(t_wall0, t_wall1) if clocks is not None else None,
         }
-        del sequence, pool
+        if args.with_library and world == 1:
+            del sequence
+            result["library"] = self.library(pool, pool_n, region, own_ms / passes)
+        del pool
         return result
+
+    # ------------------------------------------------------------ the same passes through PyTorch's own kernels
+    def library(self, pool, pool_n: int, region: float, own_pass_ms: float) -> dict:
+        """Eager PyTorch (cuBLAS, its fused attention, ATen kernels) over the same rotating pool,
+        replayed from a CUDA graph and timed the same way: a comparison beside the product path, not part of it."""
+        wl = self.wl
+        fn = wl.module if wl.module is not None else wl.fn
+        pick = (lambda ph: [ph[i] for i in self.batch_idx]) if wl.module is not None else (lambda ph: list(ph))
+        side = torch.cuda.Stream()
+        with torch.no_grad():
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(3):
+                    fn(*pick(pool[i % pool_n]))
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            keep = []
+            with torch.cuda.graph(graph):
+                for i in range(pool_n):
+                    out = fn(*pick(pool[i]))
+                    if i == 0:
+                        keep.append(out)
+                    del out
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        replays = max(3, math.ceil(region * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+        for _ in range(3):
+            graph.replay()
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (replays * pool_n)
+        del graph, keep
+        return {"what": "eager PyTorch on the same pool, CUDA-graph replays", "ms_per_pass": ms,
+                "conductor_b200_ms_per_pass": own_pass_ms, "library_over_conductor_b200": ms / own_pass_ms}
 
     # ------------------------------------------------------------ all-gather of the outputs
     def allgather(self, start: int, stop: int) -> dict:
@@ -735,6 +781,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="short device-resident regions only (for profiler runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the plan directly instead of replaying a CUDA graph")
+    ap.add_argument("--with-library", action="store_true",
+                    help="one GPU: also time eager PyTorch's own kernels on the same batches (per_config[*].library)")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="with one GPU: time the row block rank 0 of a world of this size would run (value then counts "
                          "the whole configuration per pass, i.e. what that world would reach if every rank kept this pace)")

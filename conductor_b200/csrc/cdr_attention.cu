@@ -54,6 +54,26 @@
 // under a causal mask its softmax runs beside half B's last block (-3 % on every shape, the
 // non-causal ones included: the longer issue loop of the MMA warp costs more than the overlap gains);
 // an epilogue that keeps the next chunk's tcgen05.ld in flight while the current one is stored (-2 %).
+// Structural variants, all measured on one box against this kernel (193 / 1052 / 617 us at C5, S=8192
+// non-causal, S=8192 causal) and dropped: (1) the two halves as independent chains with their own
+// 128-row work items, Q buffer, two-slot K/V ring, TMA warp and MMA warp: 206 / 1219 / 696 (a K/V block
+// is then fetched from L2 once per chain; with those fetches halved for diagnosis still 201 / 1110 / 657);
+// (2) P handed over through shared memory in the K-major swizzled operand layout instead of over S in
+// tensor memory, so that S(j+1) is issued as soon as S(j) is in registers and runs under the
+// exponentials of block j, one MMA warp per half, a three-slot ring in consumption order: the wait for
+// the scores falls from ~1700 to ~230 cycles per block, but the total is 195.6 / 1021 / 607 -- every
+// MMA then reads both operands from shared memory, P adds 64 KB of writes per block pair, and the
+// halves' exponential passes fall into step; making the paired warps of a scheduler take turns at the
+// exponentials made it 301 / 1723 / 1044; (3) this kernel with one MMA-issuing warp per half:
+// 207 / 1265 / 692.  With the exponentials replaced by a multiplication (wrong results, diagnosis
+// only) this kernel runs 183 / 1061 / 614: the softmax pass is bound by the latency of its dependent
+// instruction chains at one warp per scheduler, not by the special-function unit's throughput.
+// Micro-benchmarks beside it: a 128x128x16 MMA executes in 64.6 cycles whatever the source and layout of
+// its operands (52.7 at N=64, 128.6 at N=256); the issuing thread stays blocked while the pipe works
+// (a batch of 16 MMAs returns after 935 cycles: about one and a half MMAs are queued), and the commit
+// is seen about 210 cycles after the last MMA was issued.  Per block and half the chain is therefore
+// softmax (~2100 cycles) + P.V and the next scores (1034) + hand-over latency; taking the MMAs off it
+// needs S and P side by side in tensor memory, which two halves at head dimension 128 leave no room for.
 // What did pay in the epilogue: 256-bit stores (two per 32 columns instead of four 128-bit ones), +4 %,
 // and then handing the stores to the TMA unit from per-warp shared-memory stages, +1.5 % more.
 #include <cuda.h>
