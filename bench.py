@@ -48,6 +48,7 @@ import torch  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 POOL_BYTES_MIN = 4 * L2_BYTES          # rotating pool (inputs + outputs) is at least this large
 MAX_POOL = 64
+LANES = 2            # passes in flight in the timed sequences: one pass's ramp-up and tail overlap the other's steady state
 MAX_SEQ = 1024                         # passes captured in one CUDA graph
 REGION_S = 0.6                         # every timed region lasts at least this long
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -467,9 +468,9 @@ class Measurement:
                     for inp in s.sets:
                         s.plan(*inp)
 
-        def build(n):
+        def build(n, lanes):
             sets = [pool[i % pool_n] for i in range(n)]
-            seq = _Direct(self.plan, sets) if args.no_graphs else self.plan.capture_sequence(sets, keep_outputs="first")
+            seq = _Direct(self.plan, sets) if args.no_graphs else self.plan.capture_sequence(sets, keep_outputs="first", lanes=lanes)
             seq.replay()
             torch.cuda.synchronize()
             e0.record()
@@ -479,62 +480,80 @@ class Measurement:
             torch.cuda.synchronize()
             return seq, max(e0.elapsed_time(e1) / 2, 1e-3)
 
-        sequence, replay_ms = build(seq_len)
-        # the first estimate came from direct launches, which are launch-bound for microsecond kernels:
-        # one graph replay should last a few milliseconds, so that the host's replay calls stay far ahead
-        grown = seq_len
-        if not args.no_graphs and replay_ms < 3.0 and seq_len < MAX_SEQ:
-            grown = int(min(MAX_SEQ, seq_len * math.ceil(4.0 / replay_ms)))
-            grown = max(pool_n, grown // pool_n * pool_n)
-        if grown > seq_len:
+        def timed(lanes, n0, with_clocks):
+            """One timed region: `steps` steps of back-to-back replays of a captured sequence with `lanes`
+            independent passes in flight."""
+            n = n0
+            sequence, replay_ms = build(n, lanes)
+            # the first estimate came from direct launches, which are launch-bound for microsecond kernels:
+            # one graph replay should last a few milliseconds, so that the host's replay calls stay far ahead
+            grown = n
+            if not args.no_graphs and replay_ms < 3.0 and n < MAX_SEQ:
+                grown = int(min(MAX_SEQ, n * math.ceil(4.0 / replay_ms)))
+                grown = max(pool_n, grown // pool_n * pool_n)
+            if grown > n:
+                del sequence
+                n = grown
+                sequence, replay_ms = build(n, lanes)
+            region = 0.05 if args.quick else REGION_S
+            replays_per_step = max(1, math.ceil(region * 1e3 / (args.steps * replay_ms)))
+            for _ in range(max(args.warmup, 3) * replays_per_step if not args.quick else 1):
+                sequence.replay()
+            barrier(world)
+            t_wall0 = time.monotonic()
+            e0.record()
+            for _ in range(args.steps * replays_per_step):
+                sequence.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            t_wall1 = time.monotonic()
+            own = e0.elapsed_time(e1)
+            barrier(world)
             del sequence
-            seq_len = grown
-            sequence, replay_ms = build(seq_len)
-        region = 0.05 if args.quick else REGION_S
-        replays_per_step = max(1, math.ceil(region * 1e3 / (args.steps * replay_ms)))
-        passes_per_step = replays_per_step * seq_len    # per rank: the aggregate counts every rank's own rows x passes
+            return {"own_ms": own, "passes_per_step": replays_per_step * n, "seq_len": n,
+                    "clocks": clocks.window(t_wall0, t_wall1) if (clocks is not None and with_clocks) else None}
 
-        for _ in range(max(args.warmup, 3) * replays_per_step if not args.quick else 1):
-            sequence.replay()
-        barrier(world)
-        t_wall0 = time.monotonic()
-        e0.record()
-        for _ in range(args.steps * replays_per_step):
-            sequence.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        t_wall1 = time.monotonic()
-        own_ms = e0.elapsed_time(e1)
-        dev_ms = max_over_ranks(own_ms, world, dev)
-        rows_done = sum_over_ranks(float(rows) * args.steps * passes_per_step, world, dev)   # samples of all ranks
-        barrier(world)
-
-        passes = args.steps * passes_per_step
-        pass_ms = own_ms / passes
-        kern_ms = pass_ms / max(self.kernels_per_pass, 1)
-        if wl.bound == "hbm":
-            alg = wl.bytes_per_row * rows + wl.fixed_bytes
-            achieved = alg / (kern_ms * 1e-3) / 1e9
-            peak, unit = float(self.peaks["hbm_gbs"]), "GB/s"
-        else:
-            alg = wl.flops_per_row * rows
-            achieved = alg / max(self.kernels_per_pass, 1) / (kern_ms * 1e-3) / 1e12
-            peak, unit = float(self.peaks.get("bf16_tflops_sustained", self.peaks["bf16_tflops"])), "TFLOP/s"
-        traffic = TRAFFIC_BYTES.get(wl.key)
-        roofline = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                    "traffic": traffic * rows / wl.rows if traffic else None,
+        def roofline_of(own_ms, passes):
+            pass_ms = own_ms / passes
+            kern_ms = pass_ms / max(self.kernels_per_pass, 1)
+            if wl.bound == "hbm":
+                alg = wl.bytes_per_row * rows + wl.fixed_bytes
+                achieved = alg / (kern_ms * 1e-3) / 1e9
+                peak, unit = float(self.peaks["hbm_gbs"]), "GB/s"
+            else:
+                alg = wl.flops_per_row * rows
+                achieved = alg / max(self.kernels_per_pass, 1) / (kern_ms * 1e-3) / 1e12
+                peak, unit = float(self.peaks.get("bf16_tflops_sustained", self.peaks["bf16_tflops"])), "TFLOP/s"
+            return {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                     "algorithmic": alg, "kernel_ms": kern_ms, "kernels_per_pass": self.kernels_per_pass,
                     "launches_timed": passes * self.kernels_per_pass, "region_ms": own_ms,
                     "vs_nominal": achieved / 8000.0 if wl.bound == "hbm" else achieved / 2250.0}
+
+        lanes = 1 if args.no_graphs else max(1, args.lanes)
+        main = timed(lanes, seq_len, True)
+        own_ms = main["own_ms"]
+        passes_per_step = main["passes_per_step"]      # per rank: the aggregate counts every rank's own rows x passes
+        dev_ms = max_over_ranks(own_ms, world, dev)
+        rows_done = sum_over_ranks(float(rows) * args.steps * passes_per_step, world, dev)   # samples of all ranks
+        passes = args.steps * passes_per_step
+        roofline = roofline_of(own_ms, passes)
+        traffic = TRAFFIC_BYTES.get(wl.key)
+        roofline["traffic"] = traffic * rows / wl.rows if traffic else None
+        roofline["passes_in_flight"] = lanes
+        if lanes > 1:
+            # the same launches one at a time (every launch waits for the one before it): what one launch takes by itself
+            alone = timed(1, seq_len, False)
+            r1 = roofline_of(alone["own_ms"], args.steps * alone["passes_per_step"])
+            roofline["one_at_a_time"] = {k: r1[k] for k in ("achieved", "frac", "kernel_ms", "launches_timed", "region_ms", "vs_nominal")}
         result = {
             "rows_per_gpu": rows, "rows_done_all_ranks": rows_done, "passes_per_step": passes_per_step, "ms_per_step": dev_ms / args.steps,
             "ms_per_pass": dev_ms / passes, "timed_region_ms": dev_ms, "pool_slots": pool_n,
-            "pool_mib": pool_n * slot_bytes >> 20, "passes_per_graph": seq_len,
+            "pool_mib": pool_n * slot_bytes >> 20, "passes_per_graph": main["seq_len"], "passes_in_flight": lanes,
             "gpu_launches": passes * self.kernels_per_pass, "roofline": roofline,
-            "clocks": clocks.window(t_wall0, t_wall1) if clocks is not None else None,
+            "clocks": main["clocks"],
         }
+        region = 0.05 if args.quick else REGION_S
         if args.with_library and world == 1:
-            del sequence
             result["library"] = self.library(pool, pool_n, region, own_ms / passes)
         del pool
         return result
@@ -759,7 +778,8 @@ def gpu_arm(args, keys):
             "gpu_launches": head["gpu_launches"], "clocks": clock_info,
             "passes_per_step": head["passes_per_step"],
             "run": {"sharding": f"fixed configuration, rows partitioned over {world} GPU(s), no data-path collective",
-                    "step": "passes_per_step back-to-back passes of the compiled plan, replayed from CUDA graphs",
+                    "step": "passes_per_step passes of the compiled plan over distinct batches, replayed from CUDA graphs with "
+                            f"{head.get('passes_in_flight', 1)} independent passes in flight (roofline.one_at_a_time: the same launches serialised)",
                     "l2": "a rotating pool of distinct batches larger than 4x L2 (pool_mib per configuration)",
                     "timing": "CUDA events on the launching stream, max over ranks"},
             "host_link": pcie, "per_config": per,
@@ -781,6 +801,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="short device-resident regions only (for profiler runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch the plan directly instead of replaying a CUDA graph")
+    ap.add_argument("--lanes", type=int, default=LANES,
+                    help="independent passes in flight inside a captured sequence (Callable.capture_sequence(lanes=...)); "
+                         "1 = every launch waits for the one before it")
     ap.add_argument("--with-library", action="store_true",
                     help="one GPU: also time eager PyTorch's own kernels on the same batches (per_config[*].library)")
     ap.add_argument("--shard-of", type=int, default=1,

@@ -362,13 +362,17 @@ class Callable:
         what keeps microsecond-scale plans from being launch-bound."""
         return GraphedCall(self, [tuple(device_tensors)])
 
-    def capture_sequence(self, input_sets, keep_outputs: str = "all") -> "GraphedCall":
+    def capture_sequence(self, input_sets, keep_outputs: str = "all", lanes: int = 1) -> "GraphedCall":
         """Record one run of the plan per entry of `input_sets` (tuples of device tensors)
-        back to back in a single CUDA graph: one driver call replays the whole sequence.
+        in a single CUDA graph: one driver call replays the whole sequence.
         ``keep_outputs="first"`` keeps only the first run's output tensors; the later runs'
         outputs are released inside the capture, so the graph's memory pool holds two runs'
-        worth of outputs instead of one per run (long sequences of large graphs)."""
-        return GraphedCall(self, [tuple(t) for t in input_sets], keep_outputs=keep_outputs)
+        worth of outputs instead of one per run (long sequences of large graphs).
+        ``lanes`` > 1 records run i on branch ``i % lanes`` of the graph: the runs are independent
+        of one another (each has its own inputs and outputs), so up to `lanes` of them are in flight
+        at a time and one run's ramp-up and tail overlap another's steady state.  Runs on one
+        branch stay in order; every branch has its own scratch buffers."""
+        return GraphedCall(self, [tuple(t) for t in input_sets], keep_outputs=keep_outputs, lanes=lanes)
 
     # reference API (callable.py:96-152)
     def get_artifact(self) -> CompiledArtifact:
@@ -389,9 +393,11 @@ class GraphedCall:
     output tuple of the first run, ``all_outputs`` one tuple per run; the tensors are reused by
     every replay."""
 
-    def __init__(self, fn: Callable, input_sets, keep_outputs: str = "all"):
+    def __init__(self, fn: Callable, input_sets, keep_outputs: str = "all", lanes: int = 1):
         if keep_outputs not in ("all", "first"):
             raise ValueError("keep_outputs is 'all' or 'first'")
+        if lanes < 1:
+            raise ValueError("lanes must be at least 1")
         if not input_sets or any(not ts or any(t.device.type != "cuda" for t in ts) for ts in input_sets):
             raise DeviceError("CUDA graphs capture device-resident inputs only")
         self.fn = fn
@@ -405,14 +411,36 @@ class GraphedCall:
             fn._run_plan(dict(envs[0]), device, rows[0])        # warm-up: lazy initialisation, constants
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
+        self.lanes = lanes = min(lanes, len(input_sets))
+        ex = fn._exec()
+        if lanes > 1:
+            # every lane's scratch exists before the capture (allocations inside it would come from the graph's pool)
+            for lane in range(1, lanes):
+                ex.workspace_lane = lane
+                with torch.cuda.device(device), torch.cuda.stream(side):
+                    fn._run_plan(dict(envs[0]), device, rows[0])
+            ex.workspace_lane = 0
+            torch.cuda.current_stream(device).wait_stream(side)
+            torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.device(device), torch.cuda.graph(self.graph):
-            if keep_outputs == "all":
-                self.all_outputs = [tuple(fn._run_plan(dict(env), device, r)) for env, r in zip(envs, rows)]
-            else:
-                self.all_outputs = [tuple(fn._run_plan(dict(envs[0]), device, rows[0]))]
-                for env, r in zip(envs[1:], rows[1:]):
-                    fn._run_plan(dict(env), device, r)        # outputs dropped: their blocks are reused by the next run
+        self.all_outputs = []
+        try:
+            with torch.cuda.device(device), torch.cuda.graph(self.graph):
+                main = torch.cuda.current_stream(device)
+                branches = [main] + [torch.cuda.Stream(device=device) for _ in range(lanes - 1)]
+                for b in branches[1:]:
+                    b.wait_stream(main)                       # fork
+                for i, (env, r) in enumerate(zip(envs, rows)):
+                    ex.workspace_lane = i % lanes
+                    with torch.cuda.stream(branches[i % lanes]):
+                        out = fn._run_plan(dict(env), device, r)
+                        if keep_outputs == "all" or i == 0:
+                            self.all_outputs.append(tuple(out))
+                        del out                               # dropped outputs: their blocks are reused by the branch's next run
+                for b in branches[1:]:
+                    main.wait_stream(b)                       # join
+        finally:
+            ex.workspace_lane = 0
         self.outputs = self.all_outputs[0]
         self.runs = len(input_sets)
         self.n_kernels = self.runs * sum(1 for l in fn.launches if l.template)

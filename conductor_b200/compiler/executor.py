@@ -66,12 +66,15 @@ class GCUKernelExecutor:
         self.lib = load_library()
         self._workspaces: dict[tuple, tuple] = {}
         self._item_cache: dict[tuple, tuple] = {}
+        # which of several concurrent replays of one plan the launches being bound belong to: runs
+        # captured on different streams of one graph must not share scratch (see Callable.capture_sequence)
+        self.workspace_lane = 0
 
     def workspace_for(self, launch: KernelLaunch, ins, outs, in_desc, out_desc, params_ptr, params_size):
-        """Scratch of the size the library asks for, one buffer per (device, launch).  Launches that
-        share a buffer are ordered by the stream they run on; a plan replayed from several streams
-        at once needs one Callable per stream."""
-        key = (ins[0].device, id(launch))
+        """Scratch of the size the library asks for, one buffer per (device, launch, lane).  Launches
+        that share a buffer are ordered by the stream they run on; runs of one plan that are in flight
+        at the same time are bound under different `workspace_lane` values."""
+        key = (ins[0].device, id(launch), self.workspace_lane)
         hit = self._workspaces.get(key)
         sig = launch._marshal[0] if launch._marshal is not None else None
         if hit is not None and hit[0] == sig and sig is not None:

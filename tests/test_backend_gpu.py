@@ -102,6 +102,45 @@ def test_graph_capture_replays_the_plan():
     assert torch.equal(seq.all_outputs[1][0], seq.all_outputs[0][0]) and seq.n_kernels == 2
 
 
+@pytest.mark.parametrize("lanes", [2, 3])
+def test_captured_sequence_with_runs_in_flight_matches_single_calls(lanes):
+    """Runs recorded on several branches of one graph overlap in time; each must still produce what a
+    call by itself produces (the attention launches of different branches need their own tile counters)."""
+    from conductor_b200.compiler.gcu_backend import get_gcu_backend
+
+    get_gcu_backend().clear_cache()            # the plans looked up below are the ones compiled here
+    sets = [tuple(t.to(DEV) for t in wl.inputs_attention(2, 4, 512, 128, seed=300 + i)) for i in range(5)]
+    f = compiled(wl.causal_attention)
+    with torch.no_grad():
+        want = [f(*s).clone() for s in sets]
+    plan = list(get_gcu_backend()._compiled_functions.values())[-1]
+    seq = plan.capture_sequence(sets, lanes=lanes)
+    assert seq.lanes == lanes and seq.runs == 5
+    for _ in range(3):
+        seq.replay()
+    torch.cuda.synchronize()
+    for got, w in zip(seq.all_outputs, want):
+        assert torch.equal(got[0], w)
+    first = plan.capture_sequence(sets, keep_outputs="first", lanes=lanes)
+    (out,) = first.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want[0])
+    # a reduction with its inputs replaced between replays
+    xs = [tuple(t.to(DEV) for t in wl.inputs_reduce_mean(512, 4096, seed=310 + i)) for i in range(4)]
+    g = compiled(wl.reduce_mean_fusion)
+    with torch.no_grad():
+        g(*xs[0])
+    plan = list(get_gcu_backend()._compiled_functions.values())[-1]
+    seq = plan.capture_sequence(xs, lanes=lanes)
+    seq.replay()
+    xs[1][0].mul_(3)
+    seq.replay()
+    torch.cuda.synchronize()
+    with torch.no_grad():
+        for got, x in zip(seq.all_outputs, xs):
+            assert torch.equal(got[0], g(*x))
+
+
 def test_wrong_shape_at_call_time_raises():
     from conductor.utils.exceptions import ExecutionError
     from conductor_b200.compiler.gcu_backend import get_gcu_backend
