@@ -11,6 +11,7 @@ allocated from the plan's recorded shapes instead of ``empty_like(inputs[0])``
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Optional, Sequence
 
 import torch
@@ -67,8 +68,17 @@ class GCUKernelExecutor:
         self._workspaces: dict[tuple, tuple] = {}
         self._item_cache: dict[tuple, tuple] = {}
         # which of several concurrent replays of one plan the launches being bound belong to: runs
-        # captured on different streams of one graph must not share scratch (see Callable.capture_sequence)
-        self.workspace_lane = 0
+        # captured on different streams of one graph must not share scratch (see Callable.capture_sequence).
+        # Per thread: another thread's calls keep lane 0 while this one records a sequence.
+        self._lane = threading.local()
+
+    @property
+    def workspace_lane(self) -> int:
+        return getattr(self._lane, "value", 0)
+
+    @workspace_lane.setter
+    def workspace_lane(self, lane: int) -> None:
+        self._lane.value = int(lane)
 
     def workspace_for(self, launch: KernelLaunch, ins, outs, in_desc, out_desc, params_ptr, params_size):
         """Scratch of the size the library asks for, one buffer per (device, launch, lane).  Launches
