@@ -66,8 +66,9 @@
 // halves' exponential passes fall into step; making the paired warps of a scheduler take turns at the
 // exponentials made it 301 / 1723 / 1044; (3) this kernel with one MMA-issuing warp per half:
 // 207 / 1265 / 692.  With the exponentials replaced by a multiplication (wrong results, diagnosis
-// only) this kernel runs 183 / 1061 / 614: the softmax pass is bound by the latency of its dependent
-// instruction chains at one warp per scheduler, not by the special-function unit's throughput.
+// only) this kernel runs 183 / 1061 / 614: the exponential pass itself shrinks (1595 -> 895 cycles per
+// block), but the wait for the scores grows by as much -- the MMA warp, which serves the two halves in
+// turn and needs ~2000 cycles per group of 16 MMAs all told, sets the pace, not the special-function unit.
 // Micro-benchmarks beside it: a 128x128x16 MMA executes in 64.6 cycles whatever the source and layout of
 // its operands (52.7 at N=64, 128.6 at N=256); the issuing thread stays blocked while the pipe works
 // (a batch of 16 MMAs returns after 935 cycles: about one and a half MMAs are queued), and the commit
