@@ -85,6 +85,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 #endif
 constexpr uint32_t kMaxPolls = CDR_MAX_POLLS;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  // a phase that has already completed is seen by test_wait in ~15 cycles, where try_wait (which may
+  // suspend the thread) takes ~80 even then: look first, wait only if there is something to wait for
+  if (mbar_test(bar, parity)) return true;
   for (uint32_t i = 0; i < kMaxPolls; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
