@@ -154,3 +154,23 @@ def test_cache_key_covers_the_constants_a_plan_captures():
     w1 = [b.constant_value for b in a1.dag.buffers if getattr(b, "constant_value", None) is not None]
     w2 = [b.constant_value for b in a2.dag.buffers if getattr(b, "constant_value", None) is not None]
     assert w1 and w2 and w1[0] is not w2[0]
+
+
+def test_scratch_lane_of_the_executor_is_per_thread():
+    """Runs recorded on different branches of one CUDA graph are bound under different lanes (their
+    scratch buffers must not be shared); the lane is state of the recording thread only."""
+    import threading
+
+    from conductor_b200.compiler.executor import get_executor
+
+    ex = get_executor()
+    assert ex.workspace_lane == 0
+    ex.workspace_lane = 2
+    seen = []
+    t = threading.Thread(target=lambda: seen.append(ex.workspace_lane))
+    t.start()
+    t.join()
+    try:
+        assert seen == [0] and ex.workspace_lane == 2
+    finally:
+        ex.workspace_lane = 0
