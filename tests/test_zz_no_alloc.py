@@ -94,6 +94,34 @@ def test_noalloc_leaves_the_device_allocation_untouched():
     assert abs(got.item() - host) <= F32_TOL * max(1.0, abs(host))
 
 
+def test_noalloc_runs_inside_a_stream_capture_on_a_program_it_has_not_seen():
+    """A caller that records its step in a CUDA graph may not compile, load a module or allocate while
+    the capture is open.  After one call on the device (which resolves the scratch array's address)
+    a program this process has never run is launched inside a capture and replayed twice."""
+    x = torch.randn(300, 520, device=DEV)
+    got = torch.full((), float("nan"), device=DEV)
+    warm = params(abi.ew_program(1, [], [0]), ReduceOp.SUM)
+    rc, msg = noalloc([x], got, warm)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    fresh = params(abi.ew_program(1, [(EwOp.SIGMOID, 0, 0, 0, 0, torch.float32), (EwOp.MUL, 1, 0, 0, 0, torch.float32)], [2]),
+                   ReduceOp.SUM)                                # sum(x * sigmoid(x)): a chain no other test reduces
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            rc, msg = noalloc([x], got, fresh)
+    torch.cuda.current_stream().wait_stream(side)
+    assert rc == 0, msg
+    host = (x.cpu().double() * torch.sigmoid(x.cpu().double())).sum().item()
+    for _ in range(2):
+        got.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert abs(got.item() - host) <= 1e-4 * max(1.0, abs(host)), (got.item(), host)
+
+
 def test_noalloc_reports_bad_arguments():
     x = torch.randn(8, 8, device=DEV)
     out = torch.empty((), device=DEV)
